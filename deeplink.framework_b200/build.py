@@ -1,0 +1,107 @@
+"""Build recipe for the three native libraries (nvcc, sm_100a only).
+
+    lib/libdipu_vendor_b200.so   vendor runtime: device / stream / event / memory API, caching allocators,
+                                 stream and event pools, DICL communicator (NCCL bound at run time)
+    lib/libdiopirt_minihost.so   a small DIOPI host (the diopirt callbacks over plain tensor structs)
+    lib/libdiopi_impl.so         the DIOPI operator library: hand-written sm_100a kernels
+
+Objects go to build/ (ignored by git), libraries to lib/ next to this file so that they travel with the tree.
+Run as a script or call build().
+"""
+import concurrent.futures
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+CSRC = os.path.join(HERE, "csrc")
+OBJ = os.path.join(ROOT, "build", "obj")
+LIB = os.path.join(HERE, "lib")
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I", os.path.join(ROOT, "include"),
+          "-diag-suppress", "177"]
+
+
+def _nccl_include():
+    try:
+        import nvidia.nccl  # noqa: F401  (namespace package shipped with torch's wheels)
+        for p in nvidia.nccl.__path__:
+            inc = os.path.join(p, "include")
+            if os.path.exists(os.path.join(inc, "nccl.h")):
+                return inc
+    except Exception:
+        pass
+    for inc in ("/usr/include", "/usr/local/cuda/include"):
+        if os.path.exists(os.path.join(inc, "nccl.h")):
+            return inc
+    raise RuntimeError("nccl.h not found")
+
+
+def _sources(sub):
+    d = os.path.join(CSRC, sub)
+    return sorted(os.path.join(d, f) for f in os.listdir(d) if f.endswith((".cu", ".cpp")))
+
+
+def _headers():
+    out = []
+    for base in (CSRC, os.path.join(ROOT, "include")):
+        for dp, _, fs in os.walk(base):
+            out += [os.path.join(dp, f) for f in fs if f.endswith((".h", ".cuh", ".hpp"))]
+    return out
+
+
+def _compile(src, extra):
+    rel = os.path.relpath(src, CSRC).replace(os.sep, "_")
+    obj = os.path.join(OBJ, rel + ".o")
+    newest = max([os.path.getmtime(src), os.path.getmtime(__file__)] + [os.path.getmtime(h) for h in _headers()])
+    if os.path.exists(obj) and os.path.getmtime(obj) >= newest:
+        return obj
+    cmd = [NVCC] + ARCH + COMMON + extra + ["-c", src, "-o", obj]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, r.stdout, r.stderr))
+    return obj
+
+
+def _link(name, objs, extra):
+    out = os.path.join(LIB, name)
+    if os.path.exists(out) and all(os.path.getmtime(out) >= os.path.getmtime(o) for o in objs):
+        return out
+    cmd = [NVCC] + ARCH + ["-shared", "-o", out] + objs + extra
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("link failed for %s:\n%s\n%s" % (name, r.stdout, r.stderr))
+    return out
+
+
+def build(verbose=False):
+    os.makedirs(OBJ, exist_ok=True)
+    os.makedirs(LIB, exist_ok=True)
+    jobs = []
+    for sub, extra in (("vendor", ["-I", _nccl_include()]), ("minihost", []), ("diopi", [])):
+        for src in _sources(sub):
+            jobs.append((sub, src, extra))
+    objs = {"vendor": [], "minihost": [], "diopi": []}
+    with concurrent.futures.ThreadPoolExecutor(max_workers=max(1, os.cpu_count() or 1)) as ex:
+        futs = {ex.submit(_compile, src, extra): (sub, src) for sub, src, extra in jobs}
+        for f in concurrent.futures.as_completed(futs):
+            sub, src = futs[f]
+            objs[sub].append(f.result())
+            if verbose:
+                print("compiled", os.path.relpath(src, ROOT), flush=True)
+    for k in objs:
+        objs[k].sort()
+    vendor = _link("libdipu_vendor_b200.so", objs["vendor"], ["-ldl", "-lpthread"])
+    _link("libdiopirt_minihost.so", objs["minihost"],
+          ["-L", LIB, "-l:libdipu_vendor_b200.so", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"])
+    # the diopirt callbacks stay undefined here: the host that loads this library provides them (DIPU, or the minihost)
+    _link("libdiopi_impl.so", objs["diopi"], [])
+    return [vendor, os.path.join(LIB, "libdiopirt_minihost.so"), os.path.join(LIB, "libdiopi_impl.so")]
+
+
+if __name__ == "__main__":
+    for p in build(verbose=True):
+        print("built", p)

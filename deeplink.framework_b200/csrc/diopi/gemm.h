@@ -1,0 +1,29 @@
+// Internal description of one (batched) matrix product and the kernels that can run it.
+#pragma once
+
+#include "common.h"
+
+namespace b200 {
+
+// C[b,m,n] = alpha * sum_k A[b,m,k] * B[b,k,n] + beta * bias[b,m,n]; all strides in elements.
+struct GemmProblem {
+    int64_t batch = 1, M = 0, N = 0, K = 0;
+    const void* A = nullptr;
+    int64_t a_sb = 0, a_sm = 0, a_sk = 0;
+    const void* B = nullptr;
+    int64_t b_sb = 0, b_sk = 0, b_sn = 0;
+    void* C = nullptr;
+    int64_t c_sb = 0, c_sm = 0, c_sn = 0;
+    const void* bias = nullptr;  // optional; strides may be 0 (broadcast)
+    int64_t bias_sb = 0, bias_sm = 0, bias_sn = 0;
+    diopiDtype_t ab_dtype = diopi_dtype_unsupported;
+    diopiDtype_t c_dtype = diopi_dtype_unsupported;
+    diopiDtype_t bias_dtype = diopi_dtype_unsupported;
+    float alpha = 1.f, beta = 0.f;
+};
+
+// tcgen05 / TMEM / TMA kernel (bf16 or fp16 operands, fp32 accumulation).
+bool gemm_tc_eligible(const GemmProblem& g);
+diopiError_t gemm_tc_launch(const GemmProblem& g, cudaStream_t stream);
+
+}  // namespace b200

@@ -1,0 +1,421 @@
+// Dense contraction on the 5th-generation tensor cores: C[b] = alpha * A[b] * B[b] + beta * bias.
+//
+// One persistent CTA per SM, 192 threads in three roles:
+//   warp 0      TMA producer   - streams 128 x 64 tiles of A and BN x 64 tiles of B (bf16 / fp16) into a ring of
+//                                128-byte-swizzled shared-memory stages (cp.async.bulk.tensor, per-CTA loads only)
+//   warp 1      MMA issuer     - one thread issues tcgen05.mma (M=128, N=BN, K=16) accumulating fp32 in tensor
+//                                memory; two accumulators of BN columns each are double-buffered so the epilogue of
+//                                tile i overlaps the main loop of tile i+1
+//   warps 2..5  epilogue       - tcgen05.ld the accumulator (each warp its own 32-lane quarter), scale / add bias,
+//                                convert and store 16-byte vectors straight to global memory
+// Stages and accumulators are handed over with mbarriers; every wait is bounded (see gemm_sm100.cuh) and a
+// time-out is reported through the status word instead of hanging.
+//
+// Operand layouts (taken from the tensors' strides, no copies):
+//   A  [batch, M, K]  K contiguous
+//   B  [batch, N, K]  K contiguous  ("K-major": the transposed view of an [N,K] weight that F.linear passes), or
+//      [batch, K, N]  N contiguous  ("MN-major": a plain [K,N] matrix, e.g. V in P*V)
+//   C  [batch, M, N]  N contiguous, row pitch ldc
+// Tile order groups 8 row-blocks so that a wave of CTAs shares A and B tiles in L2.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "gemm.h"
+#include "gemm_sm100.cuh"
+#include "device_utils.cuh"
+
+namespace b200 {
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128;
+constexpr int BK = 64;          // 64 two-byte elements = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr int kGroupM = 8;
+constexpr int kSmemLimit = 232448;  // 227 KiB per CTA
+
+template <int BN>
+struct TileCfg {
+    static constexpr int kABytes = BM * BK * 2;
+    static constexpr int kBBytes = BN * BK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStagesRaw = (kSmemLimit - 2048) / kStageBytes;
+    static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
+    static constexpr int kTmemCols = (2 * BN) < 32 ? 32 : (2 * BN);
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
+};
+
+struct TcParams {
+    int M, N, K, batch;
+    int m_blocks, n_blocks, k_blocks;
+    int64_t ldc, stride_cb;
+    void* C;
+    const void* bias;  // same dtype as C, may be nullptr
+    int64_t bias_sb, bias_sr, bias_sc;
+    float alpha, beta;
+    uint32_t idesc;
+    int b_mn_major;
+    int c_vec_ok;
+    uint32_t* status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, const TcParams& p, int* b, int* mb, int* nb) {
+    const int per_batch = p.m_blocks * p.n_blocks;
+    *b = tile / per_batch;
+    const int t = tile - *b * per_batch;
+    const int group_sz = kGroupM * p.n_blocks;
+    const int g = t / group_sz;
+    const int first_m = g * kGroupM;
+    const int rows = min(p.m_blocks - first_m, kGroupM);
+    const int r = t - g * group_sz;
+    *mb = first_m + r % rows;
+    *nb = r / rows;
+}
+
+template <typename TOut>
+__device__ __forceinline__ void store_chunk(const TcParams& p, const uint32_t (&acc)[32], int b, int row, int col0) {
+    if (row >= p.M) return;
+    TOut* crow = static_cast<TOut*>(p.C) + static_cast<int64_t>(b) * p.stride_cb + static_cast<int64_t>(row) * p.ldc;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]) * p.alpha;
+    if (p.bias != nullptr) {
+        const TOut* brow = static_cast<const TOut*>(p.bias) + static_cast<int64_t>(b) * p.bias_sb + static_cast<int64_t>(row) * p.bias_sr;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (col0 + j < p.N) v[j] += p.beta * to_f32(brow[static_cast<int64_t>(col0 + j) * p.bias_sc]);
+        }
+    }
+    if (p.c_vec_ok && col0 + 32 <= p.N) {
+        constexpr int V = 16 / sizeof(TOut);
+#pragma unroll
+        for (int j = 0; j < 32; j += V) {
+            Vec16<TOut> o;
+#pragma unroll
+            for (int e = 0; e < V; ++e) o.v[e] = from_f32<TOut>(v[j + e]);
+            st16(crow + col0 + j, o);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (col0 + j < p.N) crow[col0 + j] = from_f32<TOut>(v[j]);
+        }
+    }
+}
+
+template <int BN, typename TOut>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
+    using Cfg = TileCfg<BN>;
+    constexpr int STAGES = Cfg::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte swizzle patterns repeat every 1024 bytes: stage buffers must start on that boundary
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * Cfg::kABytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::kStageBytes);
+    uint64_t* full_bar = bars;                     // [STAGES] producer -> MMA
+    uint64_t* empty_bar = bars + STAGES;           // [STAGES] MMA -> producer
+    uint64_t* acc_full = bars + 2 * STAGES;        // [2] MMA -> epilogue
+    uint64_t* acc_empty = bars + 2 * STAGES + 2;   // [2] epilogue -> MMA
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int total_tiles = p.batch * p.m_blocks * p.n_blocks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                int b, mb, nb;
+                tile_coords(tile, p, &b, &mb, &nb);
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+                    tma_load_3d(smem_a + stage * Cfg::kABytes, &map_a, &full_bar[stage], kb * BK, mb * BM, b);
+                    if (!p.b_mn_major) {
+                        tma_load_3d(smem_b + stage * Cfg::kBBytes, &map_b, &full_bar[stage], kb * BK, nb * BN, b);
+                    } else {
+#pragma unroll
+                        for (int g = 0; g < BN / 64; ++g) {
+                            tma_load_3d(smem_b + stage * Cfg::kBBytes + g * (64 * BK * 2), &map_b, &full_bar[stage], nb * BN + g * 64, kb * BK, b);
+                        }
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+                const int acc = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1u;
+                if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem_a + stage * Cfg::kABytes);
+                    const uint32_t b_addr = smem_u32(smem_b + stage * Cfg::kBBytes);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // K-major operand: 8-row groups are 1024 bytes apart, a K step of 16 elements moves 32 bytes inside
+                        // the swizzled row. MN-major B: 64-column groups are 8192 bytes apart (leading offset), 8-row K
+                        // groups 1024 bytes apart, a K step of 16 rows moves 2048 bytes.
+                        const uint64_t da = make_smem_desc_sw128(a_addr + k * (UMMA_K * 2), 16, 1024);
+                        const uint64_t db = p.b_mn_major ? make_smem_desc_sw128(b_addr + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                                         : make_smem_desc_sw128(b_addr + k * (UMMA_K * 2), 16, 1024);
+                        umma_f16_ss(d_tmem, da, db, p.idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[stage]);  // stage reusable once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) umma_commit(&acc_full[acc]);
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5) ----------------
+        const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are the ones this warp may read
+        int local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+            int b, mb, nb;
+            tile_coords(tile, p, &b, &mb, &nb);
+            const int acc = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1u;
+            if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const int row = mb * BM + quarter * 32 + lane;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int col0 = nb * BN + c * 32;
+                if (col0 >= p.N) break;  // warp-uniform
+                uint32_t r[32];
+                tmem_ld_32x32(t_row + c * 32, r);
+                tmem_ld_wait();
+                store_chunk<TOut>(p, r, b, row, col0);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (*abort_flag != 0) {
+        // A wait timed out. Give copies and MMAs that are still in flight time to land before the CTA's shared and
+        // tensor memory are released, then report.
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+        if (threadIdx.x == 0) atomicExch(p.status, 1u);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();  // the issuing lane took a different path: reconverge before the warp-wide dealloc
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                              const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode_fn() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeFn>(sym);
+        }
+        (void)cudaGetLastError();
+    });
+    return fn;
+}
+
+// 3-D map over [batch, rows, inner] with a [1, box_rows, 64] box and 128-byte swizzle.
+bool encode_map(CUtensorMap* map, bool is_bf16, const void* base, int64_t inner, int64_t rows, int64_t batch, int64_t row_pitch_elems,
+                int64_t batch_pitch_elems, int box_rows) {
+    EncodeFn fn = get_encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(batch)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_pitch_elems * 2), static_cast<cuuint64_t>(batch_pitch_elems * 2)};
+    const cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(box_rows), 1u};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    const CUresult r = fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides,
+                          box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+uint32_t* status_word() {
+    // one status word per device, allocated on first use and kept for the life of the process
+    static uint32_t* words[64] = {nullptr};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (words[dev] == nullptr) {
+        uint32_t* w = nullptr;
+        if (cudaMalloc(&w, sizeof(uint32_t)) != cudaSuccess) return nullptr;
+        cudaMemset(w, 0, sizeof(uint32_t));
+        words[dev] = w;
+    }
+    return words[dev];
+}
+
+template <int BN, typename TOut>
+cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int grid, cudaStream_t stream) {
+    using Cfg = TileCfg<BN>;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    gemm_tc_kernel<BN, TOut><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(ma, mb, p);
+    return cudaPeekAtLastError();
+}
+
+template <typename TOut>
+cudaError_t launch_tc_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int grid, cudaStream_t stream) {
+    switch (bn) {
+        case 256: return launch_tc<256, TOut>(ma, mb, p, grid, stream);
+        case 128: return launch_tc<128, TOut>(ma, mb, p, grid, stream);
+        case 64: return launch_tc<64, TOut>(ma, mb, p, grid, stream);
+        default: return launch_tc<32, TOut>(ma, mb, p, grid, stream);
+    }
+}
+
+}  // namespace
+
+bool gemm_tc_eligible(const GemmProblem& g) {
+    if (!(g.ab_dtype == diopi_dtype_bfloat16 || g.ab_dtype == diopi_dtype_float16)) return false;
+    if (!(g.c_dtype == g.ab_dtype || g.c_dtype == diopi_dtype_float32)) return false;
+    if (g.M <= 0 || g.N <= 0 || g.K <= 0 || g.batch <= 0) return false;
+    if (g.M > 0x7fffffffLL || g.N > 0x7fffffffLL || g.K > 0x7fffffffLL) return false;
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    auto pitch_ok = [](int64_t elems) { return elems > 0 && (elems * 2) % 16 == 0 && elems * 2 < (1ll << 40); };
+    // A: K contiguous
+    if (g.a_sk != 1 || !al16(g.A) || !pitch_ok(g.a_sm)) return false;
+    if (g.batch > 1 && !pitch_ok(g.a_sb)) return false;
+    if (g.a_sm < g.K) return false;
+    // B: K contiguous or N contiguous
+    if (!al16(g.B)) return false;
+    if (g.b_sk == 1) {
+        if (!pitch_ok(g.b_sn) || g.b_sn < g.K) return false;
+    } else if (g.b_sn == 1) {
+        if (!pitch_ok(g.b_sk) || g.b_sk < g.N) return false;
+    } else {
+        return false;
+    }
+    if (g.batch > 1 && !pitch_ok(g.b_sb)) return false;
+    if (g.c_sn != 1 || g.c_sm < g.N) return false;
+    if (g.bias != nullptr && g.bias_dtype != g.c_dtype) return false;
+    const int64_t tiles = g.batch * ((g.M + BM - 1) / BM) * ((g.N + 31) / 32);
+    if (tiles > 0x7fffffffLL) return false;
+    return get_encode_fn() != nullptr;
+}
+
+diopiError_t gemm_tc_launch(const GemmProblem& g, cudaStream_t stream) {
+    const bool is_bf16 = g.ab_dtype == diopi_dtype_bfloat16;
+    const bool b_mn = g.b_sk != 1;
+    const int sms = sm_count();
+    const int64_t m_blocks = (g.M + BM - 1) / BM;
+    // widest tile that still yields at least one tile per SM; MN-major B needs whole 64-column swizzle groups
+    int bn = 256;
+    const int min_bn = b_mn ? 64 : 32;
+    while (bn > min_bn && (g.N <= bn / 2 || g.batch * m_blocks * ((g.N + bn - 1) / bn) < sms)) bn >>= 1;
+    const int64_t n_blocks = (g.N + bn - 1) / bn;
+
+    CUtensorMap ma, mb;
+    B200_CHECK(encode_map(&ma, is_bf16, g.A, g.K, g.M, g.batch, g.a_sm, g.batch > 1 ? g.a_sb : g.a_sm * g.M, BM),
+               "gemm: cuTensorMapEncodeTiled failed for A");
+    if (!b_mn) {
+        B200_CHECK(encode_map(&mb, is_bf16, g.B, g.K, g.N, g.batch, g.b_sn, g.batch > 1 ? g.b_sb : g.b_sn * g.N, bn),
+                   "gemm: cuTensorMapEncodeTiled failed for B (K-major)");
+    } else {
+        B200_CHECK(encode_map(&mb, is_bf16, g.B, g.N, g.K, g.batch, g.b_sk, g.batch > 1 ? g.b_sb : g.b_sk * g.K, BK),
+                   "gemm: cuTensorMapEncodeTiled failed for B (MN-major)");
+    }
+    TcParams p;
+    p.M = static_cast<int>(g.M); p.N = static_cast<int>(g.N); p.K = static_cast<int>(g.K); p.batch = static_cast<int>(g.batch);
+    p.m_blocks = static_cast<int>(m_blocks); p.n_blocks = static_cast<int>(n_blocks); p.k_blocks = static_cast<int>((g.K + BK - 1) / BK);
+    p.ldc = g.c_sm; p.stride_cb = g.c_sb; p.C = g.C;
+    p.bias = g.bias; p.bias_sb = g.bias_sb; p.bias_sr = g.bias_sm; p.bias_sc = g.bias_sn;
+    p.alpha = g.alpha; p.beta = g.beta;
+    p.idesc = make_idesc_f16(is_bf16 ? 1 : 0, b_mn, BM, bn);
+    p.b_mn_major = b_mn ? 1 : 0;
+    const int64_t c_es = dtype_size(g.c_dtype);
+    p.c_vec_ok = ((reinterpret_cast<uintptr_t>(g.C) & 15u) == 0 && (g.c_sm * c_es) % 16 == 0 && (g.batch == 1 || (g.c_sb * c_es) % 16 == 0)) ? 1 : 0;
+    p.status = status_word();
+    B200_CHECK(p.status != nullptr, "gemm: could not allocate the kernel status word");
+    const int64_t total = static_cast<int64_t>(p.batch) * m_blocks * n_blocks;
+    const int grid = static_cast<int>(total < sms ? total : sms);
+    cudaError_t e;
+    if (g.c_dtype == diopi_dtype_bfloat16) e = launch_tc_bn<bf16>(bn, ma, mb, p, grid, stream);
+    else if (g.c_dtype == diopi_dtype_float16) e = launch_tc_bn<fp16>(bn, ma, mb, p, grid, stream);
+    else e = launch_tc_bn<float>(bn, ma, mb, p, grid, stream);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        B200_FAIL("gemm: tcgen05 kernel launch failed: %s", cudaGetErrorString(e));
+    }
+    return diopiSuccess;
+}
+
+}  // namespace b200
+
+// Status of the tensor-core kernels on the current device: 0 = no wait has ever timed out.
+// Synchronises the device. Not part of DIOPI; exported for tests and health checks.
+extern "C" DIOPI_API int diopiB200GemmStatus(void) {
+    uint32_t* w = b200::status_word();
+    if (w == nullptr) return -1;
+    uint32_t v = 0;
+    if (cudaMemcpy(&v, w, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    return static_cast<int>(v);
+}

@@ -1,0 +1,167 @@
+// diopiRotaryEmbedding: rotate feature pairs of q/k by position-dependent angles.
+//
+// x is viewed as [tokens, heads, dim]; cos/sin as [table_rows, table_cols] with table_cols = dim/2 (one angle per
+// pair) or dim (full-width tables). Token t uses table row t % table_rows, so a [seq, dim/2] table broadcasts over
+// the batch and a [batch*seq, ...] table is used row for row. One thread owns 8 pairs: it reads two 16-byte
+// vectors of x (the two partners), the matching angles, and writes two vectors. Algorithmic traffic:
+// 2 * bytes(x) + table rows touched.
+//
+// Arithmetic follows the reference's CPU restatements: half-split pairs (i, i + dim/2)
+// (dicp/dicp/vendor/AscendGraph/ext_ops.py:24-33) and interleaved pairs (2i, 2i+1), i.e. complex multiplication
+// (dicp/test/model/llama/model.py:58-69). Products and sums are formed in fp32 and rounded once.
+#include "copy.h"
+#include "device_utils.cuh"
+
+namespace b200 {
+namespace {
+
+template <typename TC>
+__device__ __forceinline__ void load_angles8(const TC* p, float (&a)[8]) {
+    if constexpr (sizeof(TC) == 4) {
+        const float4 lo = *reinterpret_cast<const float4*>(p);
+        const float4 hi = *reinterpret_cast<const float4*>(p + 4);
+        a[0] = lo.x; a[1] = lo.y; a[2] = lo.z; a[3] = lo.w;
+        a[4] = hi.x; a[5] = hi.y; a[6] = hi.z; a[7] = hi.w;
+    } else {
+        const Vec16<TC> v = ld16(p);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] = to_f32(v.v[e]);
+    }
+}
+
+// Half-split layout, 2-byte element types, dim/2 a multiple of 8.
+template <typename T, typename TC>
+__global__ void __launch_bounds__(256) rope_half_kernel(const T* x, T* out, const TC* __restrict__ cos_t,
+                                                        const TC* __restrict__ sin_t, int64_t tokens, int heads, int dim, int64_t table_rows,
+                                                        int table_cols, float sin_sign) {
+    const int half = dim / 2;
+    const int chunks = half / 8;
+    const int64_t total = tokens * heads * chunks;
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
+        const int c = static_cast<int>(i % chunks);
+        const int64_t th = i / chunks;  // token * heads + head
+        const int64_t t = th / heads;
+        const int64_t row = t % table_rows;
+        const T* px = x + th * dim + c * 8;
+        const Vec16<T> x0 = ld16_stream(px);
+        const Vec16<T> x1 = ld16_stream(px + half);
+        float c0[8], s0[8], c1[8], s1[8];
+        load_angles8<TC>(cos_t + row * table_cols + c * 8, c0);
+        load_angles8<TC>(sin_t + row * table_cols + c * 8, s0);
+        if (table_cols == dim) {
+            load_angles8<TC>(cos_t + row * table_cols + half + c * 8, c1);
+            load_angles8<TC>(sin_t + row * table_cols + half + c * 8, s1);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { c1[e] = c0[e]; s1[e] = s0[e]; }
+        }
+        Vec16<T> o0, o1;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float a = to_f32(x0.v[e]), b = to_f32(x1.v[e]);
+            o0.v[e] = from_f32<T>(a * c0[e] - b * (sin_sign * s0[e]));
+            o1.v[e] = from_f32<T>(b * c1[e] + a * (sin_sign * s1[e]));
+        }
+        T* po = out + th * dim + c * 8;
+        st16_stream(po, o0);
+        st16_stream(po + half, o1);
+    }
+}
+
+// General variant: any float dtype for x and the tables, either layout, one pair per thread.
+template <typename C>
+__global__ void rope_generic_kernel(const void* x, void* out, diopiDtype_t x_dt, const void* cos_t, const void* sin_t, diopiDtype_t t_dt,
+                                    int64_t tokens, int heads, int dim, int64_t table_rows, int table_cols, C sin_sign, bool interleaved) {
+    const int half = dim / 2;
+    const int64_t total = tokens * heads * half;
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
+        const int p = static_cast<int>(i % half);
+        const int64_t th = i / half;
+        const int64_t t = th / heads;
+        const int64_t row = t % table_rows;
+        const int64_t i0 = th * dim + (interleaved ? 2 * p : p);
+        const int64_t i1 = th * dim + (interleaved ? 2 * p + 1 : p + half);
+        int64_t a0, a1;
+        if (table_cols == dim) {
+            a0 = row * table_cols + (interleaved ? 2 * p : p);
+            a1 = row * table_cols + (interleaved ? 2 * p + 1 : p + half);
+        } else {
+            a0 = a1 = row * table_cols + p;
+        }
+        const C xa = load_as<C>(x, x_dt, i0), xb = load_as<C>(x, x_dt, i1);
+        const C c0 = load_as<C>(cos_t, t_dt, a0), s0 = sin_sign * load_as<C>(sin_t, t_dt, a0);
+        const C c1 = load_as<C>(cos_t, t_dt, a1), s1 = sin_sign * load_as<C>(sin_t, t_dt, a1);
+        store_from<C>(out, x_dt, i0, xa * c0 - xb * s0);
+        store_from<C>(out, x_dt, i1, xb * c1 + xa * s1);
+    }
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" diopiError_t diopiRotaryEmbedding(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t x, diopiConstTensorHandle_t cos,
+                                             diopiConstTensorHandle_t sin, const bool conj, const bool interleaved) {
+    B200_VIEW(vo, out);
+    B200_VIEW(vx_raw, x);
+    B200_VIEW(vc_raw, cos);
+    B200_VIEW(vs_raw, sin);
+    B200_CHECK(vx_raw.ndim >= 2, "diopiRotaryEmbedding: x needs at least [heads, dim]");
+    B200_CHECK(vo.numel == vx_raw.numel && vo.dtype == vx_raw.dtype && vo.is_contiguous(),
+               "diopiRotaryEmbedding: out must be dense and match x in shape and dtype");
+    B200_CHECK(is_floating(vx_raw.dtype) && is_floating(vc_raw.dtype) && vc_raw.dtype == vs_raw.dtype, "diopiRotaryEmbedding: floating dtypes only, cos/sin alike");
+    B200_CHECK(vc_raw.numel == vs_raw.numel && vc_raw.ndim >= 1, "diopiRotaryEmbedding: cos and sin must have the same shape");
+    if (vo.numel == 0) return diopiSuccess;
+    TensorView vx, vc, vs;
+    if (make_contiguous(ctx, vx_raw, &vx) != diopiSuccess) return diopiErrorOccurred;
+    if (make_contiguous(ctx, vc_raw, &vc) != diopiSuccess) return diopiErrorOccurred;
+    if (make_contiguous(ctx, vs_raw, &vs) != diopiSuccess) return diopiErrorOccurred;
+    const int64_t dim = vx.shape[vx.ndim - 1];
+    const int64_t heads = vx.shape[vx.ndim - 2];
+    const int64_t tokens = vx.numel / (dim * heads);
+    const int64_t table_cols = vc.shape[vc.ndim - 1];
+    B200_CHECK(dim % 2 == 0, "diopiRotaryEmbedding: head dim must be even");
+    B200_CHECK(table_cols == dim || table_cols == dim / 2, "diopiRotaryEmbedding: cos/sin last dim must be dim or dim/2 (got %lld for dim %lld)",
+               (long long)table_cols, (long long)dim);
+    const int64_t table_rows = vc.numel / table_cols;
+    B200_CHECK(table_rows > 0 && tokens % table_rows == 0, "diopiRotaryEmbedding: %lld table rows do not tile %lld tokens", (long long)table_rows,
+               (long long)tokens);
+    cudaStream_t stream = stream_of(ctx);
+    const float sign = conj ? -1.f : 1.f;
+    const bool two_byte = vx.dtype == diopi_dtype_bfloat16 || vx.dtype == diopi_dtype_float16;
+    const bool tables_ok = (vc.dtype == vx.dtype || vc.dtype == diopi_dtype_float32) && vc.aligned(16) && vs.aligned(16) && (table_cols % 8 == 0);
+    if (!interleaved && two_byte && (dim / 2) % 8 == 0 && vx.aligned(16) && vo.aligned(16) && tables_ok) {
+        const int64_t total = tokens * heads * (dim / 16);
+        int64_t blocks = (total + 255) / 256;
+        const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
+        if (blocks > cap) blocks = cap;
+        const unsigned grid = static_cast<unsigned>(blocks);
+#define LAUNCH_ROPE(T, TC)                                                                                                                       \
+    rope_half_kernel<T, TC><<<grid, 256, 0, stream>>>(static_cast<const T*>(vx.data), static_cast<T*>(vo.data), static_cast<const TC*>(vc.data), \
+                                                      static_cast<const TC*>(vs.data), tokens, (int)heads, (int)dim, table_rows, (int)table_cols, sign)
+        if (vx.dtype == diopi_dtype_bfloat16) {
+            if (vc.dtype == diopi_dtype_float32) LAUNCH_ROPE(bf16, float); else LAUNCH_ROPE(bf16, bf16);
+        } else {
+            if (vc.dtype == diopi_dtype_float32) LAUNCH_ROPE(fp16, float); else LAUNCH_ROPE(fp16, fp16);
+        }
+#undef LAUNCH_ROPE
+    } else {
+        const int64_t total = tokens * heads * (dim / 2);
+        int64_t blocks = (total + 255) / 256;
+        const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
+        if (blocks > cap) blocks = cap;
+        const unsigned grid = static_cast<unsigned>(blocks);
+        if (vx.dtype == diopi_dtype_float64) {
+            rope_generic_kernel<double><<<grid, 256, 0, stream>>>(vx.data, vo.data, vx.dtype, vc.data, vs.data, vc.dtype, tokens, (int)heads, (int)dim,
+                                                                  table_rows, (int)table_cols, (double)sign, interleaved);
+        } else {
+            rope_generic_kernel<float><<<grid, 256, 0, stream>>>(vx.data, vo.data, vx.dtype, vc.data, vs.data, vc.dtype, tokens, (int)heads, (int)dim,
+                                                                 table_rows, (int)table_cols, sign, interleaved);
+        }
+    }
+    B200_LAUNCH_CHECK("diopiRotaryEmbedding");
+    return diopiSuccess;
+}

@@ -1,0 +1,532 @@
+// Row-wise memory-bound ops: RMSNorm, LayerNorm, softmax, mean / sum.
+//
+// Layout: the reduced extent is the dense innermost run of the tensor ("row"). One CTA owns one row; every
+// thread keeps its share of the row in registers as 128-bit vectors (up to kMaxVpt per thread), so a row is
+// read from HBM exactly once and written exactly once: algorithmic traffic = 2 * row bytes (+ parameters,
+// which stay in L2). Reductions are warp shuffles plus one shared-memory hop. Rows longer than
+// 1024 threads * kMaxVpt vectors take the strided fallback at the end of this file.
+#include "copy.h"
+#include "device_utils.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kMaxVpt = 8;
+
+struct RowCfg {
+    int threads;
+    int vpt;
+};
+
+// Picks the CTA width so that each thread owns about four vectors (enough bytes in flight per SM with many
+// resident CTAs) and never more than kMaxVpt.
+bool pick_row_cfg(int64_t nvec, RowCfg* cfg) {
+    int64_t threads = (nvec + 3) / 4;
+    threads = ((threads + 31) / 32) * 32;
+    if (threads < 32) threads = 32;
+    if (threads > 1024) threads = 1024;
+    const int64_t vpt = (nvec + threads - 1) / threads;
+    if (vpt > kMaxVpt) return false;
+    cfg->threads = static_cast<int>(threads);
+    cfg->vpt = static_cast<int>(vpt <= 1 ? 1 : (vpt <= 2 ? 2 : (vpt <= 4 ? 4 : 8)));
+    return true;
+}
+
+template <typename T, int VPT>
+__device__ __forceinline__ void load_row(const T* row, int64_t nvec, Vec16<T> (&x)[VPT]) {
+    constexpr int V = Vec16<T>::N;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int64_t iv = static_cast<int64_t>(i) * blockDim.x + threadIdx.x;
+        if (iv < nvec) x[i] = ld16_stream(row + iv * V);
+    }
+}
+
+// ---- RMSNorm ---------------------------------------------------------------------------------------------
+template <typename T, int VPT>
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(const T* __restrict__ in, T* __restrict__ out, const T* __restrict__ weight,
+                                                       const T* __restrict__ bias, void* inv_rms, diopiDtype_t inv_dt, int64_t cols, float eps) {
+    constexpr int V = Vec16<T>::N;
+    __shared__ float red[32];
+    const int64_t nvec = cols / V;
+    const int64_t r = blockIdx.x;
+    const T* row = in + r * cols;
+    Vec16<T> x[VPT];
+    load_row<T, VPT>(row, nvec, x);
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        if (static_cast<int64_t>(i) * blockDim.x + threadIdx.x < nvec) {
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                const float f = to_f32(x[i].v[e]);
+                ss += f * f;
+            }
+        }
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / static_cast<float>(cols) + eps);
+    if (inv_rms != nullptr && threadIdx.x == 0) store_from<float>(inv_rms, inv_dt, r, inv);
+    T* orow = out + r * cols;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int64_t iv = static_cast<int64_t>(i) * blockDim.x + threadIdx.x;
+        if (iv < nvec) {
+            Vec16<T> y;
+            if (weight != nullptr) {
+                const Vec16<T> w = ld16(weight + iv * V);
+#pragma unroll
+                for (int e = 0; e < V; ++e) y.v[e] = from_f32<T>(to_f32(x[i].v[e]) * inv * to_f32(w.v[e]));
+            } else {
+#pragma unroll
+                for (int e = 0; e < V; ++e) y.v[e] = from_f32<T>(to_f32(x[i].v[e]) * inv);
+            }
+            if (bias != nullptr) {
+                const Vec16<T> b = ld16(bias + iv * V);
+#pragma unroll
+                for (int e = 0; e < V; ++e) y.v[e] = from_f32<T>(to_f32(y.v[e]) + to_f32(b.v[e]));
+            }
+            st16_stream(orow + iv * V, y);
+        }
+    }
+}
+
+// ---- LayerNorm ---------------------------------------------------------------------------------------------
+template <typename T, int VPT>
+__global__ void __launch_bounds__(1024) layernorm_kernel(const T* __restrict__ in, T* __restrict__ out, const T* __restrict__ weight,
+                                                         const T* __restrict__ bias, void* save_mean, void* save_invstd, diopiDtype_t stat_dt,
+                                                         int64_t cols, float eps) {
+    constexpr int V = Vec16<T>::N;
+    __shared__ float red[32];
+    const int64_t nvec = cols / V;
+    const int64_t r = blockIdx.x;
+    Vec16<T> x[VPT];
+    load_row<T, VPT>(in + r * cols, nvec, x);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        if (static_cast<int64_t>(i) * blockDim.x + threadIdx.x < nvec) {
+#pragma unroll
+            for (int e = 0; e < V; ++e) s += to_f32(x[i].v[e]);
+        }
+    }
+    const float mean = block_sum(s, red) / static_cast<float>(cols);
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        if (static_cast<int64_t>(i) * blockDim.x + threadIdx.x < nvec) {
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                const float d = to_f32(x[i].v[e]) - mean;
+                q += d * d;
+            }
+        }
+    }
+    const float var = block_sum(q, red) / static_cast<float>(cols);
+    const float rstd = rsqrtf(var + eps);
+    if (threadIdx.x == 0) {
+        if (save_mean != nullptr) store_from<float>(save_mean, stat_dt, r, mean);
+        if (save_invstd != nullptr) store_from<float>(save_invstd, stat_dt, r, rstd);
+    }
+    T* orow = out + r * cols;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int64_t iv = static_cast<int64_t>(i) * blockDim.x + threadIdx.x;
+        if (iv < nvec) {
+            Vec16<T> y;
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                float f = (to_f32(x[i].v[e]) - mean) * rstd;
+                y.v[e] = from_f32<T>(f);
+            }
+            if (weight != nullptr) {
+                const Vec16<T> w = ld16(weight + iv * V);
+                if (bias != nullptr) {
+                    const Vec16<T> b = ld16(bias + iv * V);
+#pragma unroll
+                    for (int e = 0; e < V; ++e) y.v[e] = from_f32<T>((to_f32(x[i].v[e]) - mean) * rstd * to_f32(w.v[e]) + to_f32(b.v[e]));
+                } else {
+#pragma unroll
+                    for (int e = 0; e < V; ++e) y.v[e] = from_f32<T>((to_f32(x[i].v[e]) - mean) * rstd * to_f32(w.v[e]));
+                }
+            } else if (bias != nullptr) {
+                const Vec16<T> b = ld16(bias + iv * V);
+#pragma unroll
+                for (int e = 0; e < V; ++e) y.v[e] = from_f32<T>((to_f32(x[i].v[e]) - mean) * rstd + to_f32(b.v[e]));
+            }
+            st16_stream(orow + iv * V, y);
+        }
+    }
+}
+
+// ---- softmax over the innermost run ------------------------------------------------------------------------------
+template <typename T, int VPT>
+__global__ void __launch_bounds__(1024) softmax_row_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t cols) {
+    constexpr int V = Vec16<T>::N;
+    __shared__ float red[32];
+    const int64_t nvec = cols / V;
+    const int64_t r = blockIdx.x;
+    Vec16<T> x[VPT];
+    load_row<T, VPT>(in + r * cols, nvec, x);
+    float f[VPT][V];
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const bool live = static_cast<int64_t>(i) * blockDim.x + threadIdx.x < nvec;
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            f[i][e] = live ? to_f32(x[i].v[e]) : -INFINITY;
+            m = fmaxf(m, f[i][e]);
+        }
+    }
+    m = block_max(m, red);
+    // a row of all -inf has no finite maximum: torch yields NaN there, and so does exp(-inf - -inf)
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            f[i][e] = expf(f[i][e] - m);
+            s += (static_cast<int64_t>(i) * blockDim.x + threadIdx.x < nvec) ? f[i][e] : 0.f;
+        }
+    }
+    s = block_sum(s, red);
+    const float inv = 1.f / s;
+    T* orow = out + r * cols;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int64_t iv = static_cast<int64_t>(i) * blockDim.x + threadIdx.x;
+        if (iv < nvec) {
+            Vec16<T> y;
+#pragma unroll
+            for (int e = 0; e < V; ++e) y.v[e] = from_f32<T>(f[i][e] * inv);
+            st16_stream(orow + iv * V, y);
+        }
+    }
+}
+
+// ---- row sum / mean --------------------------------------------------------------------------------------------------
+template <typename T, int VPT>
+__global__ void __launch_bounds__(1024) rowsum_kernel(const T* __restrict__ in, void* out, diopiDtype_t out_dt, int64_t cols, float scale) {
+    constexpr int V = Vec16<T>::N;
+    __shared__ float red[32];
+    const int64_t nvec = cols / V;
+    const int64_t r = blockIdx.x;
+    Vec16<T> x[VPT];
+    load_row<T, VPT>(in + r * cols, nvec, x);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        if (static_cast<int64_t>(i) * blockDim.x + threadIdx.x < nvec) {
+#pragma unroll
+            for (int e = 0; e < V; ++e) s += to_f32(x[i].v[e]);
+        }
+    }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) store_from<float>(out, out_dt, r, s * scale);
+}
+
+// ---- strided fallbacks (any dim, any dtype; one warp per output slice) --------------------------------------------------
+// The tensor is viewed as [outer, n, inner] with the reduced / normalised extent n in the middle.
+template <typename C>
+__global__ void softmax_strided_kernel(const void* in, diopiDtype_t in_dt, void* out, diopiDtype_t out_dt, int64_t outer, int64_t n,
+                                       int64_t inner) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+    for (int64_t s = warp; s < outer * inner; s += nwarps) {
+        const int64_t o = s / inner, k = s - o * inner;
+        const int64_t base = o * n * inner + k;
+        C m = -INFINITY;
+        for (int64_t j = lane; j < n; j += 32) {
+            const C v = load_as<C>(in, in_dt, base + j * inner);
+            m = v > m ? v : m;
+        }
+        for (int off = 16; off > 0; off >>= 1) {
+            const C t = __shfl_xor_sync(0xffffffffu, m, off);
+            m = t > m ? t : m;
+        }
+        C sum = 0;
+        for (int64_t j = lane; j < n; j += 32) sum += exp(load_as<C>(in, in_dt, base + j * inner) - m);
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        for (int64_t j = lane; j < n; j += 32) {
+            const C v = exp(load_as<C>(in, in_dt, base + j * inner) - m) / sum;
+            store_from<C>(out, out_dt, base + j * inner, v);
+        }
+    }
+}
+
+struct ReduceIter {
+    int nkeep, nred;
+    int64_t keep_shape[kMaxDims], keep_stride[kMaxDims];
+    int64_t red_shape[kMaxDims], red_stride[kMaxDims];
+    int64_t n_out, n_red;
+};
+
+template <typename C>
+__global__ void reduce_sum_strided_kernel(const void* in, diopiDtype_t in_dt, void* out, diopiDtype_t out_dt, const ReduceIter it, C scale) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+    for (int64_t o = warp; o < it.n_out; o += nwarps) {
+        int64_t base = 0, rem = o;
+        for (int d = it.nkeep - 1; d >= 0; --d) {
+            const int64_t q = rem / it.keep_shape[d];
+            base += (rem - q * it.keep_shape[d]) * it.keep_stride[d];
+            rem = q;
+        }
+        C acc = 0;
+        for (int64_t j = lane; j < it.n_red; j += 32) {
+            int64_t off = base, r = j;
+            for (int d = it.nred - 1; d >= 0; --d) {
+                const int64_t q = r / it.red_shape[d];
+                off += (r - q * it.red_shape[d]) * it.red_stride[d];
+                r = q;
+            }
+            acc += load_as<C>(in, in_dt, off);
+        }
+        for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        if (lane == 0) store_from<C>(out, out_dt, o, acc * scale);
+    }
+}
+
+#define B200_DISPATCH_VPT(VPT_VALUE, ...)              \
+    switch (VPT_VALUE) {                               \
+        case 1: { constexpr int VPT = 1; __VA_ARGS__; break; } \
+        case 2: { constexpr int VPT = 2; __VA_ARGS__; break; } \
+        case 4: { constexpr int VPT = 4; __VA_ARGS__; break; } \
+        default: { constexpr int VPT = 8; __VA_ARGS__; break; } \
+    }
+
+// Can `v` use the register-resident row kernels for rows of `cols` elements?
+bool row_fast_ok(const TensorView& v, int64_t cols, RowCfg* cfg) {
+    if (!(v.dtype == diopi_dtype_bfloat16 || v.dtype == diopi_dtype_float16 || v.dtype == diopi_dtype_float32)) return false;
+    const int V = 16 / static_cast<int>(v.itemsize);
+    if (cols % V != 0 || !v.aligned(16)) return false;
+    return pick_row_cfg(cols / V, cfg);
+}
+
+int64_t shape_product(diopiSize_t s) {
+    int64_t p = 1;
+    for (int64_t i = 0; i < s.len; ++i) p *= s.data[i];
+    return p;
+}
+
+bool param_ok(const TensorView* p, const TensorView& x, int64_t cols) {
+    return p == nullptr || (p->dtype == x.dtype && p->numel == cols && p->is_contiguous() && p->aligned(16) && p->device == diopi_device);
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+diopiError_t diopiRMSNorm(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiTensorHandle_t inv_rms, diopiConstTensorHandle_t input,
+                          diopiSize_t normalized_shape, diopiConstTensorHandle_t weight, diopiConstTensorHandle_t bias, double eps) {
+    B200_VIEW(vo, out);
+    B200_VIEW(vx_raw, input);
+    TensorView vw, vb, vinv;
+    if (weight && !make_view(weight, &vw, "weight")) return diopiErrorOccurred;
+    if (bias && !make_view(bias, &vb, "bias")) return diopiErrorOccurred;
+    if (inv_rms && !make_view(inv_rms, &vinv, "inv_rms")) return diopiErrorOccurred;
+    B200_CHECK(normalized_shape.len >= 1 && normalized_shape.len <= vx_raw.ndim, "diopiRMSNorm: bad normalized_shape rank");
+    for (int64_t i = 0; i < normalized_shape.len; ++i) {
+        B200_CHECK(normalized_shape.data[i] == vx_raw.shape[vx_raw.ndim - normalized_shape.len + i], "diopiRMSNorm: normalized_shape mismatches the input");
+    }
+    const int64_t cols = shape_product(normalized_shape);
+    B200_CHECK(vo.numel == vx_raw.numel && vo.dtype == vx_raw.dtype, "diopiRMSNorm: output must match the input shape and dtype");
+    B200_CHECK(vo.is_contiguous(), "diopiRMSNorm: output must be contiguous");
+    if (vo.numel == 0) return diopiSuccess;
+    const int64_t rows = vx_raw.numel / cols;
+    if (inv_rms) B200_CHECK(vinv.numel == rows && vinv.is_contiguous(), "diopiRMSNorm: inv_rms must be dense with one entry per row");
+    TensorView vx;
+    if (make_contiguous(ctx, vx_raw, &vx) != diopiSuccess) return diopiErrorOccurred;
+    RowCfg cfg;
+    B200_CHECK(row_fast_ok(vx, cols, &cfg) && vo.aligned(16),
+               "diopiRMSNorm: rows of %lld %s elements are outside the supported range (16-byte multiple, at most %d vectors)", (long long)cols,
+               dtype_name(vx.dtype), 1024 * kMaxVpt);
+    B200_CHECK(param_ok(weight ? &vw : nullptr, vx, cols) && param_ok(bias ? &vb : nullptr, vx, cols),
+               "diopiRMSNorm: weight/bias must be dense device tensors of the input dtype with normalized_shape elements");
+    cudaStream_t stream = stream_of(ctx);
+    const unsigned grid = static_cast<unsigned>(rows);
+    B200_CHECK(rows <= 0x7fffffffLL, "diopiRMSNorm: too many rows");
+#define LAUNCH_RMS(T)                                                                                                                   \
+    B200_DISPATCH_VPT(cfg.vpt, (rmsnorm_kernel<T, VPT><<<grid, cfg.threads, 0, stream>>>(                                                 \
+                                   static_cast<const T*>(vx.data), static_cast<T*>(vo.data), weight ? static_cast<const T*>(vw.data) : nullptr, \
+                                   bias ? static_cast<const T*>(vb.data) : nullptr, inv_rms ? vinv.data : nullptr,                        \
+                                   inv_rms ? vinv.dtype : diopi_dtype_float32, cols, static_cast<float>(eps))))
+    if (vx.dtype == diopi_dtype_bfloat16) { LAUNCH_RMS(bf16); }
+    else if (vx.dtype == diopi_dtype_float16) { LAUNCH_RMS(fp16); }
+    else { LAUNCH_RMS(float); }
+#undef LAUNCH_RMS
+    B200_LAUNCH_CHECK("diopiRMSNorm");
+    return diopiSuccess;
+}
+
+diopiError_t diopiLayerNorm(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiTensorHandle_t save_mean, diopiTensorHandle_t save_invstd,
+                            diopiConstTensorHandle_t input, diopiConstTensorHandle_t weight, diopiConstTensorHandle_t bias,
+                            diopiSize_t normalized_shape, double eps) {
+    B200_VIEW(vo, out);
+    B200_VIEW(vx_raw, input);
+    TensorView vw, vb, vm, vs;
+    if (weight && !make_view(weight, &vw, "weight")) return diopiErrorOccurred;
+    if (bias && !make_view(bias, &vb, "bias")) return diopiErrorOccurred;
+    if (save_mean && !make_view(save_mean, &vm, "save_mean")) return diopiErrorOccurred;
+    if (save_invstd && !make_view(save_invstd, &vs, "save_invstd")) return diopiErrorOccurred;
+    B200_CHECK(normalized_shape.len >= 1 && normalized_shape.len <= vx_raw.ndim, "diopiLayerNorm: bad normalized_shape rank");
+    for (int64_t i = 0; i < normalized_shape.len; ++i) {
+        B200_CHECK(normalized_shape.data[i] == vx_raw.shape[vx_raw.ndim - normalized_shape.len + i], "diopiLayerNorm: normalized_shape mismatches the input");
+    }
+    const int64_t cols = shape_product(normalized_shape);
+    B200_CHECK(vo.numel == vx_raw.numel && vo.dtype == vx_raw.dtype, "diopiLayerNorm: output must match the input shape and dtype");
+    B200_CHECK(vo.is_contiguous(), "diopiLayerNorm: output must be contiguous");
+    if (vo.numel == 0) return diopiSuccess;
+    const int64_t rows = vx_raw.numel / cols;
+    if (save_mean) B200_CHECK(vm.numel == rows && vm.is_contiguous(), "diopiLayerNorm: save_mean must be dense with one entry per row");
+    if (save_invstd) B200_CHECK(vs.numel == rows && vs.is_contiguous(), "diopiLayerNorm: save_invstd must be dense with one entry per row");
+    if (save_mean && save_invstd) B200_CHECK(vm.dtype == vs.dtype, "diopiLayerNorm: save_mean / save_invstd dtypes differ");
+    TensorView vx;
+    if (make_contiguous(ctx, vx_raw, &vx) != diopiSuccess) return diopiErrorOccurred;
+    RowCfg cfg;
+    B200_CHECK(row_fast_ok(vx, cols, &cfg) && vo.aligned(16),
+               "diopiLayerNorm: rows of %lld %s elements are outside the supported range (16-byte multiple, at most %d vectors)", (long long)cols,
+               dtype_name(vx.dtype), 1024 * kMaxVpt);
+    B200_CHECK(param_ok(weight ? &vw : nullptr, vx, cols) && param_ok(bias ? &vb : nullptr, vx, cols),
+               "diopiLayerNorm: weight/bias must be dense device tensors of the input dtype with normalized_shape elements");
+    cudaStream_t stream = stream_of(ctx);
+    B200_CHECK(rows <= 0x7fffffffLL, "diopiLayerNorm: too many rows");
+    const unsigned grid = static_cast<unsigned>(rows);
+    const diopiDtype_t stat_dt = save_mean ? vm.dtype : (save_invstd ? vs.dtype : diopi_dtype_float32);
+#define LAUNCH_LN(T)                                                                                                                    \
+    B200_DISPATCH_VPT(cfg.vpt, (layernorm_kernel<T, VPT><<<grid, cfg.threads, 0, stream>>>(                                               \
+                                   static_cast<const T*>(vx.data), static_cast<T*>(vo.data), weight ? static_cast<const T*>(vw.data) : nullptr, \
+                                   bias ? static_cast<const T*>(vb.data) : nullptr, save_mean ? vm.data : nullptr,                        \
+                                   save_invstd ? vs.data : nullptr, stat_dt, cols, static_cast<float>(eps))))
+    if (vx.dtype == diopi_dtype_bfloat16) { LAUNCH_LN(bf16); }
+    else if (vx.dtype == diopi_dtype_float16) { LAUNCH_LN(fp16); }
+    else { LAUNCH_LN(float); }
+#undef LAUNCH_LN
+    B200_LAUNCH_CHECK("diopiLayerNorm");
+    return diopiSuccess;
+}
+
+diopiError_t diopiSoftmax(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input, int64_t dim) {
+    B200_VIEW(vo, out);
+    B200_VIEW(vx_raw, input);
+    B200_CHECK(vo.numel == vx_raw.numel, "diopiSoftmax: output must match the input shape");
+    B200_CHECK(vo.is_contiguous(), "diopiSoftmax: output must be contiguous");
+    B200_CHECK(is_floating(vx_raw.dtype) && is_floating(vo.dtype), "diopiSoftmax: floating dtypes only");
+    if (vo.numel == 0) return diopiSuccess;
+    const int nd = vx_raw.ndim == 0 ? 1 : vx_raw.ndim;
+    if (dim < 0) dim += nd;
+    B200_CHECK(dim >= 0 && dim < nd, "diopiSoftmax: dim out of range");
+    TensorView vx;
+    if (make_contiguous(ctx, vx_raw, &vx) != diopiSuccess) return diopiErrorOccurred;
+    int64_t outer = 1, inner = 1;
+    const int64_t n = vx.ndim == 0 ? 1 : vx.shape[dim];
+    for (int d = 0; d < dim; ++d) outer *= vx.shape[d];
+    for (int d = static_cast<int>(dim) + 1; d < vx.ndim; ++d) inner *= vx.shape[d];
+    cudaStream_t stream = stream_of(ctx);
+    RowCfg cfg;
+    if (inner == 1 && vo.dtype == vx.dtype && row_fast_ok(vx, n, &cfg) && vo.aligned(16) && outer <= 0x7fffffffLL) {
+        const unsigned grid = static_cast<unsigned>(outer);
+#define LAUNCH_SM(T) \
+    B200_DISPATCH_VPT(cfg.vpt, (softmax_row_kernel<T, VPT><<<grid, cfg.threads, 0, stream>>>(static_cast<const T*>(vx.data), static_cast<T*>(vo.data), n)))
+        if (vx.dtype == diopi_dtype_bfloat16) { LAUNCH_SM(bf16); }
+        else if (vx.dtype == diopi_dtype_float16) { LAUNCH_SM(fp16); }
+        else { LAUNCH_SM(float); }
+#undef LAUNCH_SM
+    } else {
+        const int64_t slices = outer * inner;
+        int64_t blocks = (slices * 32 + 255) / 256;
+        const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+        if (blocks > cap) blocks = cap;
+        if (vo.dtype == diopi_dtype_float64) {
+            softmax_strided_kernel<double><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(vx.data, vx.dtype, vo.data, vo.dtype, outer, n, inner);
+        } else {
+            softmax_strided_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(vx.data, vx.dtype, vo.data, vo.dtype, outer, n, inner);
+        }
+    }
+    B200_LAUNCH_CHECK("diopiSoftmax");
+    return diopiSuccess;
+}
+
+static diopiError_t reduce_sum_impl(diopiContextHandle_t ctx, const char* name, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                    diopiSize_t dim, bool mean) {
+    B200_VIEW(vo, out);
+    B200_VIEW(vx, input);
+    B200_CHECK(vo.is_contiguous(), "%s: output must be contiguous", name);
+    B200_CHECK(vx.device == diopi_device && vo.device == diopi_device, "%s: operands must be device tensors", name);
+    bool reduced[kMaxDims] = {false};
+    if (dim.len == 0 || dim.data == nullptr) {
+        for (int d = 0; d < vx.ndim; ++d) reduced[d] = true;
+    } else {
+        for (int64_t i = 0; i < dim.len; ++i) {
+            int64_t d = dim.data[i];
+            if (d < 0) d += vx.ndim;
+            B200_CHECK(d >= 0 && d < (vx.ndim == 0 ? 1 : vx.ndim), "%s: dim out of range", name);
+            if (vx.ndim > 0) reduced[d] = true;
+        }
+    }
+    ReduceIter it;
+    it.nkeep = it.nred = 0;
+    it.n_out = it.n_red = 1;
+    for (int d = 0; d < vx.ndim; ++d) {
+        if (reduced[d]) {
+            it.red_shape[it.nred] = vx.shape[d];
+            it.red_stride[it.nred++] = vx.stride[d];
+            it.n_red *= vx.shape[d];
+        } else {
+            it.keep_shape[it.nkeep] = vx.shape[d];
+            it.keep_stride[it.nkeep++] = vx.stride[d];
+            it.n_out *= vx.shape[d];
+        }
+    }
+    B200_CHECK(vo.numel == it.n_out, "%s: output has %lld elements, expected %lld", name, (long long)vo.numel, (long long)it.n_out);
+    if (vo.numel == 0) return diopiSuccess;
+    cudaStream_t stream = stream_of(ctx);
+    if (it.n_red == 0) return diopiZeroInp(ctx, out);
+    const double scale = mean ? 1.0 / static_cast<double>(it.n_red) : 1.0;
+
+    // fast path: the reduced dims are the dense tail of a dense tensor
+    bool tail = vx.is_contiguous();
+    for (int d = 0, seen = 0; d < vx.ndim && tail; ++d) {
+        if (reduced[d]) seen = 1;
+        else if (seen && vx.shape[d] != 1) tail = false;
+    }
+    RowCfg cfg;
+    if (tail && row_fast_ok(vx, it.n_red, &cfg) && it.n_out <= 0x7fffffffLL) {
+        const unsigned grid = static_cast<unsigned>(it.n_out);
+#define LAUNCH_RS(T) \
+    B200_DISPATCH_VPT(cfg.vpt, (rowsum_kernel<T, VPT><<<grid, cfg.threads, 0, stream>>>(static_cast<const T*>(vx.data), vo.data, vo.dtype, it.n_red, static_cast<float>(scale))))
+        if (vx.dtype == diopi_dtype_bfloat16) { LAUNCH_RS(bf16); }
+        else if (vx.dtype == diopi_dtype_float16) { LAUNCH_RS(fp16); }
+        else { LAUNCH_RS(float); }
+#undef LAUNCH_RS
+    } else {
+        int64_t blocks = (it.n_out * 32 + 255) / 256;
+        const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+        if (blocks > cap) blocks = cap;
+        if (vo.dtype == diopi_dtype_float64) {
+            reduce_sum_strided_kernel<double><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(vx.data, vx.dtype, vo.data, vo.dtype, it, scale);
+        } else if (is_floating(vo.dtype)) {
+            reduce_sum_strided_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(vx.data, vx.dtype, vo.data, vo.dtype, it, static_cast<float>(scale));
+        } else {
+            B200_CHECK(!mean, "%s: mean needs a floating output", name);
+            reduce_sum_strided_kernel<int64_t><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(vx.data, vx.dtype, vo.data, vo.dtype, it, (int64_t)1);
+        }
+    }
+    B200_LAUNCH_CHECK(name);
+    return diopiSuccess;
+}
+
+diopiError_t diopiMean(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input, diopiSize_t dim) {
+    return reduce_sum_impl(ctx, "diopiMean", out, input, dim, true);
+}
+diopiError_t diopiSum(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input, diopiSize_t dim) {
+    return reduce_sum_impl(ctx, "diopiSum", out, input, dim, false);
+}
+
+}  // extern "C"

@@ -1,0 +1,469 @@
+"""Python mirror of DIPU's vendor interface (namespace dipu::devapis) over the vendor runtime's C-ABI.
+
+Function names, argument meaning and error behaviour follow the reference declarations in
+dipu/torch_dipu/csrc_dipu/runtime/device/deviceapis.h:23-124 and diclapis.h:20-82: void functions raise on any driver
+error (the reference throws c10::Error through TORCH_CHECK), mallocDevice returns OpStatus.ERR_NOMEM instead of
+raising when throwExcepion is False, getEventStatus maps "not ready" to PENDING. Streams, events and communicators are
+opaque integer handles.
+"""
+import ctypes
+import enum
+
+from . import _native
+
+_v = _native.vendor
+
+
+class OpStatus(enum.IntEnum):
+    SUCCESS = 0
+    ERR_UNKNOWN = 1
+    ERR_NOMEM = 2
+
+
+class EventStatus(enum.IntEnum):
+    PENDING = 0
+    RUNNING = 1
+    DEFERRED = 2
+    READY = 3
+
+
+class diclResult_t(enum.IntEnum):
+    DICL_SUCCESS = 0
+    DICL_ERR_UNDEF = 0x1000
+
+
+class ReduceOp(enum.IntEnum):  # same order as c10d::ReduceOp
+    SUM = 0
+    AVG = 1
+    PRODUCT = 2
+    MIN = 3
+    MAX = 4
+
+
+class VendorError(RuntimeError):
+    pass
+
+
+class DeviceProperties(ctypes.Structure):
+    _fields_ = [("name", ctypes.c_char * 256), ("totalGlobalMem", ctypes.c_size_t), ("major", ctypes.c_int32), ("minor", ctypes.c_int32),
+                ("multiProcessorCount", ctypes.c_int32)]
+
+
+class AllocStats(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int64) for n in ("allocated_bytes", "allocated_bytes_peak", "reserved_bytes", "reserved_bytes_peak",
+                                              "active_blocks", "segments", "num_alloc_retries", "num_ooms", "num_device_mallocs",
+                                              "num_cache_hits")]
+
+    def as_dict(self):
+        return {n: getattr(self, n) for n, _ in self._fields_}
+
+
+class UniqueId(ctypes.Structure):
+    _fields_ = [("internal", ctypes.c_char * 128)]
+
+
+_v.b200_last_error.restype = ctypes.c_char_p
+_vp, _sz, _i = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+_SIGS = {
+    "b200_initialize_vendor": [], "b200_finalize_vendor": [], "b200_current_device": [ctypes.POINTER(_i)],
+    "b200_get_device_properties": [_i, ctypes.POINTER(DeviceProperties)],
+    "b200_get_device_status": [_i, ctypes.POINTER(_sz), ctypes.POINTER(_sz)],
+    "b200_set_device": [_i], "b200_reset_device": [_i], "b200_sync_device": [], "b200_check_last_error": [],
+    "b200_get_device_count": [ctypes.POINTER(_i)], "b200_get_driver_version": [ctypes.POINTER(_i)],
+    "b200_get_runtime_version": [ctypes.POINTER(_i)],
+    "b200_create_stream": [ctypes.POINTER(_vp), _i], "b200_destroy_stream": [_vp], "b200_destroy_stream_on": [_vp, _i],
+    "b200_release_stream": [], "b200_sync_stream": [_vp], "b200_stream_wait_event": [_vp, _vp],
+    "b200_create_event": [ctypes.POINTER(_vp)], "b200_destroy_event": [_vp], "b200_wait_event": [_vp], "b200_record_event": [_vp, _vp],
+    "b200_event_elapsed_time": [ctypes.POINTER(ctypes.c_float), _vp, _vp], "b200_get_event_status": [_vp, ctypes.POINTER(_i)],
+    "b200_malloc_host": [ctypes.POINTER(_vp), _sz], "b200_free_host": [_vp], "b200_malloc_device": [ctypes.POINTER(_vp), _sz],
+    "b200_free_device": [_vp], "b200_memset_async": [_vp, _vp, _i, _sz],
+    "b200_memcpy_d2d": [_sz, _i, _vp, _i, _vp], "b200_memcpy_h2d": [_sz, _vp, _vp], "b200_memcpy_d2h": [_sz, _vp, _vp],
+    "b200_memcpy_d2d_async": [_vp, _sz, _i, _vp, _i, _vp], "b200_memcpy_h2d_async": [_vp, _sz, _vp, _vp],
+    "b200_memcpy_d2h_async": [_vp, _sz, _vp, _vp],
+    "b200_cache_alloc": [ctypes.POINTER(_vp), _sz, _i, _vp], "b200_cache_free": [_vp], "b200_cache_record_stream": [_vp, _vp],
+    "b200_cache_empty": [], "b200_cache_stats": [_i, ctypes.POINTER(AllocStats)], "b200_cache_reset_peak": [_i],
+    "b200_cache_configure": [ctypes.c_char_p], "b200_cache_use_fake_backend": [_sz, _i], "b200_cache_fake_complete_events": [],
+    "b200_host_cache_alloc": [ctypes.POINTER(_vp), _sz], "b200_host_cache_free": [_vp], "b200_host_cache_record_stream": [_vp, _vp],
+    "b200_host_cache_empty": [],
+    "b200_default_stream": [_i, ctypes.POINTER(_vp)], "b200_stream_from_pool": [_i, ctypes.POINTER(_vp)],
+    "b200_event_from_pool": [ctypes.POINTER(_vp)], "b200_event_to_pool": [_vp], "b200_release_all_pools": [],
+    "b200_dicl_get_unique_id": [ctypes.POINTER(UniqueId)],
+    "b200_dicl_comm_init_rank": [ctypes.POINTER(_vp), _i, ctypes.POINTER(UniqueId), _i, _i], "b200_dicl_comm_destroy": [_vp],
+    "b200_dicl_get_comm_async_error": [_vp],
+    "b200_dicl_all_reduce": [_vp, _vp, _sz, _i, _i, _vp, _vp], "b200_dicl_broadcast": [_vp, _vp, _sz, _i, _i, _vp, _vp],
+    "b200_dicl_all_gather": [_vp, _vp, _sz, _i, _vp, _vp], "b200_dicl_reduce": [_vp, _vp, _sz, _i, _i, _i, _vp, _vp],
+    "b200_dicl_reduce_scatter": [_vp, _vp, _sz, _i, _i, _vp, _vp], "b200_dicl_send": [_vp, _sz, _i, _i, _vp, _vp],
+    "b200_dicl_recv": [_vp, _sz, _i, _i, _vp, _vp],
+    "b200_dicl_all_to_all_equal_split": [_vp, _vp, _sz, _i, _vp, _vp],
+    "b200_dicl_all_to_all_unequal_split": [_vp, ctypes.POINTER(_sz), ctypes.POINTER(_sz), _vp, ctypes.POINTER(_sz), ctypes.POINTER(_sz), _i, _vp,
+                                           _vp],
+    "b200_dicl_get_comm_name": [ctypes.c_char_p, _sz, _vp],
+}
+for _n, _a in _SIGS.items():
+    getattr(_v, _n).argtypes = _a
+    getattr(_v, _n).restype = ctypes.c_int
+for _n in ("b200_stream_not_null", "b200_is_stream_empty", "b200_is_pinned_ptr", "b200_dicl_unique_id_bytes"):
+    getattr(_v, _n).restype = ctypes.c_int
+_v.b200_stream_not_null.argtypes = [_vp]
+_v.b200_is_stream_empty.argtypes = [_vp]
+_v.b200_is_pinned_ptr.argtypes = [_vp]
+
+C_SYMBOLS = sorted(list(_SIGS) + ["b200_stream_not_null", "b200_is_stream_empty", "b200_is_pinned_ptr", "b200_dicl_unique_id_bytes",
+                                  "b200_last_error"])
+
+
+def last_error():
+    return _v.b200_last_error().decode()
+
+
+def _check(rc, what):
+    if rc != 0:
+        raise VendorError("%s failed (status %d): %s" % (what, rc, last_error()))
+
+
+# ---- device --------------------------------------------------------------------------------------------------
+def initializeVendor():
+    _check(_v.b200_initialize_vendor(), "initializeVendor")
+
+
+def finalizeVendor():
+    _check(_v.b200_finalize_vendor(), "finalizeVendor")
+
+
+def current_device():
+    d = _i()
+    _check(_v.b200_current_device(ctypes.byref(d)), "current_device")
+    return d.value
+
+
+def getDeviceProperties(device_index):
+    p = DeviceProperties()
+    _check(_v.b200_get_device_properties(device_index, ctypes.byref(p)), "getDeviceProperties")
+    return p
+
+
+def getDeviceStatus(device_index):
+    f, t = _sz(), _sz()
+    _check(_v.b200_get_device_status(device_index, ctypes.byref(f), ctypes.byref(t)), "getDeviceStatus")
+    return f.value, t.value
+
+
+def setDevice(dev):
+    _check(_v.b200_set_device(dev), "setDevice")
+
+
+def resetDevice(dev=0):
+    _check(_v.b200_reset_device(dev), "resetDevice")
+
+
+def syncDevice():
+    _check(_v.b200_sync_device(), "syncDevice")
+
+
+def checkLastError():
+    _check(_v.b200_check_last_error(), "checkLastError")
+
+
+def getDeviceCount():
+    n = _i()
+    _check(_v.b200_get_device_count(ctypes.byref(n)), "getDeviceCount")
+    return n.value
+
+
+def getDriverVersion():
+    n = _i()
+    _check(_v.b200_get_driver_version(ctypes.byref(n)), "getDriverVersion")
+    return n.value
+
+
+def getRuntimeVersion():
+    n = _i()
+    _check(_v.b200_get_runtime_version(ctypes.byref(n)), "getRuntimeVersion")
+    return n.value
+
+
+# ---- streams / events ---------------------------------------------------------------------------------------------
+def createStream(prior=False):
+    s = _vp()
+    _check(_v.b200_create_stream(ctypes.byref(s), int(prior)), "createStream")
+    return s.value
+
+
+def destroyStream(stream, devId=None):
+    if devId is None:
+        _check(_v.b200_destroy_stream(stream), "destroyStream")
+    else:
+        _check(_v.b200_destroy_stream_on(stream, devId), "destroyStream")
+
+
+def releaseStream():
+    _check(_v.b200_release_stream(), "releaseStream")
+
+
+def syncStream(stream):
+    _check(_v.b200_sync_stream(stream), "syncStream")
+
+
+def streamNotNull(stream):
+    return bool(_v.b200_stream_not_null(stream))
+
+
+def streamWaitEvent(stream, event):
+    _check(_v.b200_stream_wait_event(stream, event), "streamWaitEvent")
+
+
+def isStreamEmpty(stream):
+    return bool(_v.b200_is_stream_empty(stream))
+
+
+def createEvent():
+    e = _vp()
+    _check(_v.b200_create_event(ctypes.byref(e)), "createEvent")
+    return e.value
+
+
+def destroyEvent(event):
+    _check(_v.b200_destroy_event(event), "destroyEvent")
+
+
+def waitEvent(event):
+    _check(_v.b200_wait_event(event), "waitEvent")
+
+
+def recordEvent(event, stream):
+    _check(_v.b200_record_event(event, stream), "recordEvent")
+
+
+def eventElapsedTime(start, end):
+    ms = ctypes.c_float()
+    _check(_v.b200_event_elapsed_time(ctypes.byref(ms), start, end), "eventElapsedTime")
+    return ms.value
+
+
+def getEventStatus(event):
+    st = _i()
+    _check(_v.b200_get_event_status(event, ctypes.byref(st)), "getEventStatus")
+    return EventStatus(st.value)
+
+
+def getDefaultStream(device):
+    s = _vp()
+    _check(_v.b200_default_stream(device, ctypes.byref(s)), "getDefaultStream")
+    return s.value
+
+
+def getStreamFromPool(device):
+    s = _vp()
+    _check(_v.b200_stream_from_pool(device, ctypes.byref(s)), "getStreamFromPool")
+    return s.value
+
+
+def getEventFromPool():
+    e = _vp()
+    _check(_v.b200_event_from_pool(ctypes.byref(e)), "getEventFromPool")
+    return e.value
+
+
+def restoreEventToPool(event):
+    _check(_v.b200_event_to_pool(event), "restoreEventToPool")
+
+
+# ---- memory --------------------------------------------------------------------------------------------------------
+def mallocHost(nbytes):
+    p = _vp()
+    _check(_v.b200_malloc_host(ctypes.byref(p), nbytes), "mallocHost")
+    return p.value
+
+
+def freeHost(p):
+    _check(_v.b200_free_host(p), "freeHost")
+
+
+def mallocDevice(nbytes, throwExcepion=True):
+    """Returns (OpStatus, pointer). With throwExcepion=False an out-of-memory condition is reported, not raised."""
+    p = _vp()
+    rc = _v.b200_malloc_device(ctypes.byref(p), nbytes)
+    if rc == OpStatus.ERR_NOMEM and not throwExcepion:
+        return OpStatus.ERR_NOMEM, None
+    _check(rc, "mallocDevice")
+    return OpStatus.SUCCESS, p.value
+
+
+def freeDevice(p):
+    _check(_v.b200_free_device(p), "freeDevice")
+
+
+def isPinnedPtr(p):
+    return bool(_v.b200_is_pinned_ptr(p))
+
+
+def memSetAsync(stream, ptr, val, size):
+    _check(_v.b200_memset_async(stream, ptr, val, size), "memSetAsync")
+
+
+def memCopyD2D(nbytes, dstDevId, dst, srcDevId, src):
+    _check(_v.b200_memcpy_d2d(nbytes, dstDevId, dst, srcDevId, src), "memCopyD2D")
+
+
+def memCopyH2D(nbytes, dst, src):
+    _check(_v.b200_memcpy_h2d(nbytes, dst, src), "memCopyH2D")
+
+
+def memCopyD2H(nbytes, dst, src):
+    _check(_v.b200_memcpy_d2h(nbytes, dst, src), "memCopyD2H")
+
+
+def memCopyD2DAsync(stream, nbytes, dstDevId, dst, srcDevId, src):
+    _check(_v.b200_memcpy_d2d_async(stream, nbytes, dstDevId, dst, srcDevId, src), "memCopyD2DAsync")
+
+
+def memCopyH2DAsync(stream, nbytes, dst, src):
+    _check(_v.b200_memcpy_h2d_async(stream, nbytes, dst, src), "memCopyH2DAsync")
+
+
+def memCopyD2HAsync(stream, nbytes, dst, src):
+    _check(_v.b200_memcpy_d2h_async(stream, nbytes, dst, src), "memCopyD2HAsync")
+
+
+# ---- caching allocator (what dipu::getAllocator(DIPU) offers) -----------------------------------------------------------
+class CachingAllocator:
+    @staticmethod
+    def allocate(nbytes, device, stream):
+        p = _vp()
+        rc = _v.b200_cache_alloc(ctypes.byref(p), nbytes, device, stream)
+        if rc == OpStatus.ERR_NOMEM:
+            raise MemoryError(last_error())
+        _check(rc, "allocate")
+        return p.value
+
+    @staticmethod
+    def free(p):
+        _check(_v.b200_cache_free(p), "free")
+
+    @staticmethod
+    def recordStream(p, stream):
+        _check(_v.b200_cache_record_stream(p, stream), "recordStream")
+
+    @staticmethod
+    def emptyCache():
+        _check(_v.b200_cache_empty(), "emptyCache")
+
+    @staticmethod
+    def stats(device):
+        s = AllocStats()
+        _check(_v.b200_cache_stats(device, ctypes.byref(s)), "stats")
+        return s.as_dict()
+
+    @staticmethod
+    def resetPeakStats(device):
+        _check(_v.b200_cache_reset_peak(device), "resetPeakStats")
+
+    @staticmethod
+    def configure(conf):
+        _check(_v.b200_cache_configure(conf.encode()), "configure")
+
+    @staticmethod
+    def useFakeBackend(capacity, pending_events=False):
+        _check(_v.b200_cache_use_fake_backend(capacity, int(pending_events)), "useFakeBackend")
+
+    @staticmethod
+    def fakeCompleteEvents():
+        _check(_v.b200_cache_fake_complete_events(), "fakeCompleteEvents")
+
+
+class CachingHostAllocator:
+    @staticmethod
+    def allocate(nbytes):
+        p = _vp()
+        _check(_v.b200_host_cache_alloc(ctypes.byref(p), nbytes), "host allocate")
+        return p.value
+
+    @staticmethod
+    def free(p):
+        _check(_v.b200_host_cache_free(p), "host free")
+
+    @staticmethod
+    def recordStream(p, stream):
+        _check(_v.b200_host_cache_record_stream(p, stream), "host recordStream")
+
+    @staticmethod
+    def emptyCache():
+        _check(_v.b200_host_cache_empty(), "host emptyCache")
+
+
+# ---- DICL ------------------------------------------------------------------------------------------------------------------
+DICL_UNIQUE_ID_BYTES_SIZE = _v.b200_dicl_unique_id_bytes()
+
+
+def _dicl(rc, what):
+    if rc != 0:
+        raise VendorError("call dicl error, expr = %s, status %d: %s" % (what, rc, last_error()))
+    return diclResult_t.DICL_SUCCESS
+
+
+def diclGetUniqueId():
+    uid = UniqueId()
+    _dicl(_v.b200_dicl_get_unique_id(ctypes.byref(uid)), "diclGetUniqueId")
+    return bytes(ctypes.string_at(ctypes.byref(uid), 128))
+
+
+def diclCommInitRank(nranks, uniqueId, rank, localDeviceId=-1):
+    uid = UniqueId()
+    ctypes.memmove(ctypes.byref(uid), uniqueId, 128)
+    comm = _vp()
+    _dicl(_v.b200_dicl_comm_init_rank(ctypes.byref(comm), nranks, ctypes.byref(uid), rank, localDeviceId), "diclCommInitRank")
+    return comm.value
+
+
+def diclCommDestroy(comm):
+    return _dicl(_v.b200_dicl_comm_destroy(comm), "diclCommDestroy")
+
+
+def diclGetCommAsyncError(comm):
+    rc = _v.b200_dicl_get_comm_async_error(comm)
+    return diclResult_t.DICL_SUCCESS if rc == 0 else diclResult_t.DICL_ERR_UNDEF
+
+
+def diclAllReduce(sendBuf, recvBuf, count, datatype, reduceOp, comm, stream):
+    return _dicl(_v.b200_dicl_all_reduce(sendBuf, recvBuf, count, datatype, int(reduceOp), comm, stream), "diclAllReduce")
+
+
+def diclBroadcast(sendBuf, recvBuf, count, datatype, root, comm, stream):
+    return _dicl(_v.b200_dicl_broadcast(sendBuf, recvBuf, count, datatype, root, comm, stream), "diclBroadcast")
+
+
+def diclAllGather(sendBuf, recvBuf, sendCount, datatype, comm, stream):
+    return _dicl(_v.b200_dicl_all_gather(sendBuf, recvBuf, sendCount, datatype, comm, stream), "diclAllGather")
+
+
+def diclReduce(sendBuf, recvBuf, count, datatype, reduceOp, root, comm, stream):
+    return _dicl(_v.b200_dicl_reduce(sendBuf, recvBuf, count, datatype, int(reduceOp), root, comm, stream), "diclReduce")
+
+
+def diclReduceScatter(sendBuf, recvBuf, recvCount, datatype, op, comm, stream):
+    return _dicl(_v.b200_dicl_reduce_scatter(sendBuf, recvBuf, recvCount, datatype, int(op), comm, stream), "diclReduceScatter")
+
+
+def diclSend(sendBuf, count, datatype, peer, comm, stream):
+    return _dicl(_v.b200_dicl_send(sendBuf, count, datatype, peer, comm, stream), "diclSend")
+
+
+def diclRecv(recvBuf, count, datatype, peer, comm, stream):
+    return _dicl(_v.b200_dicl_recv(recvBuf, count, datatype, peer, comm, stream), "diclRecv")
+
+
+def diclAllToAllEqualSplit(sendBuf, recvBuf, count, dataType, comm, stream):
+    return _dicl(_v.b200_dicl_all_to_all_equal_split(sendBuf, recvBuf, count, dataType, comm, stream), "diclAllToAllEqualSplit")
+
+
+def diclAllToAllUnequalSplit(sendBuf, sendCounts, sendDisplacements, recvBuf, recvCounts, recvDisplacements, dataType, comm, stream):
+    n = len(sendCounts)
+    arr = lambda v: (ctypes.c_size_t * n)(*v)  # noqa: E731
+    return _dicl(_v.b200_dicl_all_to_all_unequal_split(sendBuf, arr(sendCounts), arr(sendDisplacements), recvBuf, arr(recvCounts),
+                                                       arr(recvDisplacements), dataType, comm, stream), "diclAllToAllUnequalSplit")
+
+
+def diclGetCommName(comm):
+    buf = ctypes.create_string_buffer(64)
+    _dicl(_v.b200_dicl_get_comm_name(buf, 64, comm), "diclGetCommName")
+    return buf.value.decode()

@@ -1,0 +1,229 @@
+"""ctypes binding of the DIOPI C-ABI (include/diopi/functions.h, functions_ext.h) through the minihost.
+
+Tensors are torch tensors used purely as memory holders: a handle records data pointer, shape, strides, dtype and
+device, exactly the metadata DIPU's diopirt callbacks expose. Every diopiXxx function of the library is callable as
+`diopi.diopiXxx(ctx, ...)` with torch tensors, Python numbers and lists in the argument order of the C prototype;
+a non-zero return code raises DiopiError carrying diopiGetLastErrorString().
+"""
+import ctypes
+
+import torch
+
+from . import _native
+
+_lib = _native.diopi
+_host = _native.host
+
+# ---- enums (include/diopi/diopirt.h) -------------------------------------------------------------------------
+diopi_host, diopi_device = 0, 1
+DTYPE = {
+    torch.int8: 0, torch.uint8: 1, torch.int16: 2, torch.int32: 4, torch.int64: 6, torch.float16: 8, torch.float32: 9,
+    torch.float64: 10, torch.bool: 11, torch.bfloat16: 12,
+}
+RoundModeNone, RoundModeTrunc, RoundModeFloor = 0, 1, 2
+
+
+class DiopiError(RuntimeError):
+    pass
+
+
+class _Size(ctypes.Structure):
+    _fields_ = [("data", ctypes.POINTER(ctypes.c_int64)), ("len", ctypes.c_int64)]
+
+
+class _ScalarU(ctypes.Union):
+    _fields_ = [("fval", ctypes.c_double), ("ival", ctypes.c_int64)]
+
+
+class _Scalar(ctypes.Structure):
+    _anonymous_ = ("u",)
+    _fields_ = [("stype", ctypes.c_int), ("u", _ScalarU)]
+
+
+def _scalar(v):
+    s = _Scalar()
+    if isinstance(v, bool) or isinstance(v, int):
+        s.stype = 6  # diopi_dtype_int64 (bools travel as int64, reference diopi_helper.cpp:74-119)
+        s.ival = int(v)
+    else:
+        s.stype = 10  # diopi_dtype_float64
+        s.fval = float(v)
+    return s
+
+
+_host.minihostMakeTensor.restype = ctypes.c_void_p
+_host.minihostMakeTensor.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64),
+                                     ctypes.c_int, ctypes.c_int, ctypes.c_int]
+_host.minihostFreeTensor.argtypes = [ctypes.c_void_p]
+_host.minihostMakeContext.restype = ctypes.c_void_p
+_host.minihostMakeContext.argtypes = [ctypes.c_void_p, ctypes.c_int]
+_host.minihostResetContext.argtypes = [ctypes.c_void_p]
+_host.minihostFreeContext.argtypes = [ctypes.c_void_p]
+_host.minihostWorkspaceCount.restype = ctypes.c_int64
+_host.minihostWorkspaceCount.argtypes = [ctypes.c_void_p]
+_lib.diopiGetLastErrorString.restype = ctypes.c_char_p
+_lib.diopiGetVendorName.restype = ctypes.c_char_p
+_lib.diopiGetImplVersion.restype = ctypes.c_char_p
+_lib.diopiB200GemmStatus.restype = ctypes.c_int
+
+
+class Handle:
+    """A diopiTensorHandle_t describing a torch tensor's memory. Keeps the tensor alive."""
+
+    __slots__ = ("tensor", "ptr")
+
+    def __init__(self, t):
+        if t.dtype not in DTYPE:
+            raise DiopiError("dtype %s has no diopi counterpart" % t.dtype)
+        nd = t.dim()
+        shape = (ctypes.c_int64 * max(nd, 1))(*t.shape)
+        stride = (ctypes.c_int64 * max(nd, 1))(*t.stride())
+        dev = diopi_device if t.is_cuda else diopi_host
+        idx = t.device.index if t.is_cuda else 0
+        self.tensor = t
+        self.ptr = _host.minihostMakeTensor(ctypes.c_void_p(t.data_ptr()), nd, shape, stride, DTYPE[t.dtype], dev, idx or 0)
+        if not self.ptr:
+            raise DiopiError("could not create a tensor handle")
+
+    def __del__(self):
+        if getattr(self, "ptr", None):
+            _host.minihostFreeTensor(self.ptr)
+            self.ptr = None
+
+
+def handle(t):
+    return t if isinstance(t, Handle) else Handle(t)
+
+
+class Context:
+    """diopiContext: the stream every op of a call is enqueued on, plus the workspace the op requested."""
+
+    def __init__(self, stream=None, device=None):
+        if stream is None:
+            stream = torch.cuda.current_stream().cuda_stream if torch.cuda.is_available() else 0
+        if device is None:
+            device = torch.cuda.current_device() if torch.cuda.is_available() else 0
+        self.stream = int(stream)
+        self.device = int(device)
+        self.ptr = _host.minihostMakeContext(ctypes.c_void_p(self.stream), self.device)
+
+    def release_workspace(self):
+        """What the DIPU wrapper does when it returns: workspace tensors go back to the caching allocator."""
+        _host.minihostResetContext(self.ptr)
+
+    def workspace_count(self):
+        return _host.minihostWorkspaceCount(self.ptr)
+
+    def __del__(self):
+        if getattr(self, "ptr", None):
+            _host.minihostFreeContext(self.ptr)
+            self.ptr = None
+
+
+# ---- signatures ---------------------------------------------------------------------------------------------
+# T: tensor handle   t: tensor handle or None   s: const diopiScalar_t*   i: int64   d: double   b: bool
+# z: diopiSize_t by value   L: (const handle*, int64 count)   r: diopiRoundMode_t
+SIGNATURES = {
+    "diopiCopyInp": "tT", "diopiCastDtype": "Tt", "diopiFill": "Ts", "diopiZeroInp": "T", "diopiOnes": "Tz", "diopiZeros": "Tz",
+    "diopiArange": "Tsss",
+    "diopiAdd": "Ttts", "diopiAddInp": "Tts", "diopiAddScalar": "Ttss", "diopiAddInpScalar": "Tss",
+    "diopiSub": "Ttts", "diopiSubInp": "Tts", "diopiSubScalar": "Ttss", "diopiSubInpScalar": "Tss",
+    "diopiMul": "Ttt", "diopiMulInp": "Tt", "diopiMulScalar": "Tts", "diopiMulInpScalar": "Ts",
+    "diopiDiv": "Tttr", "diopiDivInp": "Ttr", "diopiDivScalar": "Ttsr", "diopiDivInpScalar": "Tsr",
+    "diopiPow": "Tts", "diopiPowInp": "Ts", "diopiPowTensor": "Ttt", "diopiPowScalar": "Tst",
+    "diopiNeg": "Tt", "diopiNegInp": "T", "diopiRsqrt": "Tt", "diopiRsqrtInp": "T", "diopiSqrt": "Tt", "diopiReciprocal": "Tt",
+    "diopiExp": "Tt", "diopiSin": "Tt", "diopiSinInp": "T", "diopiCos": "Tt", "diopiCosInp": "T", "diopiSilu": "Tt", "diopiSiluInp": "T",
+    "diopiSigmoid": "Tt", "diopiRelu": "Tt", "diopiTanh": "Tt",
+    "diopiTriu": "Tti", "diopiTriuInp": "Ti", "diopiMaskedFill": "Tttt", "diopiMaskedFillInp": "Ttt", "diopiMaskedFillScalar": "Ttts",
+    "diopiMaskedFillInpScalar": "Tts", "diopiWhere": "Tttt", "diopiCat": "TLi", "diopiIndexSelect": "Ttit", "diopiEmbedding": "Tttibb",
+    "diopiMean": "Ttz", "diopiSum": "Ttz", "diopiSoftmax": "Tti", "diopiLayerNorm": "TTTtttzd",
+    "diopiMm": "Ttt", "diopiAddmm": "Ttttss", "diopiBmm": "Ttt", "diopiBaddbmm": "Ttttdd", "diopiBaddbmmInp": "Tttdd", "diopiMatmul": "Ttt",
+    "diopiLinear": "Tttt",
+    "diopiRMSNorm": "TTtzttd", "diopiRotaryEmbedding": "Ttttbb",
+}
+
+_CTYPES = {"T": ctypes.c_void_p, "t": ctypes.c_void_p, "s": ctypes.POINTER(_Scalar), "i": ctypes.c_int64, "d": ctypes.c_double,
+           "b": ctypes.c_bool, "z": _Size, "r": ctypes.c_int}
+
+
+def _bind(name):
+    fn = getattr(_lib, name)
+    sig = SIGNATURES[name]
+    argtypes = [ctypes.c_void_p]
+    for c in sig:
+        if c == "L":
+            argtypes += [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int64]
+        else:
+            argtypes.append(_CTYPES[c])
+    fn.argtypes = argtypes
+    fn.restype = ctypes.c_int
+
+    def call(ctx, *args):
+        if len(args) != len(sig):
+            raise TypeError("%s expects %d arguments after ctx, got %d" % (name, len(sig), len(args)))
+        cargs = [ctx.ptr]
+        keep = []
+        for c, a in zip(sig, args):
+            if c in "Tt":
+                if a is None:
+                    cargs.append(None)
+                else:
+                    h = handle(a)
+                    keep.append(h)
+                    cargs.append(h.ptr)
+            elif c == "s":
+                if a is None:
+                    cargs.append(None)
+                else:
+                    s = _scalar(a)
+                    keep.append(s)
+                    cargs.append(ctypes.byref(s))
+            elif c == "z":
+                vals = list(a) if a is not None else []
+                arr = (ctypes.c_int64 * max(len(vals), 1))(*vals)
+                keep.append(arr)
+                cargs.append(_Size(ctypes.cast(arr, ctypes.POINTER(ctypes.c_int64)), len(vals)))
+            elif c == "L":
+                hs = [handle(x) for x in a]
+                keep.append(hs)
+                arr = (ctypes.c_void_p * max(len(hs), 1))(*[h.ptr for h in hs])
+                keep.append(arr)
+                cargs += [arr, len(hs)]
+            elif c == "b":
+                cargs.append(bool(a))
+            elif c == "d":
+                cargs.append(float(a))
+            else:
+                cargs.append(int(a))
+        rc = fn(*cargs)
+        if rc != 0:
+            raise DiopiError("%s failed with code %d: %s" % (name, rc, last_error()))
+        return rc
+
+    call.__name__ = name
+    return call
+
+
+def last_error():
+    return _lib.diopiGetLastErrorString().decode()
+
+
+def vendor_name():
+    return _lib.diopiGetVendorName().decode()
+
+
+def gemm_status():
+    """0 unless a bounded wait inside a tensor-core kernel ever timed out on the current device (synchronises)."""
+    return _lib.diopiB200GemmStatus()
+
+
+def __getattr__(name):
+    if name in SIGNATURES:
+        f = _bind(name)
+        globals()[name] = f
+        return f
+    raise AttributeError(name)
+
+
+def exported_functions():
+    return sorted(SIGNATURES)

@@ -1,0 +1,234 @@
+"""A Llama decoder layer expressed as the stream of DIOPI calls DIPU dispatches for it.
+
+This is harness code, not a model library: it stands where the Python op stream of an eager torch module stands in a
+DIPU process (reference call stack: torch dispatcher -> generated wrapper -> ::diopiXxx, see
+dipu/scripts/autogen_diopi_wrapper/diopi_wrapper_template.py:100-142). Every arithmetic step is one DIOPI call through
+the C-ABI; reshapes / transposes are metadata-only views, which DIPU also serves without calling DIOPI
+(dipu/torch_dipu/csrc_dipu/aten/RegisterDIPU.cpp:382-406). The op order follows the reference's own Llama block
+(dicp/test/model/llama/model.py:104-201).
+
+Tensor parallelism (Megatron style): wq / wk / wv / w1 / w3 are split by output features (heads, FFN columns), wo / w2 by
+input features; the partial sums after wo and w2 are all-reduced through devapis.diclAllReduce on a pool stream,
+bracketed by events the way ProcessGroupDICL::doComm does it
+(dipu/torch_dipu/csrc_dipu/runtime/distributed/ProcessGroupDICL.cpp:438-485).
+"""
+import math
+
+import torch
+
+from . import devapis, diopi
+
+
+def _cfg_get(cfg, name, default=None):
+    return getattr(cfg, name, default)
+
+
+def rope_tables(head_dim, positions, base, device):
+    """cos / sin [len(positions), head_dim/2] in float32, built on the host (a one-off table, as in the reference model)."""
+    inv = 1.0 / (base ** (torch.arange(0, head_dim, 2)[: head_dim // 2].float() / head_dim))
+    ang = torch.outer(positions.float(), inv).float()
+    return torch.cos(ang).to(device), torch.sin(ang).to(device)
+
+
+def embed(table, ids, ctx=None):
+    """Embedding lookup the way DIPU runs it: aten::embedding lowers to index_select(weight, 0, ids.reshape(-1))."""
+    ctx = ctx or diopi.Context()
+    flat = ids.reshape(-1)
+    out = torch.empty((flat.numel(), table.shape[1]), dtype=table.dtype, device=table.device)
+    diopi.diopiIndexSelect(ctx, out, table, 0, flat)
+    return out
+
+
+class TpGroup:
+    """The communicator side of a tensor-parallel group: one DICL communicator and one pool stream per rank."""
+
+    def __init__(self, rank, size, unique_id, device):
+        self.rank, self.size, self.device = rank, size, device
+        self.comm = devapis.diclCommInitRank(size, unique_id, rank, device)
+        self.stream = devapis.getStreamFromPool(device)
+        self.pre_event = devapis.getEventFromPool()
+        self.post_event = devapis.getEventFromPool()
+
+    def all_reduce_(self, tensor, compute_stream):
+        """In-place SUM all-reduce of a dense tensor; the compute stream waits for the result without a host block."""
+        devapis.recordEvent(self.pre_event, compute_stream)
+        devapis.streamWaitEvent(self.stream, self.pre_event)
+        devapis.diclAllReduce(tensor.data_ptr(), tensor.data_ptr(), tensor.numel(), diopi.DTYPE[tensor.dtype], devapis.ReduceOp.SUM, self.comm,
+                              self.stream)
+        devapis.recordEvent(self.post_event, self.stream)
+        devapis.streamWaitEvent(compute_stream, self.post_event)
+
+    def close(self):
+        devapis.syncStream(self.stream)
+        devapis.diclCommDestroy(self.comm)
+        self.comm = None
+
+
+class DecoderLayer:
+    def __init__(self, cfg, weights, dtype=torch.bfloat16, device="cuda:0", tp_rank=0, tp_size=1, tp_group=None):
+        self.hidden = cfg.hidden
+        self.head_dim = cfg.head_dim
+        self.heads_total = cfg.heads
+        self.kv_heads_total = _cfg_get(cfg, "kv_heads", cfg.heads)
+        assert self.heads_total % tp_size == 0 and self.kv_heads_total % tp_size == 0 and cfg.ffn % tp_size == 0
+        self.heads = self.heads_total // tp_size
+        self.kv_heads = self.kv_heads_total // tp_size
+        self.ffn = cfg.ffn // tp_size
+        self.eps = cfg.eps
+        self.rope_base = _cfg_get(cfg, "rope_base", 10000.0)
+        self.interleaved = _cfg_get(cfg, "rope_layout", "half") == "interleaved"
+        self.dtype, self.device = dtype, torch.device(device)
+        self.tp_rank, self.tp_size, self.tp_group = tp_rank, tp_size, tp_group
+        d, r = self.head_dim, tp_rank
+        hq, hk, f = self.heads, self.kv_heads, self.ffn
+
+        def put(t):
+            return t.to(dtype).contiguous().to(self.device)
+
+        self.wq = put(weights["wq"][r * hq * d:(r + 1) * hq * d])
+        self.wk = put(weights["wk"][r * hk * d:(r + 1) * hk * d])
+        self.wv = put(weights["wv"][r * hk * d:(r + 1) * hk * d])
+        self.wo = put(weights["wo"][:, r * hq * d:(r + 1) * hq * d])
+        self.w1 = put(weights["w1"][r * f:(r + 1) * f])
+        self.w3 = put(weights["w3"][r * f:(r + 1) * f])
+        self.w2 = put(weights["w2"][:, r * f:(r + 1) * f])
+        self.attention_norm = put(weights["attention_norm"])
+        self.ffn_norm = put(weights["ffn_norm"])
+        self._tables = {}
+        self._masks = {}
+        self.launches = 0  # DIOPI calls issued (each is at least one kernel launch or device copy)
+
+    # ---- helpers ------------------------------------------------------------------------------------------
+    def _empty(self, *shape, dtype=None):
+        return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
+
+    def _call(self, fn, ctx, *args):
+        self.launches += 1
+        return fn(ctx, *args)
+
+    def _linear(self, ctx, x, w):
+        """F.linear on the CUDA vendor reaches DIOPI as mm(x, W.t()) with a transposed view of the weight."""
+        out = self._empty(x.shape[0], w.shape[0])
+        self._call(diopi.diopiMm, ctx, out, x, w.t())
+        return out
+
+    def _tables_for(self, positions_key, positions):
+        if positions_key not in self._tables:
+            self._tables[positions_key] = rope_tables(self.head_dim, positions, self.rope_base, self.device)
+        return self._tables[positions_key]
+
+    def _mask_for(self, ctx, seq):
+        """Additive causal mask [seq, seq]: -inf above the diagonal, built once with fill + triu."""
+        if seq not in self._masks:
+            m = self._empty(seq, seq)
+            self._call(diopi.diopiFill, ctx, m, float("-inf"))
+            self._call(diopi.diopiTriuInp, ctx, m, 1)
+            self._masks[seq] = m
+        return self._masks[seq]
+
+    def _rope(self, ctx, x, cos, sin):
+        out = torch.empty_like(x)
+        self._call(diopi.diopiRotaryEmbedding, ctx, out, x, cos, sin, False, self.interleaved)
+        return out
+
+    def _expand_kv(self, ctx, t):
+        """[B, kv_heads, S, D] -> [B, heads, S, D] for grouped-query attention: an expand view materialised by copy_."""
+        g = self.heads // self.kv_heads
+        if g == 1:
+            return t
+        b, hk, s, d = t.shape
+        out = self._empty(b, hk, g, s, d)
+        self._call(diopi.diopiCopyInp, ctx, t.unsqueeze(2).expand(b, hk, g, s, d), out)
+        return out.view(b, hk * g, s, d)
+
+    def _all_reduce(self, ctx, t):
+        if self.tp_size > 1:
+            self.tp_group.all_reduce_(t, ctx.stream)
+
+    def _ffn(self, ctx, h):
+        hn = torch.empty_like(h)
+        self._call(diopi.diopiRMSNorm, ctx, hn, None, h, [self.hidden], self.ffn_norm, None, self.eps)
+        g = self._linear(ctx, hn, self.w1)
+        u = self._linear(ctx, hn, self.w3)
+        self._call(diopi.diopiSiluInp, ctx, g)
+        self._call(diopi.diopiMulInp, ctx, g, u)
+        dn = self._linear(ctx, g, self.w2)
+        self._all_reduce(ctx, dn)
+        out = torch.empty_like(h)
+        self._call(diopi.diopiAdd, ctx, out, h, dn, 1)
+        return out
+
+    # ---- prefill ---------------------------------------------------------------------------------------------------
+    def prefill(self, x, batch, seq, ctx=None):
+        """x [batch*seq, hidden] -> [batch*seq, hidden]; causal attention through bmm + softmax."""
+        ctx = ctx or diopi.Context()
+        t, d, hq, hk = batch * seq, self.head_dim, self.heads, self.kv_heads
+        hn = torch.empty_like(x)
+        self._call(diopi.diopiRMSNorm, ctx, hn, None, x, [self.hidden], self.attention_norm, None, self.eps)
+        q = self._linear(ctx, hn, self.wq).view(t, hq, d)
+        k = self._linear(ctx, hn, self.wk).view(t, hk, d)
+        v = self._linear(ctx, hn, self.wv).view(batch, seq, hk, d)
+        cos, sin = self._tables_for(("prefill", seq), torch.arange(seq))
+        q = self._rope(ctx, q, cos, sin).view(batch, seq, hq, d)
+        k = self._rope(ctx, k, cos, sin).view(batch, seq, hk, d)
+        # [B, S, h, D] -> [B, h, S, D]: .transpose(1, 2).contiguous() is a copy_ from a strided view
+        qt, kt, vt = self._empty(batch, hq, seq, d), self._empty(batch, hk, seq, d), self._empty(batch, hk, seq, d)
+        self._call(diopi.diopiCopyInp, ctx, q.transpose(1, 2), qt)
+        self._call(diopi.diopiCopyInp, ctx, k.transpose(1, 2), kt)
+        self._call(diopi.diopiCopyInp, ctx, v.transpose(1, 2), vt)
+        kt, vt = self._expand_kv(ctx, kt), self._expand_kv(ctx, vt)
+        scores = self._empty(batch * hq, seq, seq)
+        self._call(diopi.diopiBmm, ctx, scores, qt.view(batch * hq, seq, d), kt.view(batch * hq, seq, d).transpose(1, 2))
+        self._call(diopi.diopiDivInpScalar, ctx, scores, math.sqrt(d), diopi.RoundModeNone)
+        self._call(diopi.diopiAddInp, ctx, scores, self._mask_for(ctx, seq), 1)
+        self._call(diopi.diopiSoftmax, ctx, scores, scores, -1)
+        av = self._empty(batch * hq, seq, d)
+        self._call(diopi.diopiBmm, ctx, av, scores, vt.view(batch * hq, seq, d))
+        merged = self._empty(batch, seq, hq, d)
+        self._call(diopi.diopiCopyInp, ctx, av.view(batch, hq, seq, d).transpose(1, 2), merged)
+        attn = self._linear(ctx, merged.view(t, hq * d), self.wo)
+        self._all_reduce(ctx, attn)
+        h = torch.empty_like(x)
+        self._call(diopi.diopiAdd, ctx, h, x, attn, 1)
+        out = self._ffn(ctx, h)
+        ctx.release_workspace()
+        return out
+
+    # ---- decode ------------------------------------------------------------------------------------------------------
+    def decode(self, x, k_cache, v_cache, position, ctx=None):
+        """x [batch, hidden]; caches [batch, local kv heads, L, D], slot `position` receives the new key / value and
+        attention covers slots 0..position. Returns [batch, hidden]."""
+        ctx = ctx or diopi.Context()
+        b, d, hq, hk = x.shape[0], self.head_dim, self.heads, self.kv_heads
+        length = position + 1
+        hn = torch.empty_like(x)
+        self._call(diopi.diopiRMSNorm, ctx, hn, None, x, [self.hidden], self.attention_norm, None, self.eps)
+        q = self._linear(ctx, hn, self.wq).view(b, hq, d)
+        k = self._linear(ctx, hn, self.wk).view(b, hk, d)
+        v = self._linear(ctx, hn, self.wv).view(b, hk, d)
+        cos, sin = self._tables_for(("decode", position), torch.tensor([position]))
+        q = self._rope(ctx, q, cos, sin)
+        k = self._rope(ctx, k, cos, sin)
+        # KV append: copy_ into a strided slice of the cache
+        self._call(diopi.diopiCopyInp, ctx, k, k_cache[:, :, position, :])
+        self._call(diopi.diopiCopyInp, ctx, v, v_cache[:, :, position, :])
+        keys, vals = k_cache[:, :, :length, :], v_cache[:, :, :length, :]
+        if hq != hk:
+            keys, vals = self._expand_kv(ctx, keys), self._expand_kv(ctx, vals)
+        cap = keys.shape[2] if hq != hk else k_cache.shape[2]
+        # [B, h, L, D] -> [B*h, L, D] is a free view as long as heads are dense in the cache
+        kview = torch.as_strided(keys, (b * hq, length, d), (cap * d, d, 1), keys.storage_offset())
+        vview = torch.as_strided(vals, (b * hq, length, d), (cap * d, d, 1), vals.storage_offset())
+        scores = self._empty(b * hq, 1, length)
+        self._call(diopi.diopiBmm, ctx, scores, q.reshape(b * hq, 1, d), kview.transpose(1, 2))
+        self._call(diopi.diopiDivInpScalar, ctx, scores, math.sqrt(d), diopi.RoundModeNone)
+        self._call(diopi.diopiSoftmax, ctx, scores, scores, -1)
+        av = self._empty(b * hq, 1, d)
+        self._call(diopi.diopiBmm, ctx, av, scores, vview)
+        attn = self._linear(ctx, av.view(b, hq * d), self.wo)
+        self._all_reduce(ctx, attn)
+        h = torch.empty_like(x)
+        self._call(diopi.diopiAdd, ctx, h, x, attn, 1)
+        out = self._ffn(ctx, h)
+        ctx.release_workspace()
+        return out

@@ -1,0 +1,178 @@
+/*
+ * DIOPI operator functions exported by libdiopi_impl.so (B200 / sm_100a implementation).
+ *
+ * Every prototype is written from the call expression DIPU's generated adapters use; the
+ * citation after each group is the line of
+ *     dipu/scripts/autogen_diopi_wrapper/diopi_functions.yaml
+ * (reference project path) that holds the `interface:` string, i.e. the exact argument order
+ * a DIPU build binds against.  PROVISIONAL: to be diffed against the pinned upstream
+ * diopi/functions.h, which the reference tree does not vendor.
+ *
+ * Conventions the adapters rely on (dipu/torch_dipu/csrc_dipu/aten/ops/OpUtils.hpp:324-338):
+ * inputs may be non-contiguous, broadcast against the output, of mixed dtype, or 0-dim host
+ * tensors; outputs are pre-allocated by the host with the promoted dtype; optional tensors are
+ * NULL; scalars are passed by pointer; all work is enqueued on the context's stream.
+ */
+#ifndef DIOPI_FUNCTIONS_H_
+#define DIOPI_FUNCTIONS_H_
+
+#include "diopi/diopirt.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- copy / cast / fill ---------------------------------------------------------------- */
+/* yaml:2969-2995  note the order: source first, destination second. dtype cast, broadcast
+ * (expand), arbitrary strides and peer devices are all handled here. */
+DIOPI_API diopiError_t diopiCopyInp(diopiContextHandle_t ctx, diopiConstTensorHandle_t src, diopiTensorHandle_t dest);
+/* upstream convenience entry (no DIPU call site in this snapshot): out = cast(input) */
+DIOPI_API diopiError_t diopiCastDtype(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input);
+/* yaml:28-29 */
+DIOPI_API diopiError_t diopiFill(diopiContextHandle_t ctx, diopiTensorHandle_t input, const diopiScalar_t* value);
+/* yaml:2433-2454 */
+DIOPI_API diopiError_t diopiZeroInp(diopiContextHandle_t ctx, diopiTensorHandle_t input);
+DIOPI_API diopiError_t diopiOnes(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiSize_t size);
+DIOPI_API diopiError_t diopiZeros(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiSize_t size);
+/* yaml:2341-2347 */
+DIOPI_API diopiError_t diopiArange(diopiContextHandle_t ctx, diopiTensorHandle_t out, const diopiScalar_t* start,
+                                   const diopiScalar_t* end, const diopiScalar_t* step);
+
+/* ---- binary arithmetic (broadcast + type promotion) ------------------------------------ */
+/* yaml:40-69 */
+DIOPI_API diopiError_t diopiAdd(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                diopiConstTensorHandle_t other, const diopiScalar_t* alpha);
+DIOPI_API diopiError_t diopiAddInp(diopiContextHandle_t ctx, diopiTensorHandle_t input, diopiConstTensorHandle_t other,
+                                   const diopiScalar_t* alpha);
+/* yaml:26-38 */
+DIOPI_API diopiError_t diopiAddScalar(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                      const diopiScalar_t* other, const diopiScalar_t* alpha);
+DIOPI_API diopiError_t diopiAddInpScalar(diopiContextHandle_t ctx, diopiTensorHandle_t input, const diopiScalar_t* other,
+                                         const diopiScalar_t* alpha);
+/* yaml:72-92,1374 */
+DIOPI_API diopiError_t diopiSub(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                diopiConstTensorHandle_t other, const diopiScalar_t* alpha);
+DIOPI_API diopiError_t diopiSubInp(diopiContextHandle_t ctx, diopiTensorHandle_t input, diopiConstTensorHandle_t other,
+                                   const diopiScalar_t* alpha);
+DIOPI_API diopiError_t diopiSubScalar(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                      const diopiScalar_t* other, const diopiScalar_t* alpha);
+DIOPI_API diopiError_t diopiSubInpScalar(diopiContextHandle_t ctx, diopiTensorHandle_t input, const diopiScalar_t* other,
+                                         const diopiScalar_t* alpha);
+/* yaml:159-202  (on the CUDA vendor `other` may be a 0-dim HOST tensor: yaml:169-183) */
+DIOPI_API diopiError_t diopiMul(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                diopiConstTensorHandle_t other);
+DIOPI_API diopiError_t diopiMulInp(diopiContextHandle_t ctx, diopiTensorHandle_t input, diopiConstTensorHandle_t other);
+DIOPI_API diopiError_t diopiMulScalar(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                      const diopiScalar_t* other);
+DIOPI_API diopiError_t diopiMulInpScalar(diopiContextHandle_t ctx, diopiTensorHandle_t input, const diopiScalar_t* other);
+/* yaml:94-151 */
+DIOPI_API diopiError_t diopiDiv(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                diopiConstTensorHandle_t other, diopiRoundMode_t rounding_mode);
+DIOPI_API diopiError_t diopiDivInp(diopiContextHandle_t ctx, diopiTensorHandle_t input, diopiConstTensorHandle_t other,
+                                   diopiRoundMode_t rounding_mode);
+DIOPI_API diopiError_t diopiDivScalar(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                      const diopiScalar_t* other, diopiRoundMode_t rounding_mode);
+DIOPI_API diopiError_t diopiDivInpScalar(diopiContextHandle_t ctx, diopiTensorHandle_t input, const diopiScalar_t* other,
+                                         diopiRoundMode_t rounding_mode);
+/* yaml:1299-1327 */
+DIOPI_API diopiError_t diopiPow(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                const diopiScalar_t* exponent);
+DIOPI_API diopiError_t diopiPowInp(diopiContextHandle_t ctx, diopiTensorHandle_t input, const diopiScalar_t* exponent);
+DIOPI_API diopiError_t diopiPowTensor(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                      diopiConstTensorHandle_t exponent);
+DIOPI_API diopiError_t diopiPowScalar(diopiContextHandle_t ctx, diopiTensorHandle_t out, const diopiScalar_t* input,
+                                      diopiConstTensorHandle_t exponent);
+
+/* ---- unary ------------------------------------------------------------------------------ */
+/* yaml:782-791 */
+DIOPI_API diopiError_t diopiNeg(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input);
+DIOPI_API diopiError_t diopiNegInp(diopiContextHandle_t ctx, diopiTensorHandle_t input);
+/* yaml:1179-1185 */
+DIOPI_API diopiError_t diopiRsqrt(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input);
+DIOPI_API diopiError_t diopiRsqrtInp(diopiContextHandle_t ctx, diopiTensorHandle_t input);
+/* yaml:794-802 */
+DIOPI_API diopiError_t diopiSqrt(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input);
+/* yaml:1789 */
+DIOPI_API diopiError_t diopiReciprocal(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input);
+/* yaml:1505 */
+DIOPI_API diopiError_t diopiExp(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input);
+/* yaml:1733-1753 */
+DIOPI_API diopiError_t diopiSin(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input);
+DIOPI_API diopiError_t diopiSinInp(diopiContextHandle_t ctx, diopiTensorHandle_t input);
+DIOPI_API diopiError_t diopiCos(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input);
+DIOPI_API diopiError_t diopiCosInp(diopiContextHandle_t ctx, diopiTensorHandle_t input);
+/* yaml:1767-1786 */
+DIOPI_API diopiError_t diopiSilu(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input);
+DIOPI_API diopiError_t diopiSiluInp(diopiContextHandle_t ctx, diopiTensorHandle_t input);
+/* yaml:1953 */
+DIOPI_API diopiError_t diopiSigmoid(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input);
+/* yaml:563 */
+DIOPI_API diopiError_t diopiRelu(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input);
+/* yaml:1511 */
+DIOPI_API diopiError_t diopiTanh(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input);
+
+/* ---- masks / selection ------------------------------------------------------------------ */
+/* yaml:2507-2516 */
+DIOPI_API diopiError_t diopiTriu(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input, int64_t diagonal);
+DIOPI_API diopiError_t diopiTriuInp(diopiContextHandle_t ctx, diopiTensorHandle_t input, int64_t diagonal);
+/* yaml:1432-1453 */
+DIOPI_API diopiError_t diopiMaskedFill(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                       diopiConstTensorHandle_t mask, diopiConstTensorHandle_t value);
+DIOPI_API diopiError_t diopiMaskedFillInp(diopiContextHandle_t ctx, diopiTensorHandle_t input, diopiConstTensorHandle_t mask,
+                                          diopiConstTensorHandle_t value);
+DIOPI_API diopiError_t diopiMaskedFillScalar(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                             diopiConstTensorHandle_t mask, const diopiScalar_t* value);
+DIOPI_API diopiError_t diopiMaskedFillInpScalar(diopiContextHandle_t ctx, diopiTensorHandle_t input, diopiConstTensorHandle_t mask,
+                                                const diopiScalar_t* value);
+/* yaml:1566-1571 */
+DIOPI_API diopiError_t diopiWhere(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t condition,
+                                  diopiConstTensorHandle_t input, diopiConstTensorHandle_t other);
+/* yaml:1418-1430 */
+DIOPI_API diopiError_t diopiCat(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t* tensors,
+                                int64_t num_inputs, int64_t dim);
+/* yaml:1926-1933  (aten::embedding lowers to this on DIPU: row gather, bit-exact) */
+DIOPI_API diopiError_t diopiIndexSelect(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                        int64_t dim, diopiConstTensorHandle_t index);
+/* named by the north star; no DIPU call site in this snapshot (only the backward, yaml:2523-2526) */
+DIOPI_API diopiError_t diopiEmbedding(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t weight,
+                                      diopiConstTensorHandle_t indices, int64_t padding_idx, bool scale_grad_byfreq, bool sparse);
+
+/* ---- reductions / normalisation ---------------------------------------------------------- */
+/* yaml:830-842 */
+DIOPI_API diopiError_t diopiMean(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input, diopiSize_t dim);
+/* yaml:584-592 */
+DIOPI_API diopiError_t diopiSum(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input, diopiSize_t dim);
+/* yaml:1290-1292 */
+DIOPI_API diopiError_t diopiSoftmax(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input, int64_t dim);
+/* yaml:350-369 */
+DIOPI_API diopiError_t diopiLayerNorm(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiTensorHandle_t save_mean,
+                                      diopiTensorHandle_t save_invstd, diopiConstTensorHandle_t input, diopiConstTensorHandle_t weight,
+                                      diopiConstTensorHandle_t bias, diopiSize_t normalized_shape, double eps);
+
+/* ---- dense contractions ------------------------------------------------------------------ */
+/* yaml:1829-1837 */
+DIOPI_API diopiError_t diopiMm(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                               diopiConstTensorHandle_t mat2);
+/* yaml:594-597 */
+DIOPI_API diopiError_t diopiAddmm(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                  diopiConstTensorHandle_t mat1, diopiConstTensorHandle_t mat2, const diopiScalar_t* beta,
+                                  const diopiScalar_t* alpha);
+/* yaml:1755-1765 */
+DIOPI_API diopiError_t diopiBmm(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                diopiConstTensorHandle_t mat2);
+/* yaml:1534-1554 */
+DIOPI_API diopiError_t diopiBaddbmm(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                    diopiConstTensorHandle_t batch1, diopiConstTensorHandle_t batch2, double beta, double alpha);
+DIOPI_API diopiError_t diopiBaddbmmInp(diopiContextHandle_t ctx, diopiTensorHandle_t input, diopiConstTensorHandle_t batch1,
+                                       diopiConstTensorHandle_t batch2, double beta, double alpha);
+/* yaml:1885-1893 */
+DIOPI_API diopiError_t diopiMatmul(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                   diopiConstTensorHandle_t other);
+/* yaml:902-909 (not registered for the CUDA vendor, which sees mm(x, W.t()) instead; exported for completeness) */
+DIOPI_API diopiError_t diopiLinear(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                   diopiConstTensorHandle_t weight, diopiConstTensorHandle_t bias);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DIOPI_FUNCTIONS_H_ */

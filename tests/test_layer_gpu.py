@@ -1,0 +1,101 @@
+"""The decoder layer as a stream of DIOPI calls on the GPU against the CPU oracle and the reference's golden output."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import llama_cpu
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _err(got, ref):
+    got = got.float().cpu().reshape(ref.shape)
+    return (got - ref).abs().max().item(), ((got - ref).norm() / ref.norm()).item()
+
+
+def test_c1_fp32_layer_matches_reference_block(pkg):
+    """The CPU configuration (fp32, batch 1, seq 128, hidden 512, 8x64 heads, FFN 1376) run on the GPU, compared with the
+    output of the reference's own TransformerBlock."""
+    from dipu_b200 import layer as L
+    g = np.load(os.path.join(GOLD, "c1_block.npz"))
+    cfg = llama_cpu.LayerConfig(hidden=512, heads=8, kv_heads=8, head_dim=64, ffn=1376, eps=1e-6, rope_layout="interleaved")
+    w = llama_cpu.make_weights(cfg, seed=1234)
+    emb = llama_cpu.make_embedding(32000, 512, seed=1234)
+    ids = torch.from_numpy(g["ids"])
+    lay = L.DecoderLayer(cfg, w, dtype=torch.float32, device=DEV)
+    x = L.embed(emb.to(DEV), ids.to(DEV))
+    assert torch.equal(x.cpu(), torch.from_numpy(g["x"]).view(128, 512))  # embedding gather: bit-exact
+    y = lay.prefill(x, 1, 128)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(y.cpu().numpy().reshape(1, 128, 512), g["y"], rtol=1e-3, atol=2e-5)
+
+
+@pytest.mark.parametrize("kv_heads", [8, 2])
+def test_bf16_prefill_layer(pkg, kv_heads):
+    from dipu_b200 import layer as L
+    cfg = llama_cpu.LayerConfig(hidden=1024, heads=8, kv_heads=kv_heads, head_dim=128, ffn=2752, eps=1e-6)
+    w = llama_cpu.make_weights(cfg, seed=21)
+    emb = llama_cpu.make_embedding(32000, 1024, seed=21)
+    ids = llama_cpu.make_token_ids(2, 256, seed=21)
+    ref = llama_cpu.decoder_layer_prefill(cfg, llama_cpu.round_weights(w, torch.bfloat16), llama_cpu.round_tensor(emb, torch.bfloat16), ids)
+    lay = L.DecoderLayer(cfg, w, dtype=torch.bfloat16, device=DEV)
+    y = lay.prefill(L.embed(emb.to(torch.bfloat16).to(DEV), ids.to(DEV)), 2, 256)
+    torch.cuda.synchronize()
+    max_abs, rel = _err(y, ref)
+    assert pkg.diopi.gemm_status() == 0
+    assert max_abs <= 2e-2 and rel <= 5e-3, (max_abs, rel)
+
+
+@pytest.mark.parametrize("kv_heads", [8, 4])
+def test_bf16_decode_layer(pkg, kv_heads):
+    from dipu_b200 import layer as L
+    cfg = llama_cpu.LayerConfig(hidden=1024, heads=8, kv_heads=kv_heads, head_dim=128, ffn=2752, eps=1e-6)
+    w = llama_cpu.make_weights(cfg, seed=31)
+    b, cap, pos = 4, 512, 300
+    kc, vc = llama_cpu.make_kv_cache(cfg, b, cap, seed=31)
+    rng = np.random.default_rng(32)
+    x = torch.from_numpy(rng.standard_normal((b, 1024), dtype=np.float32) * 0.5)
+    bf = torch.bfloat16
+    ref, kref, vref = llama_cpu.decoder_layer_decode(cfg, llama_cpu.round_weights(w, bf), llama_cpu.round_tensor(x, bf),
+                                                     llama_cpu.round_tensor(kc, bf), llama_cpu.round_tensor(vc, bf), pos)
+    lay = L.DecoderLayer(cfg, w, dtype=bf, device=DEV)
+    kd, vd = kc.to(bf).to(DEV), vc.to(bf).to(DEV)
+    y = lay.decode(x.to(bf).to(DEV), kd, vd, pos)
+    torch.cuda.synchronize()
+    max_abs, rel = _err(y, ref)
+    assert pkg.diopi.gemm_status() == 0
+    assert max_abs <= 2e-2 and rel <= 5e-3, (max_abs, rel)
+    # the appended key / value slot
+    ka, _ = _err(kd[:, :, pos], kref[:, :, pos])
+    va, _ = _err(vd[:, :, pos], vref[:, :, pos])
+    assert ka <= 2e-2 and va <= 2e-2
+    # every other slot is untouched, bit for bit
+    mask = torch.ones(cap, dtype=torch.bool)
+    mask[pos] = False
+    assert torch.equal(kd.cpu()[:, :, mask], kc.to(bf)[:, :, mask])
+
+
+def test_tp_shards_sum_to_unsharded_layer_on_one_gpu(pkg):
+    """Two tensor-parallel ranks emulated one after the other on one GPU: the row-parallel partial sums of the attention
+    block, added where the all-reduce would add them, reproduce the unsharded attention output. (w2 is zeroed so that a
+    rank's layer output is exactly x + its attention partial.)"""
+    from dipu_b200 import layer as L
+    cfg = llama_cpu.LayerConfig(hidden=512, heads=8, kv_heads=8, head_dim=64, ffn=1376, eps=1e-6)
+    w = llama_cpu.make_weights(cfg, seed=41)
+    rng = np.random.default_rng(42)
+    x = torch.from_numpy(rng.standard_normal((128, 512), dtype=np.float32) * 0.5)
+    full_attn = llama_cpu.attention_prefill(cfg, w, llama_cpu.rms_norm(x, w["attention_norm"], cfg.eps), 2, 64)
+    wz = dict(w)
+    wz["w2"] = torch.zeros_like(w["w2"])
+    acc = torch.zeros_like(full_attn)
+    for r in range(2):
+        lay = L.DecoderLayer(cfg, wz, dtype=torch.float32, device=DEV, tp_rank=r, tp_size=2)
+        lay.tp_size = 1  # no communicator on one GPU: the partial sums are added on the host below
+        y = lay.prefill(x.to(DEV), 2, 64)
+        torch.cuda.synchronize()
+        acc += y.cpu() - x
+    np.testing.assert_allclose(acc.numpy(), full_attn.numpy(), rtol=1e-3, atol=2e-5)

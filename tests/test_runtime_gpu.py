@@ -1,0 +1,145 @@
+"""Vendor runtime on a real device: devapis primitives, stream / event pools and the caching allocator
+(semantics pinned by dipu/tests/python/individual_scripts/test_memory_stats.py:6-82, test_allocator.py:6-90,
+test_rt_tensor.py:109-124, unittests/test_get_device_properties.py:5-13)."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_device_queries(devapis):
+    assert devapis.getDeviceCount() >= 1
+    p = devapis.getDeviceProperties(0)
+    assert p.name.decode().startswith("NVIDIA") and p.major >= 10 and p.multiProcessorCount > 0 and p.totalGlobalMem >= 256 << 20
+    free, total = devapis.getDeviceStatus(0)
+    assert 0 < free <= total
+    devapis.setDevice(0)
+    assert devapis.current_device() == 0
+    assert devapis.getDriverVersion() > 0 and devapis.getRuntimeVersion() > 0
+    devapis.checkLastError()
+
+
+def test_streams_events_copies(devapis):
+    devapis.setDevice(0)
+    s = devapis.createStream()
+    assert devapis.streamNotNull(s) and not devapis.streamNotNull(None)
+    e0, e1 = devapis.createEvent(), devapis.createEvent()
+    n = 64 << 20
+    st, d0 = devapis.mallocDevice(n)
+    st2, d1 = devapis.mallocDevice(n)
+    assert st == devapis.OpStatus.SUCCESS and st2 == devapis.OpStatus.SUCCESS
+    h = devapis.mallocHost(n)
+    assert devapis.isPinnedPtr(h)
+    ctypes.memset(h, 0x5a, n)
+    devapis.recordEvent(e0, s)
+    devapis.memCopyH2DAsync(s, n, d0, h)
+    devapis.memCopyD2DAsync(s, n, 0, d1, 0, d0)
+    devapis.memSetAsync(s, d0, 0, n)
+    devapis.recordEvent(e1, s)
+    devapis.waitEvent(e1)
+    assert devapis.getEventStatus(e1) == devapis.EventStatus.READY
+    assert devapis.eventElapsedTime(e0, e1) > 0
+    assert devapis.isStreamEmpty(s)
+    back = (ctypes.c_ubyte * 16)()
+    devapis.memCopyD2H(16, ctypes.addressof(back), d1)
+    assert bytes(back) == b"\x5a" * 16
+    devapis.memCopyD2H(16, ctypes.addressof(back), d0)
+    assert bytes(back) == b"\x00" * 16
+    s2 = devapis.getStreamFromPool(0)
+    devapis.streamWaitEvent(s2, e1)
+    devapis.syncStream(s2)
+    assert devapis.getDefaultStream(0) == devapis.getDefaultStream(0)
+    pool = {devapis.getStreamFromPool(0) for _ in range(16)}
+    assert len(pool) == 8  # eight pool streams handed out round-robin
+    ev = devapis.getEventFromPool()
+    devapis.restoreEventToPool(ev)
+    assert devapis.getEventFromPool() == ev  # recycled
+    devapis.restoreEventToPool(ev)
+    devapis.freeDevice(d0)
+    devapis.freeDevice(d1)
+    devapis.freeHost(h)
+    devapis.destroyEvent(e0)
+    devapis.destroyEvent(e1)
+    devapis.destroyStream(s)
+
+
+def test_malloc_device_reports_nomem_without_raising(devapis):
+    devapis.setDevice(0)
+    _, total = devapis.getDeviceStatus(0)
+    st, p = devapis.mallocDevice(total * 4, throwExcepion=False)  # larger than the device: refused by the driver up front
+    assert st == devapis.OpStatus.ERR_NOMEM and p is None
+    devapis.checkLastError()  # the error state was cleared
+    with pytest.raises(devapis.VendorError):
+        devapis.mallocDevice(total * 4)
+
+
+def test_caching_allocator_on_device(devapis):
+    A = devapis.CachingAllocator
+    A.useFakeBackend(0)  # make sure the CUDA backend is active
+    devapis.setDevice(0)
+    s = devapis.getDefaultStream(0)
+    A.emptyCache()
+    base = A.stats(0)
+    ptrs = []
+    expect = 0
+    for numel in (1, 100, 1000, 300000, 5 << 20, 40 << 20):
+        nbytes = 4 * numel
+        ptrs.append(A.allocate(nbytes, 0, s))
+        expect += ((nbytes - 1) | 511) + 1
+        st = A.stats(0)
+        assert st["allocated_bytes"] - base["allocated_bytes"] >= expect - 0  # rounded to 512 B, never less
+        assert st["reserved_bytes"] >= st["allocated_bytes"]
+    # memory is usable
+    torch.cuda.synchronize()
+    devapis.memSetAsync(s, ptrs[-1], 1, 160 << 20)
+    devapis.syncStream(s)
+    for p in ptrs:
+        A.free(p)
+    st = A.stats(0)
+    assert st["allocated_bytes"] == base["allocated_bytes"] and st["reserved_bytes"] > 0
+    # a second round of the same sizes is served from the cache
+    mallocs = st["num_device_mallocs"]
+    again = [A.allocate(4 * n, 0, s) for n in (1, 100, 1000, 300000, 5 << 20, 40 << 20)]
+    assert A.stats(0)["num_device_mallocs"] == mallocs
+    for p in again:
+        A.free(p)
+    # cross-stream use defers the reuse until the other stream's work is done
+    p = A.allocate(1 << 20, 0, s)
+    other = devapis.getStreamFromPool(0)
+    A.recordStream(p, other)
+    A.free(p)
+    devapis.syncStream(other)
+    q = A.allocate(1 << 20, 0, s)
+    A.free(q)
+    A.emptyCache()
+    assert A.stats(0)["reserved_bytes"] == 0
+    assert A.stats(0)["allocated_bytes_peak"] >= expect
+    A.resetPeakStats(0)
+    assert A.stats(0)["allocated_bytes_peak"] == 0
+
+
+def test_allocator_every_small_size(devapis):
+    # dipu/tests/python/individual_scripts/test_allocator.py:6-90 sweeps 0..32 KiB byte by byte; a stride keeps this quick
+    A = devapis.CachingAllocator
+    devapis.setDevice(0)
+    s = devapis.getDefaultStream(0)
+    live = []
+    for n in list(range(0, 2050)) + list(range(2050, 32768, 97)):
+        p = A.allocate(n, 0, s)
+        if n == 0:
+            assert p is None
+        else:
+            assert p % 512 == 0
+            live.append(p)
+        if len(live) > 64:
+            A.free(live.pop(0))
+    for p in live:
+        A.free(p)
+    hp = devapis.CachingHostAllocator.allocate(1000)
+    assert devapis.isPinnedPtr(hp)
+    devapis.CachingHostAllocator.recordStream(hp, s)
+    devapis.CachingHostAllocator.free(hp)
+    devapis.CachingHostAllocator.emptyCache()
+    A.emptyCache()
