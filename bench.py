@@ -1,0 +1,414 @@
+"""Benchmark of the hot path: decoder-layer tokens/s through the DIOPI C-ABI on the B200 vendor backend.
+
+    python bench.py --gpus N --steps K --warmup W            # this repository's arm
+    python bench.py --impl reference --gpus N --steps K ...  # the reference's CPU path (torch CPU aten), host cores
+
+Workload (config.workload): the Llama-2-7B-shaped decoder layer in prefill, bf16, batch 8 x seq 2048 (16384 tokens),
+hidden 4096, 32 heads x 128, SwiGLU 11008, causal attention through bmm + softmax, weights N(0, 0.02), activations from
+seeded token ids through the embedding table [32000, 4096]. Everything is synthetic and seeded. With N > 1 GPUs the layer
+is tensor-parallel (column-parallel q/k/v/gate/up, row-parallel o/down, diclAllReduce after o_proj and down_proj): total
+work is fixed, so scaling is "strong".
+
+A step is one layer forward over the 16384 tokens. `value` times steps whose input hidden states are resident in HBM;
+`e2e` times the call a user makes with host buffers: token ids copied from pinned host memory, embedding lookup, layer,
+and the layer output copied back to pinned host memory, every step. One JSON line is printed by rank 0.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SEED = 1234
+VOCAB = 32000
+
+
+class Cfg:
+    def __init__(self, hidden=4096, heads=32, kv_heads=32, head_dim=128, ffn=11008, eps=1e-6, rope_base=10000.0, rope_layout="half"):
+        self.hidden, self.heads, self.kv_heads, self.head_dim, self.ffn = hidden, heads, kv_heads, head_dim, ffn
+        self.eps, self.rope_base, self.rope_layout = eps, rope_base, rope_layout
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "tflops_burst": p["bf16_tflops"], "tflops_sustained": p["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops_burst": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()  # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons, power = [], None, set(), []
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax = float(f[2])
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm),
+                "power_w_max": max(power) if power else None}
+
+
+def make_device_weights(cfg, device, dtype):
+    """Full (unsharded) N(0, 0.02) weights, identical on every rank (same seed), generated on the device."""
+    g = torch.Generator(device=device)
+    g.manual_seed(SEED)
+
+    def n(*shape):
+        return (torch.randn(shape, generator=g, device=device, dtype=torch.float32) * 0.02).to(dtype)
+
+    d = cfg.head_dim
+    return {
+        "wq": n(cfg.heads * d, cfg.hidden), "wk": n(cfg.kv_heads * d, cfg.hidden), "wv": n(cfg.kv_heads * d, cfg.hidden),
+        "wo": n(cfg.hidden, cfg.heads * d), "w1": n(cfg.ffn, cfg.hidden), "w3": n(cfg.ffn, cfg.hidden), "w2": n(cfg.hidden, cfg.ffn),
+        "attention_norm": torch.ones(cfg.hidden, device=device, dtype=dtype), "ffn_norm": torch.ones(cfg.hidden, device=device, dtype=dtype),
+    }
+
+
+def layer_flops(cfg, batch, seq, tp):
+    t = batch * seq
+    d = cfg.head_dim
+    lin = 2 * t * (cfg.hidden * (cfg.heads * d) * 2 + cfg.hidden * (cfg.kv_heads * d) * 2 + 3 * cfg.hidden * cfg.ffn) / tp
+    attn = 4 * batch * cfg.heads * seq * seq * d / tp
+    return lin, attn
+
+
+# ---------------------------------------------------------------------------------------------------------------------------
+def run_reference(args, rank, world):
+    """The reference's own CPU implementation of the path: DIPU's forced CPU fallback executes torch CPU aten kernels
+    (CPUFallback.cpp:130). Timed on the host cores with all threads, each step a bounded sample of the workload."""
+    if rank != 0:
+        return
+    from oracle import llama_cpu
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cfg = llama_cpu.LayerConfig(hidden=4096, heads=32, kv_heads=32, head_dim=128, ffn=11008)
+    sample_batch, seq = 1, 2048
+    w = llama_cpu.make_weights(cfg, seed=SEED)
+    emb = llama_cpu.make_embedding(VOCAB, cfg.hidden, seed=SEED)
+    ids = llama_cpu.make_token_ids(8, seq, seed=SEED)[:sample_batch]
+    with torch.no_grad():
+        for _ in range(max(args.warmup, 1)):
+            llama_cpu.decoder_layer_prefill(cfg, w, emb, ids)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            llama_cpu.decoder_layer_prefill(cfg, w, emb, ids)
+        dt = time.perf_counter() - t0
+    value = sample_batch * seq * args.steps / dt
+    sample = "1 of the 8 sequences per step (2048 tokens), fp32, torch CPU aten, %d threads" % cores
+    line = {
+        "impl": "reference", "metric": "decoder-layer tokens/s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "llama2-7b-shaped decoder layer, prefill, batch 8 x seq 2048, bmm+softmax attention", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def cpu_baseline_leg():
+    """Bounded CPU sample for the cpu_baseline object of this repository's arm (rank 0, N = 1 only)."""
+    from oracle import llama_cpu
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cfg = llama_cpu.LayerConfig(hidden=4096, heads=32, kv_heads=32, head_dim=128, ffn=11008)
+    w = llama_cpu.make_weights(cfg, seed=SEED)
+    emb = llama_cpu.make_embedding(VOCAB, cfg.hidden, seed=SEED)
+    ids = llama_cpu.make_token_ids(8, 2048, seed=SEED)[:1]
+    with torch.no_grad():
+        llama_cpu.decoder_layer_prefill(cfg, w, emb, ids)
+        t0 = time.perf_counter()
+        reps = 0
+        while reps < 3 or (time.perf_counter() - t0 < 10.0 and reps < 50):
+            llama_cpu.decoder_layer_prefill(cfg, w, emb, ids)
+            reps += 1
+        dt = time.perf_counter() - t0
+    return {"value": 2048 * reps / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": "%d forward passes over 1 of the 8 sequences (2048 tokens), fp32, torch CPU aten, %d threads" % (reps, cores)}
+
+
+# ---------------------------------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="skip the secondary decode measurement")
+    ap.add_argument("--no-caching-allocator", action="store_true", help="let torch use its own allocator for tensors")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import __graft_entry__ as entry
+    pkg = entry.load_package()  # raises when the CUDA libraries are missing: there is no fallback path
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the product has no CPU path")
+    if not args.no_caching_allocator:
+        pkg.install_caching_allocator()
+    torch.cuda.set_device(local_rank)
+    device = "cuda:%d" % local_rank
+    from dipu_b200 import devapis, diopi
+    from dipu_b200 import layer as L
+
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("gloo", rank=rank, world_size=world)  # control plane only: barriers and timing exchange
+    tp_group = None
+    if world > 1:
+        uid = [devapis.diclGetUniqueId() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)  # the unique id travels through the store as bytes, as in ProcessGroupDICL
+        tp_group = L.TpGroup(rank, world, uid[0], local_rank)
+
+    cfg = Cfg()
+    dtype = torch.bfloat16
+    batch, seq = args.batch, args.seq
+    tokens = batch * seq
+    weights = make_device_weights(cfg, device, dtype)
+    lay = L.DecoderLayer(cfg, weights, dtype=dtype, device=device, tp_rank=rank, tp_size=world, tp_group=tp_group)
+    del weights
+    g = torch.Generator(device=device)
+    g.manual_seed(SEED + 1)
+    table = (torch.randn((VOCAB, cfg.hidden), generator=g, device=device, dtype=torch.float32) * 0.02).to(dtype)
+    gi = torch.Generator()
+    gi.manual_seed(SEED + 2)
+    ids_host = torch.randint(0, VOCAB, (batch, seq), generator=gi, dtype=torch.int64).pin_memory()
+    ids_dev = torch.empty((batch, seq), dtype=torch.int64, device=device)
+    out_host = torch.empty((tokens, cfg.hidden), dtype=dtype).pin_memory()
+
+    stream = torch.cuda.current_stream()
+    ctx = diopi.Context(stream=stream.cuda_stream, device=local_rank)
+    x = L.embed(table, ids_host.to(device), ctx)  # resident input of the device-timed region
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    def step_resident():
+        return lay.prefill(x, batch, seq, ctx)
+
+    def step_e2e():
+        devapis.memCopyH2DAsync(stream.cuda_stream, ids_host.numel() * 8, ids_dev.data_ptr(), ids_host.data_ptr())  # this step's input
+        h = L.embed(table, ids_dev, ctx)
+        y = lay.prefill(h, batch, seq, ctx)
+        devapis.memCopyD2HAsync(stream.cuda_stream, y.numel() * y.element_size(), out_host.data_ptr(), y.data_ptr())  # this step's result
+        return y
+
+    # ---- device-resident timing ----
+    for _ in range(args.warmup):
+        step_resident()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    lay.launches = 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step_resident()
+    e1.record(stream)
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    launches = lay.launches
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end-to-end timing (host buffers in, host buffers out) ----
+    for _ in range(2):
+        step_e2e()
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step_e2e()
+    e1.record(stream)
+    barrier()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1))
+
+    # ---- per-op device times: the same step with events around every DIOPI call ----
+    per_op = {}
+    orig_call = lay._call
+
+    def timed_call(fn, c, *a):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(stream)
+        r = orig_call(fn, c, *a)
+        e.record(stream)
+        per_op.setdefault(fn.__name__, []).append((s, e, a))
+        return r
+
+    lay._call = timed_call
+    reps = 3
+    for _ in range(reps):
+        step_resident()
+    torch.cuda.synchronize()
+    lay._call = orig_call
+    peaks = measured_peaks()
+    ops = {}
+    mm_flops, mm_ms, bmm_flops, bmm_ms = 0.0, 0.0, 0.0, 0.0
+    for name, recs in per_op.items():
+        ms = sum(s.elapsed_time(e) for s, e, _ in recs) / reps
+        ops[name] = {"ms_per_step": round(ms, 4), "calls_per_step": len(recs) // reps}
+        if name in ("diopiMm", "diopiBmm"):
+            fl = 0.0
+            for _, _, a in recs:
+                out, a0, b0 = a[0], a[1], a[2]
+                fl += 2.0 * out.numel() * a0.shape[-1]
+            fl /= reps
+            ops[name]["tflops"] = round(fl / (ms * 1e-3) / 1e12, 1)
+            if name == "diopiMm":
+                mm_flops, mm_ms = fl, ms
+            else:
+                bmm_flops, bmm_ms = fl, ms
+        else:
+            by = 0.0
+            for _, _, a in recs:
+                seen = set()
+                for t in a:
+                    if isinstance(t, torch.Tensor) and t.is_cuda and t.data_ptr() not in seen:
+                        seen.add(t.data_ptr())
+                        by += t.numel() * t.element_size()
+                if name.endswith("Inp") or name.endswith("InpScalar"):
+                    by += a[0].numel() * a[0].element_size()  # read-modify-write of the first operand
+            by /= reps
+            ops[name]["gbs"] = round(by / (ms * 1e-3) / 1e9, 1)
+    mm_calls = ops.get("diopiMm", {}).get("calls_per_step", 1)
+    achieved = mm_flops / (mm_ms * 1e-3) / 1e12 if mm_ms > 0 else 0.0
+    roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel (diopiMm: the 7 projection GEMMs of the layer)", "achieved": round(achieved, 1),
+                "peak": peaks["tflops_sustained"], "unit": "TFLOP/s", "frac": round(achieved / peaks["tflops_sustained"], 4),
+                "peak_source": "%s bf16 cuBLAS, sustained (kernel timed inside a long step)" % peaks["source"],
+                "flops_per_launch": mm_flops / max(mm_calls, 1), "ms_per_launch": mm_ms / max(mm_calls, 1), "traffic": None}
+
+    # ---- secondary measurement: the same layer in decode (batch 64, KV length 4096) ----
+    decode = None
+    if not args.no_decode:
+        decode = run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ranks, peaks)
+
+    if rank == 0:
+        lin, attn = layer_flops(cfg, batch, seq, world)
+        value = tokens * args.steps / (ms_total * 1e-3)
+        e2e_value = tokens * args.steps / (ms_e2e * 1e-3)
+        line = {
+            "metric": "decoder-layer tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "llama2-7b-shaped decoder layer, prefill, batch %d x seq %d, bmm+softmax attention" % (batch, seq),
+                       "hidden": cfg.hidden, "heads": cfg.heads, "head_dim": cfg.head_dim, "ffn": cfg.ffn, "tokens_per_step": tokens,
+                       "parallelism": "tp%d" % world, "l2": "inputs larger than L2: weights 405 MB + >=134 MB per activation, no flush",
+                       "allocator": "torch default" if args.no_caching_allocator else "b200 caching allocator (pluggable)"},
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": ids_host.numel() * 8,
+                    "d2h_bytes_per_step": out_host.numel() * out_host.element_size()},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": roofline,
+            "layer_tflops": round((lin + attn) * args.steps / (ms_total * 1e-3) / 1e12, 1),
+            "ops": ops,
+            "decode": decode,
+            "gemm_status": diopi.gemm_status(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline_leg()
+        else:
+            line["cpu_baseline"] = None
+        print(json.dumps(line), flush=True)
+    if tp_group is not None:
+        barrier()
+        tp_group.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ranks, peaks):
+    """7B-shaped layer in decode: batch 64, one new token per sequence, bf16 KV cache of length 4096 per sequence."""
+    b, length = 64, 4096
+    g = torch.Generator(device=device)
+    g.manual_seed(SEED + 3)
+    kc = torch.randn((b, lay.kv_heads, length, cfg.head_dim), generator=g, device=device, dtype=torch.float32).to(dtype)
+    vc = torch.randn((b, lay.kv_heads, length, cfg.head_dim), generator=g, device=device, dtype=torch.float32).to(dtype)
+    xd = (torch.randn((b, cfg.hidden), generator=g, device=device, dtype=torch.float32) * 0.5).to(dtype)
+    for _ in range(5):
+        lay.decode(xd, kc, vc, length - 1, ctx)
+    barrier()
+    steps = 50
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        lay.decode(xd, kc, vc, length - 1, ctx)
+    e1.record(stream)
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1)) / steps
+    d = cfg.head_dim
+    weight_bytes = 2 * (cfg.hidden * lay.heads * d * 2 + cfg.hidden * lay.kv_heads * d * 2 + 3 * cfg.hidden * lay.ffn)
+    kv_bytes = 2 * 2 * b * lay.kv_heads * length * d
+    gbs = (weight_bytes + kv_bytes) / (ms * 1e-3) / 1e9
+    return {"workload": "decode, batch 64, KV length 4096, tp%d" % world, "tokens_per_s": b / (ms * 1e-3), "ms_per_step": ms,
+            "algorithmic_bytes_per_step_per_gpu": weight_bytes + kv_bytes, "achieved_gbs": round(gbs, 1),
+            "hbm_frac": round(gbs / peaks["hbm_gbs"], 4), "peak_source": peaks["source"]}
+
+
+if __name__ == "__main__":
+    main()

@@ -12,4 +12,18 @@ Importing the package loads the native libraries; it fails if they have not been
 from . import _native  # noqa: F401  (raises ImportError when the libraries are missing)
 from . import devapis, diopi  # noqa: F401
 
-__all__ = ["devapis", "diopi"]
+__all__ = ["devapis", "diopi", "install_caching_allocator"]
+
+_allocator_installed = False
+
+
+def install_caching_allocator():
+    """Makes torch allocate every CUDA tensor through this runtime's caching allocator (what DIPU does with
+    c10::SetAllocator). Must run before the process allocates any CUDA memory through torch."""
+    global _allocator_installed
+    if _allocator_installed:
+        return
+    import torch
+    alloc = torch.cuda.memory.CUDAPluggableAllocator(_native.VENDOR_LIB, "b200_torch_alloc", "b200_torch_free")
+    torch.cuda.memory.change_current_allocator(alloc)
+    _allocator_installed = True

@@ -20,6 +20,7 @@
 
 #include <stddef.h>
 #include <stdint.h>
+#include <sys/types.h>
 
 #ifdef __cplusplus
 extern "C" {
@@ -131,6 +132,12 @@ B200_API b200Status_t b200_cache_configure(const char* conf);
  * pending_events != 0 makes every recorded event stay "not ready" until b200_cache_fake_complete_events(). */
 B200_API b200Status_t b200_cache_use_fake_backend(size_t capacity, int pending_events);
 B200_API b200Status_t b200_cache_fake_complete_events(void);
+
+/* Allocation hooks with the signatures torch.cuda.memory.CUDAPluggableAllocator expects, so that a stock torch build can
+ * use this allocator for every device tensor, as DIPU does through c10::SetAllocator
+ * (runtime/core/allocator/DIPUCachingAllocator.cpp:336-342). */
+B200_API void* b200_torch_alloc(ssize_t size, int device, void* stream);
+B200_API void b200_torch_free(void* ptr, ssize_t size, int device, void* stream);
 
 /* ---- caching pinned-host allocator (runtime/core/allocator/DIPUCachingHostAllocator.cpp:99-299) --------- */
 B200_API b200Status_t b200_host_cache_alloc(void** p, size_t nbytes);

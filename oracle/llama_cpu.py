@@ -134,64 +134,75 @@ def _expand_kv(cfg, t):
 
 
 # ---- the layer --------------------------------------------------------------------------------------------------------
-def attention_prefill(cfg, w, x, batch, seq):
+# `step` is applied wherever the eager op stream materialises a tensor. The identity gives the fp32 oracle. Rounding to
+# bf16 there (step=stepwise(torch.bfloat16)) gives what the reference's literal CPU fallback produces on bf16 tensors:
+# its custom fallbacks up-cast fp16 only, so every op reads and writes bf16
+# (dipu/torch_dipu/csrc_dipu/aten/ops/CustomFallbackFunctions.hpp:23-30) while computing in fp32 internally.
+def _identity(t):
+    return t
+
+
+def stepwise(dtype):
+    return lambda t: t.to(dtype).to(torch.float32)
+
+
+def attention_prefill(cfg, w, x, batch, seq, step=_identity):
     t = batch * seq
     d = cfg.head_dim
-    q = (x @ w["wq"].t()).view(t, cfg.heads, d)
-    k = (x @ w["wk"].t()).view(t, cfg.kv_heads, d)
-    v = (x @ w["wv"].t()).view(batch, seq, cfg.kv_heads, d)
+    q = step(x @ w["wq"].t()).view(t, cfg.heads, d)
+    k = step(x @ w["wk"].t()).view(t, cfg.kv_heads, d)
+    v = step(x @ w["wv"].t()).view(batch, seq, cfg.kv_heads, d)
     cos, sin = rope_tables(d, torch.arange(seq), cfg.rope_base)
-    q = rotary(cfg, q, cos, sin).view(batch, seq, cfg.heads, d).transpose(1, 2)
-    k = rotary(cfg, k, cos, sin).view(batch, seq, cfg.kv_heads, d).transpose(1, 2)
+    q = step(rotary(cfg, q, cos, sin)).view(batch, seq, cfg.heads, d).transpose(1, 2)
+    k = step(rotary(cfg, k, cos, sin)).view(batch, seq, cfg.kv_heads, d).transpose(1, 2)
     v = v.transpose(1, 2)
     k, v = _expand_kv(cfg, k), _expand_kv(cfg, v)
-    scores = torch.matmul(q, k.transpose(2, 3)) / math.sqrt(d)
-    scores = scores + causal_mask(seq)
-    probs = torch.softmax(scores.float(), dim=-1)
-    out = torch.matmul(probs, v).transpose(1, 2).contiguous().view(t, cfg.heads * d)
-    return out @ w["wo"].t()
+    scores = step(step(torch.matmul(q, k.transpose(2, 3))) / math.sqrt(d))
+    scores = step(scores + causal_mask(seq))
+    probs = step(torch.softmax(scores.float(), dim=-1))
+    out = step(torch.matmul(probs, v)).transpose(1, 2).contiguous().view(t, cfg.heads * d)
+    return step(out @ w["wo"].t())
 
 
-def feed_forward(w, x):
-    return (torch.nn.functional.silu(x @ w["w1"].t()) * (x @ w["w3"].t())) @ w["w2"].t()
+def feed_forward(w, x, step=_identity):
+    gate = step(torch.nn.functional.silu(step(x @ w["w1"].t())))
+    return step(step(gate * step(x @ w["w3"].t())) @ w["w2"].t())
 
 
-def decoder_layer_prefill(cfg, w, embedding, ids):
+def decoder_layer_prefill_from_hidden(cfg, w, x, batch, seq, step=_identity):
+    h = step(x + attention_prefill(cfg, w, step(rms_norm(x, w["attention_norm"], cfg.eps)), batch, seq, step))
+    return step(h + feed_forward(w, step(rms_norm(h, w["ffn_norm"], cfg.eps)), step))
+
+
+def decoder_layer_prefill(cfg, w, embedding, ids, step=_identity):
     """ids [B, S] int64 -> layer output [B*S, hidden] float32."""
     batch, seq = ids.shape
-    x = embedding[ids.reshape(-1)]
-    h = x + attention_prefill(cfg, w, rms_norm(x, w["attention_norm"], cfg.eps), batch, seq)
-    return h + feed_forward(w, rms_norm(h, w["ffn_norm"], cfg.eps))
+    return decoder_layer_prefill_from_hidden(cfg, w, embedding[ids.reshape(-1)], batch, seq, step)
 
 
-def decoder_layer_prefill_from_hidden(cfg, w, x, batch, seq):
-    h = x + attention_prefill(cfg, w, rms_norm(x, w["attention_norm"], cfg.eps), batch, seq)
-    return h + feed_forward(w, rms_norm(h, w["ffn_norm"], cfg.eps))
-
-
-def decoder_layer_decode(cfg, w, x, k_cache, v_cache, position):
+def decoder_layer_decode(cfg, w, x, k_cache, v_cache, position, step=_identity):
     """One new token per sequence. x [B, hidden]; caches [B, kv_heads, L, D] whose slot `position` is overwritten by the
     new token's key / value; attention covers slots 0..position. Returns (out [B, hidden], k_cache, v_cache)."""
     b = x.shape[0]
     d = cfg.head_dim
-    hn = rms_norm(x, w["attention_norm"], cfg.eps)
-    q = (hn @ w["wq"].t()).view(b, cfg.heads, d)
-    k = (hn @ w["wk"].t()).view(b, cfg.kv_heads, d)
-    v = (hn @ w["wv"].t()).view(b, cfg.kv_heads, d)
+    hn = step(rms_norm(x, w["attention_norm"], cfg.eps))
+    q = step(hn @ w["wq"].t()).view(b, cfg.heads, d)
+    k = step(hn @ w["wk"].t()).view(b, cfg.kv_heads, d)
+    v = step(hn @ w["wv"].t()).view(b, cfg.kv_heads, d)
     cos, sin = rope_tables(d, torch.tensor([position]), cfg.rope_base)
-    q = rotary(cfg, q, cos, sin)
-    k = rotary(cfg, k, cos, sin)
+    q = step(rotary(cfg, q, cos, sin))
+    k = step(rotary(cfg, k, cos, sin))
     k_cache = k_cache.clone()
     v_cache = v_cache.clone()
     k_cache[:, :, position, :] = k
     v_cache[:, :, position, :] = v
     keys = _expand_kv(cfg, k_cache[:, :, : position + 1, :])
     vals = _expand_kv(cfg, v_cache[:, :, : position + 1, :])
-    scores = torch.matmul(q.unsqueeze(2), keys.transpose(2, 3)) / math.sqrt(d)  # [B, heads, 1, L]
-    probs = torch.softmax(scores.float(), dim=-1)
-    ctx = torch.matmul(probs, vals).reshape(b, cfg.heads * d)
-    h = x + ctx @ w["wo"].t()
-    out = h + feed_forward(w, rms_norm(h, w["ffn_norm"], cfg.eps))
+    scores = step(step(torch.matmul(q.unsqueeze(2), keys.transpose(2, 3))) / math.sqrt(d))  # [B, heads, 1, L]
+    probs = step(torch.softmax(scores.float(), dim=-1))
+    ctx = step(torch.matmul(probs, vals)).reshape(b, cfg.heads * d)
+    h = step(x + step(ctx @ w["wo"].t()))
+    out = step(h + feed_forward(w, step(rms_norm(h, w["ffn_norm"], cfg.eps)), step))
     return out, k_cache, v_cache
 
 
