@@ -22,6 +22,7 @@
 #include <mutex>
 
 #include "gemm.h"
+#include "diopi/functions_b200.h"
 #include "gemm_sm100.cuh"
 #include "device_utils.cuh"
 
