@@ -20,6 +20,8 @@ struct GemmProblem {
     diopiDtype_t c_dtype = diopi_dtype_unsupported;
     diopiDtype_t bias_dtype = diopi_dtype_unsupported;
     float alpha = 1.f, beta = 0.f;
+    // Status word to report into; nullptr = the per-device word the library allocates on first use.
+    uint32_t* status_override = nullptr;
 };
 
 // tcgen05 / TMEM / TMA kernel (bf16 or fp16 operands, fp32 accumulation).

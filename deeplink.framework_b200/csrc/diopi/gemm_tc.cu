@@ -394,7 +394,7 @@ diopiError_t gemm_tc_launch(const GemmProblem& g, cudaStream_t stream) {
     p.b_mn_major = b_mn ? 1 : 0;
     const int64_t c_es = dtype_size(g.c_dtype);
     p.c_vec_ok = ((reinterpret_cast<uintptr_t>(g.C) & 15u) == 0 && (g.c_sm * c_es) % 16 == 0 && (g.batch == 1 || (g.c_sb * c_es) % 16 == 0)) ? 1 : 0;
-    p.status = status_word();
+    p.status = g.status_override != nullptr ? g.status_override : status_word();
     B200_CHECK(p.status != nullptr, "gemm: could not allocate the kernel status word");
     const int64_t total = static_cast<int64_t>(p.batch) * m_blocks * n_blocks;
     const int grid = static_cast<int>(total < sms ? total : sms);
@@ -418,5 +418,79 @@ extern "C" DIOPI_API int diopiB200GemmStatus(void) {
     if (w == nullptr) return -1;
     uint32_t v = 0;
     if (cudaMemcpy(&v, w, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    return static_cast<int>(v);
+}
+
+// ---- matrix product that allocates nothing ---------------------------------------------------------------------------
+// The tensor-core kernel's only scratch is its status word. diopiMm keeps it in memory obtained with cudaMalloc on
+// first use; here it lives in a static block of the library image, so the entry point below never allocates.
+namespace {
+constexpr int kNoAllocScratchWords = 64;  // 256 bytes; word 0 is the status word, the rest is reserved
+static __device__ __align__(256) uint32_t g_noalloc_scratch[kNoAllocScratchWords];
+
+std::mutex g_noalloc_mu;
+uint32_t* g_noalloc_ptr[64] = {nullptr};
+
+// Device address of the static block on the current device. In host code the array's name is only a handle for the
+// runtime, not an address a kernel could use: the address has to be asked for, once per device.
+uint32_t* noalloc_scratch_ptr() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        (void)cudaGetLastError();
+        b200::set_last_error("diopiB200MmNoAlloc: cannot determine the current device");
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (g_noalloc_ptr[dev] == nullptr) {
+        uint32_t* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+        if (e != cudaSuccess || ptr == nullptr) {
+            (void)cudaGetLastError();
+            b200::set_last_error("diopiB200MmNoAlloc: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+            return nullptr;
+        }
+        g_noalloc_ptr[dev] = ptr;
+    }
+    return g_noalloc_ptr[dev];
+}
+}  // namespace
+
+extern "C" DIOPI_API diopiError_t diopiB200MmNoAlloc(diopiStreamHandle_t stream, void* out, const void* mat1, const void* mat2, int64_t m,
+                                                     int64_t n, int64_t k, int64_t ld1, int64_t ld2, int mat2_is_nk, int64_t ldo,
+                                                     diopiDtype_t dtype) {
+    using namespace b200;
+    B200_CHECK(out != nullptr && mat1 != nullptr && mat2 != nullptr, "diopiB200MmNoAlloc: NULL operand");
+    B200_CHECK(dtype == diopi_dtype_bfloat16 || dtype == diopi_dtype_float16, "diopiB200MmNoAlloc: dtype must be bfloat16 or float16, got %s",
+               dtype_name(dtype));
+    const int64_t lim = 0x7fffffffLL;
+    B200_CHECK(m >= 1 && n >= 1 && k >= 1 && m <= lim && n <= lim && k <= lim,
+               "diopiB200MmNoAlloc: dimensions must lie in [1, 2^31): got m=%lld n=%lld k=%lld", (long long)m, (long long)n, (long long)k);
+    GemmProblem g;
+    g.batch = 1; g.M = m; g.N = n; g.K = k;
+    g.A = mat1; g.a_sm = ld1; g.a_sk = 1;
+    g.B = mat2;
+    if (mat2_is_nk) { g.b_sn = ld2; g.b_sk = 1; } else { g.b_sk = ld2; g.b_sn = 1; }
+    g.C = out; g.c_sm = ldo; g.c_sn = 1;
+    g.ab_dtype = dtype; g.c_dtype = dtype;
+    B200_CHECK(gemm_tc_eligible(g),
+               "diopiB200MmNoAlloc: operands do not meet the tensor-core kernel's layout rules (16-byte aligned pointers, pitches that are "
+               "multiples of 8 elements and at least the row length); this entry point has no other path");
+    uint32_t* scratch = noalloc_scratch_ptr();
+    if (scratch == nullptr) return diopiErrorOccurred;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // the block keeps whatever the previous call left: the status word must start at zero
+    B200_CUDA(cudaMemsetAsync(scratch, 0, sizeof(uint32_t), s));
+    g.status_override = scratch;
+    return gemm_tc_launch(g, s);
+}
+
+extern "C" DIOPI_API int diopiB200NoAllocStatus(void) {
+    uint32_t* scratch = noalloc_scratch_ptr();
+    if (scratch == nullptr) return -1;
+    uint32_t v = 0;
+    if (cudaMemcpy(&v, scratch, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return -1;
+    }
     return static_cast<int>(v);
 }

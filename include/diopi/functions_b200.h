@@ -14,6 +14,32 @@ extern "C" {
  * device-side wait has ever timed out, 1 afterwards, -1 if it cannot be read. Synchronises the device. */
 DIOPI_API int diopiB200GemmStatus(void);
 
+/* No counterpart in the reference.
+ *
+ * Matrix product for callers that are not allowed to allocate device memory at the moment of the call: code running
+ * while a framework's allocator lock is held or inside an allocator callback, a host whose memory pool is frozen
+ * (fixed-budget serving processes), or a thread that must not enter the driver's allocation path. diopiMm obtains the
+ * tensor-core kernel's status word with cudaMalloc on first use; this variant keeps that scratch in a 256-byte
+ * static __device__ block inside the library instead (every GPU that loads the library holds those 256 bytes until
+ * exit) and calls no cudaMalloc / cudaFree / host-allocator routine.
+ *
+ *   out  [m, n]  row pitch ldo            (elements)
+ *   mat1 [m, k]  row pitch ld1, k contiguous
+ *   mat2 [n, k]  row pitch ld2 when mat2_is_nk != 0 (a weight in nn.Linear layout: out = mat1 * mat2^T),
+ *        [k, n]  row pitch ld2 otherwise
+ *   dtype: diopi_dtype_bfloat16 or diopi_dtype_float16 for all three; fp32 accumulation.
+ * Pointers must be 16-byte aligned and pitches multiples of 8 elements (the TMA rules); anything else, and any
+ * dimension outside [1, 2^31), is rejected with diopiErrorOccurred and a message, never served by another path.
+ * The scratch need of this kernel does not grow with the problem, so the static block is always enough.
+ *
+ * The first call on a device looks up the block's device address and sets a kernel attribute; make that first call
+ * before any stream capture. Every call clears the status word on `stream` before the kernel runs and all calls share
+ * the block, which keeps the last call's value: calls that overlap on the GPU (different streams) race on it, so
+ * serialise them. diopiB200NoAllocStatus() reads the word back (synchronises). */
+DIOPI_API diopiError_t diopiB200MmNoAlloc(diopiStreamHandle_t stream, void* out, const void* mat1, const void* mat2, int64_t m, int64_t n,
+                                          int64_t k, int64_t ld1, int64_t ld2, int mat2_is_nk, int64_t ldo, diopiDtype_t dtype);
+DIOPI_API int diopiB200NoAllocStatus(void);
+
 #ifdef __cplusplus
 }
 #endif

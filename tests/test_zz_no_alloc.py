@@ -1,0 +1,70 @@
+"""diopiB200MmNoAlloc: the matrix product for callers that may not allocate device memory when they call (code that runs
+under an allocator lock or inside an allocator callback, processes with a frozen memory pool). Its scratch - the
+tensor-core kernel's status word - sits in a static block of the library instead of memory from cudaMalloc.
+
+The entry point is called through the C-ABI with raw pointers, twice in a row, and each result is compared with what the
+regular entry point (diopiMm) writes for the same operands: the kernel is the same, so the outputs must be bit-identical;
+the result is also held to the bf16 tolerance of the other GEMM tests against fp32 CPU. The file name sorts last so that a
+run that stops at the first failure has already run every other test; the test needs nothing from earlier tests.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+BF16 = 12  # diopi_dtype_bfloat16
+
+
+def _rnd(shape, seed, scale=1.0):
+    rng = np.random.default_rng(seed)
+    return (torch.from_numpy(rng.standard_normal(size=shape, dtype=np.float32)) * scale).to(torch.bfloat16)
+
+
+def _bind(pkg):
+    lib = pkg._native.diopi
+    fn = lib.diopiB200MmNoAlloc
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                   ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int64, ctypes.c_int]
+    lib.diopiB200NoAllocStatus.restype = ctypes.c_int
+    return fn, lib.diopiB200NoAllocStatus
+
+
+def test_no_alloc_mm_matches_regular_entry_point_twice(pkg, diopi):
+    fn, status = _bind(pkg)
+    stream = torch.cuda.current_stream().cuda_stream
+    ctx = diopi.Context()
+    cases = [(300, 264, 136, True, 1), (1024, 512, 256, False, 2)]  # (m, n, k, weight layout [n, k]?, seed): two calls in a row
+    for m, n, k, nk, seed in cases:
+        a = _rnd((m, k), seed).to(DEV)
+        b = _rnd((n, k) if nk else (k, n), seed + 10, 0.05).to(DEV)
+        got = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+        rc = fn(stream, got.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, k, k if nk else n, 1 if nk else 0, n, BF16)
+        assert rc == 0, diopi.last_error()
+        want = torch.empty((m, n), dtype=torch.bfloat16, device=DEV)
+        diopi.diopiMm(ctx, want, a, b.t() if nk else b)
+        torch.cuda.synchronize()
+        assert status() == 0
+        assert torch.equal(got, want)
+        ref = a.float().cpu() @ (b.float().cpu().t() if nk else b.float().cpu())
+        g = got.float().cpu()
+        assert ((g - ref).norm() / ref.norm()).item() <= 5e-3
+        assert ((g - ref).abs().max() / ref.abs().max()).item() <= 2e-2
+
+
+def test_no_alloc_mm_rejects_what_it_cannot_serve(pkg, diopi):
+    fn, _ = _bind(pkg)
+    stream = torch.cuda.current_stream().cuda_stream
+    a = torch.zeros((64, 72), dtype=torch.bfloat16, device=DEV)
+    b = torch.zeros((64, 72), dtype=torch.bfloat16, device=DEV)
+    out = torch.zeros((64, 64), dtype=torch.bfloat16, device=DEV)
+    # pitch of 71 elements is not a multiple of 8
+    assert fn(stream, out.data_ptr(), a.data_ptr(), b.data_ptr(), 64, 64, 71, 71, 71, 1, 64, BF16) != 0
+    assert "layout rules" in diopi.last_error()
+    assert fn(stream, out.data_ptr(), a.data_ptr(), b.data_ptr(), 64, 64, 1 << 31, 72, 72, 1, 64, BF16) != 0
+    assert "2^31" in diopi.last_error()
+    assert fn(stream, out.data_ptr(), a.data_ptr(), b.data_ptr(), 64, 64, 72, 72, 72, 1, 64, 9) != 0  # fp32 is not served
+    assert fn(stream, None, a.data_ptr(), b.data_ptr(), 64, 64, 72, 72, 72, 1, 64, BF16) != 0
