@@ -46,53 +46,55 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clocks, power and throttle reasons through NVML (read-only queries) while the timed region runs."""
 
-    def __init__(self, gpu_index):
-        self.gpu_index = gpu_index
-        self.proc = None
-        self.lines = []
+    def __init__(self, gpu_index, period_s=0.02):
+        self.gpu_index, self.period_s = gpu_index, period_s
+        self.samples, self.power, self.reasons = [], [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self.thread = None
+        self.nvml = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
         except Exception:
-            self.proc = None
+            self.nvml = None
+            return
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+    def _run(self):
+        n = self.nvml
+        names = {"hw_slowdown": getattr(n, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(n, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(n, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(n, "nvmlClocksThrottleReasonSwPowerCap", 0x4)}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)))
+                self.power.append(n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0)
+                mask = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._stop.wait(self.period_s)
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()  # the exact process started above
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        sm, smax, reasons, power = [], None, set(), []
-        for ln in self.lines:
-            f = [x.strip() for x in ln.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                smax = float(f[2])
-                power.append(float(f[3]))
-            except ValueError:
-                continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm),
-                "power_w_max": max(power) if power else None}
+        if self.nvml is None or self.thread is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable"]}
+        self._stop.set()
+        self.thread.join(timeout=2)
+        sm = sorted(self.samples)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_min_mhz": sm[0] if sm else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(sm), "power_w_max": max(self.power) if self.power else None}
 
 
 def make_device_weights(cfg, device, dtype):
@@ -179,7 +181,7 @@ def cpu_baseline_leg():
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
@@ -232,7 +234,10 @@ def main():
     gi.manual_seed(SEED + 2)
     ids_host = torch.randint(0, VOCAB, (batch, seq), generator=gi, dtype=torch.int64).pin_memory()
     ids_dev = torch.empty((batch, seq), dtype=torch.int64, device=device)
-    out_host = torch.empty((tokens, cfg.hidden), dtype=dtype).pin_memory()
+    out_host = [torch.empty((tokens, cfg.hidden), dtype=dtype).pin_memory() for _ in range(2)]  # double-buffered results
+    copy_stream = devapis.getStreamFromPool(local_rank)   # D2H of step i overlaps the compute of step i+1
+    copy_events = [devapis.getEventFromPool(), devapis.getEventFromPool()]
+    done_events = [devapis.getEventFromPool(), devapis.getEventFromPool()]
 
     stream = torch.cuda.current_stream()
     ctx = diopi.Context(stream=stream.cuda_stream, device=local_rank)
@@ -253,11 +258,26 @@ def main():
     def step_resident():
         return lay.prefill(x, batch, seq, ctx)
 
+    e2e_state = {"i": 0}
+
     def step_e2e():
+        """Host buffers in, host buffers out. The result goes back on a pool stream, handed over with events the way DIPU's
+        non-blocking copies do; the allocator is told that the copy stream still reads the block (record_stream)."""
+        i = e2e_state["i"] & 1
+        e2e_state["i"] += 1
         devapis.memCopyH2DAsync(stream.cuda_stream, ids_host.numel() * 8, ids_dev.data_ptr(), ids_host.data_ptr())  # this step's input
         h = L.embed(table, ids_dev, ctx)
         y = lay.prefill(h, batch, seq, ctx)
-        devapis.memCopyD2HAsync(stream.cuda_stream, y.numel() * y.element_size(), out_host.data_ptr(), y.data_ptr())  # this step's result
+        devapis.recordEvent(copy_events[i], stream.cuda_stream)
+        devapis.streamWaitEvent(copy_stream, copy_events[i])
+        if e2e_state["i"] > 2:
+            devapis.waitEvent(done_events[i])  # the host buffer's previous copy (two steps back) has landed
+        devapis.memCopyD2HAsync(copy_stream, y.numel() * y.element_size(), out_host[i].data_ptr(), y.data_ptr())  # this step's result
+        devapis.recordEvent(done_events[i], copy_stream)
+        if not args.no_caching_allocator:
+            devapis.CachingAllocator.recordStream(y.data_ptr(), copy_stream)
+        else:
+            y.record_stream(torch.cuda.ExternalStream(copy_stream))
         return y
 
     # ---- device-resident timing ----
@@ -282,11 +302,16 @@ def main():
     for _ in range(2):
         step_e2e()
     barrier()
+    devapis.syncStream(copy_stream)
     e0.record(stream)
     for _ in range(args.steps):
         step_e2e()
+    # the timed region ends when the last result has landed in host memory
+    devapis.recordEvent(copy_events[0], copy_stream)
+    devapis.streamWaitEvent(stream.cuda_stream, copy_events[0])
     e1.record(stream)
     barrier()
+    devapis.syncStream(copy_stream)
     ms_e2e = max_over_ranks(e0.elapsed_time(e1))
 
     # ---- per-op device times: the same step with events around every DIOPI call ----
@@ -361,7 +386,8 @@ def main():
                        "parallelism": "tp%d" % world, "l2": "inputs larger than L2: weights 405 MB + >=134 MB per activation, no flush",
                        "allocator": "torch default" if args.no_caching_allocator else "b200 caching allocator (pluggable)"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": ids_host.numel() * 8,
-                    "d2h_bytes_per_step": out_host.numel() * out_host.element_size()},
+                    "d2h_bytes_per_step": out_host[0].numel() * out_host[0].element_size(),
+                    "note": "result copied back on a pool stream, overlapping the next step's compute"},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": roofline,

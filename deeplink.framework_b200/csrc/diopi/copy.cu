@@ -68,41 +68,66 @@ void launch_cast(const void* src, void* dst, int64_t numel, cudaStream_t stream)
 
 // ---- 3. strided copy of fixed-size words ---------------------------------------------------------------------
 struct WordIter {
-    int ndim;
-    int64_t nwords;
+    int ndim;            // outer dims (the dense inner run is not counted)
+    int64_t nrows;       // product of the outer dims
+    int64_t row_words;   // words per inner run
     int64_t shape[kMaxDims];
     int64_t sstride[kMaxDims];  // in words
     int64_t dstride[kMaxDims];
 };
 
-template <typename W>
+// The tensor is a set of dense inner runs ("rows") of row_words words each, placed by the outer strides. A group of
+// GROUP lanes walks one row; the outer index is decomposed once per row, not once per word. Each group keeps four rows
+// in flight.
+template <typename W, int GROUP>
 __global__ void __launch_bounds__(256) strided_word_copy_kernel(const W* __restrict__ src, W* __restrict__ dst, const WordIter it) {
-    constexpr int UNROLL = 4;
-    const int64_t tile = static_cast<int64_t>(blockDim.x) * UNROLL;
-    for (int64_t base = static_cast<int64_t>(blockIdx.x) * tile; base < it.nwords; base += static_cast<int64_t>(gridDim.x) * tile) {
-        W val[UNROLL];
-        int64_t doff[UNROLL];
+    constexpr int ROWS = 4;
+    const int lane = threadIdx.x % GROUP;
+    const int64_t group = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) / GROUP;
+    const int64_t row0 = group * ROWS;
+    int64_t so[ROWS], d_o[ROWS];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int64_t i = base + u * blockDim.x + threadIdx.x;
-            if (i < it.nwords) {
-                int64_t rem = i, so = 0, d_o = 0;
-                for (int d = it.ndim - 1; d >= 0; --d) {
-                    const int64_t q = rem / it.shape[d];
-                    const int64_t c = rem - q * it.shape[d];
-                    rem = q;
-                    so += c * it.sstride[d];
-                    d_o += c * it.dstride[d];
-                }
-                doff[u] = d_o;
-                val[u] = src[so];
-            }
+    for (int r = 0; r < ROWS; ++r) {
+        int64_t rem = row0 + r, s = 0, d = 0;
+        for (int k = it.ndim - 1; k >= 0; --k) {
+            const int64_t q = rem / it.shape[k];
+            const int64_t c = rem - q * it.shape[k];
+            rem = q;
+            s += c * it.sstride[k];
+            d += c * it.dstride[k];
+        }
+        so[r] = s;
+        d_o[r] = d;
+    }
+    for (int64_t w = lane; w < it.row_words; w += GROUP) {
+        W val[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            if (row0 + r < it.nrows) val[r] = src[so[r] + w];
         }
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int64_t i = base + u * blockDim.x + threadIdx.x;
-            if (i < it.nwords) dst[doff[u]] = val[u];
+        for (int r = 0; r < ROWS; ++r) {
+            if (row0 + r < it.nrows) dst[d_o[r] + w] = val[r];
         }
+    }
+}
+
+template <typename W>
+void launch_word_copy(const void* src, void* dst, const WordIter& wi, cudaStream_t stream) {
+    int group = 32;
+    while (group > 1 && group / 2 >= wi.row_words) group >>= 1;
+    const int64_t groups = (wi.nrows + 3) / 4;
+    const int64_t threads = groups * group;
+    const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
+    const W* s = static_cast<const W*>(src);
+    W* d = static_cast<W*>(dst);
+    switch (group) {
+        case 32: strided_word_copy_kernel<W, 32><<<grid, 256, 0, stream>>>(s, d, wi); break;
+        case 16: strided_word_copy_kernel<W, 16><<<grid, 256, 0, stream>>>(s, d, wi); break;
+        case 8: strided_word_copy_kernel<W, 8><<<grid, 256, 0, stream>>>(s, d, wi); break;
+        case 4: strided_word_copy_kernel<W, 4><<<grid, 256, 0, stream>>>(s, d, wi); break;
+        case 2: strided_word_copy_kernel<W, 2><<<grid, 256, 0, stream>>>(s, d, wi); break;
+        default: strided_word_copy_kernel<W, 1><<<grid, 256, 0, stream>>>(s, d, wi); break;
     }
 }
 
@@ -146,23 +171,22 @@ bool try_word_copy(const TensorView& src, const TensorView& dst, cudaStream_t st
     if (word < es) word = static_cast<int>(es);
     const int64_t epw = word / es;
     WordIter wi;
-    wi.ndim = it.ndim;
-    wi.nwords = it.numel / epw;
-    for (int d = 0; d < it.ndim; ++d) {
+    wi.ndim = last;
+    wi.row_words = it.shape[last] / epw;
+    wi.nrows = 1;
+    for (int d = 0; d < last; ++d) {
         wi.shape[d] = it.shape[d];
         wi.dstride[d] = it.stride[0][d] / epw;
         wi.sstride[d] = it.stride[1][d] / epw;
+        wi.nrows *= it.shape[d];
     }
-    wi.shape[last] = it.shape[last] / epw;
-    wi.dstride[last] = 1;
-    wi.sstride[last] = 1;
-    const int grid = ew_grid((wi.nwords + 3) / 4 + 1, 256);
+    if ((wi.nrows + 3) / 4 * 32 / 256 + 1 > 0x7fffffffLL) return false;
     switch (word) {
-        case 16: strided_word_copy_kernel<uint4><<<grid, 256, 0, stream>>>(static_cast<const uint4*>(src.data), static_cast<uint4*>(dst.data), wi); break;
-        case 8: strided_word_copy_kernel<uint2><<<grid, 256, 0, stream>>>(static_cast<const uint2*>(src.data), static_cast<uint2*>(dst.data), wi); break;
-        case 4: strided_word_copy_kernel<uint32_t><<<grid, 256, 0, stream>>>(static_cast<const uint32_t*>(src.data), static_cast<uint32_t*>(dst.data), wi); break;
-        case 2: strided_word_copy_kernel<uint16_t><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(src.data), static_cast<uint16_t*>(dst.data), wi); break;
-        default: strided_word_copy_kernel<uint8_t><<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(src.data), static_cast<uint8_t*>(dst.data), wi); break;
+        case 16: launch_word_copy<uint4>(src.data, dst.data, wi, stream); break;
+        case 8: launch_word_copy<uint2>(src.data, dst.data, wi, stream); break;
+        case 4: launch_word_copy<uint32_t>(src.data, dst.data, wi, stream); break;
+        case 2: launch_word_copy<uint16_t>(src.data, dst.data, wi, stream); break;
+        default: launch_word_copy<uint8_t>(src.data, dst.data, wi, stream); break;
     }
     return true;
 }

@@ -412,6 +412,13 @@ diopiError_t diopiDivScalar(diopiContextHandle_t ctx, diopiTensorHandle_t out, d
     B200_VIEW(vo, out);
     B200_VIEW(vi, input);
     B200_CHECK(other != nullptr, "diopiDivScalar: scalar operand is NULL");
+    // Two-byte float outputs: x / s is formed as x * (1 / s) in fp32 (as ATen's CUDA kernel does for a scalar divisor).
+    // The product differs from the quotient by at most one fp32 ulp, far below the output's own rounding step, and the
+    // multiply keeps the kernel at the memory roofline. fp32 / fp64 / integer outputs use true division.
+    if (rounding_mode == RoundModeNone && (vo.dtype == diopi_dtype_bfloat16 || vo.dtype == diopi_dtype_float16) && vi.dtype == vo.dtype &&
+        scalar_f(other) != 0.0) {
+        return affine(ctx, "diopiDivScalar", vo, vi, 1.0 / scalar_f(other), 0, 0.0, 0);
+    }
     ScalarArgs sa;
     sa.f[0] = scalar_f(other); sa.i[0] = scalar_i(other); sa.i[1] = rounding_mode;
     const TensorView* ins[1] = {&vi};

@@ -146,55 +146,83 @@ __global__ void __launch_bounds__(256) ew_generic_kernel(const EwIter<NIN + 1> i
 // period[a]: number of 16-byte vectors after which input a repeats (0 = same length as the output).
 struct VecPeriods {
     int64_t period[3];
+    int narrow;  // every vector index fits 32 bits: the repeat index is then a 32-bit remainder (a 64-bit one costs ~10x more)
 };
 
-template <typename T, int NIN, typename Op>
-__global__ void __launch_bounds__(256) ew_vec_kernel(T* out, const T* a0, const T* a1, const T* a2, int64_t numel,
-                                                     const VecPeriods per, const Op op) {
+// One CTA = one tile of 256 threads x 4 vectors (16 KiB per operand); all loads of a thread are issued before the first
+// use. BCAST = false: every input is as long as the output (no index arithmetic beyond the tile offset).
+template <typename T, int NIN, bool BCAST, typename Op>
+__global__ void __launch_bounds__(256, 4) ew_vec_kernel(T* out, const T* a0, const T* a1, const T* a2, int64_t numel, const VecPeriods per,
+                                                        const Op op) {
     constexpr int V = Vec16<T>::N;
     constexpr int UNROLL = 4;
     const int64_t nvec = numel / V;
-    const int64_t tile = static_cast<int64_t>(blockDim.x) * UNROLL;
     const T* ins[3] = {a0, a1, a2};
-    for (int64_t base = static_cast<int64_t>(blockIdx.x) * tile; base < nvec; base += static_cast<int64_t>(gridDim.x) * tile) {
-        Vec16<T> x[NIN > 0 ? NIN : 1][UNROLL];
+    const int64_t base = static_cast<int64_t>(blockIdx.x) * (256 * UNROLL) + threadIdx.x;
+    // A repeating input is indexed by (vector index mod period). One remainder per thread and input; the other three
+    // vectors of the thread sit 256 vectors further on each, so their index follows by addition and a conditional wrap.
+    int64_t rep[NIN > 0 ? NIN : 1];
+    if constexpr (BCAST) {
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int64_t iv = base + u * blockDim.x + threadIdx.x;
-            if (iv < nvec) {
-#pragma unroll
-                for (int a = 0; a < NIN; ++a) {
-                    if (per.period[a] == 0) x[a][u] = ld16_stream(ins[a] + iv * V);
-                    else x[a][u] = ld16(ins[a] + (iv % per.period[a]) * V);
-                }
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int64_t iv = base + u * blockDim.x + threadIdx.x;
-            if (iv < nvec) {
-                Vec16<T> r;
-#pragma unroll
-                for (int e = 0; e < V; ++e) {
-                    float y;
-                    if constexpr (NIN == 0) y = op();
-                    else if constexpr (NIN == 1) y = op(to_f32(x[0][u].v[e]));
-                    else if constexpr (NIN == 2) y = op(to_f32(x[0][u].v[e]), to_f32(x[1][u].v[e]));
-                    else y = op(to_f32(x[0][u].v[e]), to_f32(x[1][u].v[e]), to_f32(x[2][u].v[e]));
-                    r.v[e] = from_f32<T>(y);
-                }
-                st16_stream(out + iv * V, r);
+        for (int a = 0; a < NIN; ++a) {
+            rep[a] = 0;
+            if (per.period[a] != 0) {
+                rep[a] = per.narrow ? static_cast<int64_t>(static_cast<uint32_t>(base) % static_cast<uint32_t>(per.period[a])) : base % per.period[a];
             }
         }
     }
+    Vec16<T> x[NIN > 0 ? NIN : 1][UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        const int64_t iv = base + u * 256;
+        if (iv < nvec) {
+#pragma unroll
+            for (int a = 0; a < NIN; ++a) {
+                if (!BCAST || per.period[a] == 0) {
+                    x[a][u] = ld16_stream(ins[a] + iv * V);
+                } else {
+                    x[a][u] = ld16(ins[a] + rep[a] * V);
+                }
+            }
+        }
+        if constexpr (BCAST) {
+#pragma unroll
+            for (int a = 0; a < NIN; ++a) {
+                if (per.period[a] != 0) {
+                    rep[a] += 256;
+                    if (per.period[a] >= 256) {
+                        if (rep[a] >= per.period[a]) rep[a] -= per.period[a];
+                    } else {
+                        rep[a] %= per.period[a];  // short rows (fewer than 256 vectors): rare, small
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        const int64_t iv = base + u * 256;
+        if (iv < nvec) {
+            Vec16<T> r;
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                float y;
+                if constexpr (NIN == 0) y = op();
+                else if constexpr (NIN == 1) y = op(to_f32(x[0][u].v[e]));
+                else if constexpr (NIN == 2) y = op(to_f32(x[0][u].v[e]), to_f32(x[1][u].v[e]));
+                else y = op(to_f32(x[0][u].v[e]), to_f32(x[1][u].v[e]), to_f32(x[2][u].v[e]));
+                r.v[e] = from_f32<T>(y);
+            }
+            st16_stream(out + iv * V, r);
+        }
+    }
     // ragged tail (numel not a multiple of the vector width): one thread per element
-    const int64_t tail0 = nvec * V;
     if (blockIdx.x == 0) {
-        for (int64_t i = tail0 + threadIdx.x; i < numel; i += blockDim.x) {
+        for (int64_t i = nvec * V + threadIdx.x; i < numel; i += blockDim.x) {
             float in[3] = {0.f, 0.f, 0.f};
 #pragma unroll
             for (int a = 0; a < NIN; ++a) {
-                const int64_t j = per.period[a] == 0 ? i : i % (per.period[a] * V);
+                const int64_t j = (!BCAST || per.period[a] == 0) ? i : i % (per.period[a] * V);
                 in[a] = to_f32(ins[a][j]);
             }
             float y;
@@ -205,6 +233,83 @@ __global__ void __launch_bounds__(256) ew_vec_kernel(T* out, const T* a0, const 
             out[i] = from_f32<T>(y);
         }
     }
+}
+
+// Binary op whose input `REP` is a dense block that repeats along the leading dimensions (a [S, S] mask added to
+// [B*H, S, S] scores). A CTA owns one 1024-vector tile of the block, keeps it in registers and streams the matching tile of
+// every repetition through it, so the repeating operand is read once in total instead of once per repetition (and the L2
+// carries only the streaming operand). gridDim.y splits the repetitions.
+template <typename T, int REP, typename Op>
+__global__ void __launch_bounds__(256, 4) ew_repeat_kernel(T* out, const T* dense, const T* block, int64_t period, int64_t reps, const Op op) {
+    constexpr int V = Vec16<T>::N;
+    constexpr int UNROLL = 4;
+    const int64_t tile0 = static_cast<int64_t>(blockIdx.x) * (256 * UNROLL) + threadIdx.x;
+    Vec16<T> blk[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        const int64_t iv = tile0 + u * 256;
+        if (iv < period) blk[u] = ld16(block + iv * V);
+    }
+    const int64_t per_y = (reps + gridDim.y - 1) / gridDim.y;
+    const int64_t r0 = static_cast<int64_t>(blockIdx.y) * per_y;
+    const int64_t r1 = r0 + per_y < reps ? r0 + per_y : reps;
+    for (int64_t r = r0; r < r1; ++r) {
+        const int64_t base = r * period;
+        Vec16<T> x[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int64_t iv = tile0 + u * 256;
+            if (iv < period) x[u] = ld16_stream(dense + (base + iv) * V);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int64_t iv = tile0 + u * 256;
+            if (iv < period) {
+                Vec16<T> y;
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    const float a = to_f32(x[u].v[e]), b = to_f32(blk[u].v[e]);
+                    y.v[e] = from_f32<T>(REP == 1 ? op(a, b) : op(b, a));
+                }
+                st16_stream(out + (base + iv) * V, y);
+            }
+        }
+    }
+}
+
+template <typename T, int NIN, typename Op>
+void launch_vec(const TensorView& out, const void* const* p, const VecPeriods& per, const Op& op, cudaStream_t stream) {
+    constexpr int V = Vec16<T>::N;
+    const int64_t nvec = out.numel / V;
+    if constexpr (NIN == 2) {
+        // exactly one repeating input, at least one full tile long, whole vectors only
+        const int rep = (per.period[0] != 0 && per.period[1] == 0) ? 0 : ((per.period[1] != 0 && per.period[0] == 0) ? 1 : -1);
+        if (rep >= 0 && per.period[rep] >= 1024 && out.numel % V == 0 && nvec % per.period[rep] == 0) {
+            const int64_t period = per.period[rep], reps = nvec / period;
+            const int64_t tiles = (period + 1023) / 1024;
+            int64_t ysplit = (static_cast<int64_t>(sm_count()) * 8 + tiles - 1) / tiles;  // about eight CTAs per SM in total
+            if (ysplit > reps) ysplit = reps;
+            if (ysplit > 65535) ysplit = 65535;
+            if (ysplit < 1) ysplit = 1;
+            if (tiles <= 0x7fffffffLL) {
+                dim3 grid(static_cast<unsigned>(tiles), static_cast<unsigned>(ysplit));
+                T* o = static_cast<T*>(out.data);
+                if (rep == 1) ew_repeat_kernel<T, 1, Op><<<grid, 256, 0, stream>>>(o, static_cast<const T*>(p[0]), static_cast<const T*>(p[1]), period, reps, op);
+                else ew_repeat_kernel<T, 0, Op><<<grid, 256, 0, stream>>>(o, static_cast<const T*>(p[1]), static_cast<const T*>(p[0]), period, reps, op);
+                return;
+            }
+        }
+    }
+    int64_t blocks = (nvec + 1023) / 1024;
+    if (blocks < 1) blocks = 1;
+    const unsigned grid = static_cast<unsigned>(blocks);
+    const bool bcast = per.period[0] != 0 || per.period[1] != 0 || per.period[2] != 0;
+    T* o = static_cast<T*>(out.data);
+    const T* a0 = static_cast<const T*>(p[0]);
+    const T* a1 = static_cast<const T*>(p[1]);
+    const T* a2 = static_cast<const T*>(p[2]);
+    if (bcast) ew_vec_kernel<T, NIN, true, Op><<<grid, 256, 0, stream>>>(o, a0, a1, a2, out.numel, per, op);
+    else ew_vec_kernel<T, NIN, false, Op><<<grid, 256, 0, stream>>>(o, a0, a1, a2, out.numel, per, op);
 }
 
 // Does `in` qualify for the vector kernel against the dense output `out`? Fills the repeat period.
@@ -262,29 +367,19 @@ diopiError_t launch_elementwise(diopiContextHandle_t ctx, const char* name, cons
     const bool vec_dtype = out.dtype == diopi_dtype_bfloat16 || out.dtype == diopi_dtype_float16 || out.dtype == diopi_dtype_float32;
     if (allow_vec && vec_dtype && out.is_contiguous() && out.aligned(16)) {
         const int vec_elems = 16 / static_cast<int>(out.itemsize);
-        VecPeriods per{{0, 0, 0}};
+        VecPeriods per{{0, 0, 0}, 0};
         bool ok = true;
         for (int a = 0; a < NIN && ok; ++a) ok = vec_operand_ok(out, *ins[a], vec_elems, &per.period[a]);
         if (ok) {
             const int64_t nvec = out.numel / vec_elems;
-            const int threads = 256;
-            const int grid = ew_grid((nvec + 3) / 4 + 1, threads);
+            per.narrow = nvec < 0xffffffffLL ? 1 : 0;
+            B200_CHECK((nvec + 1023) / 1024 <= 0x7fffffffLL, "%s: tensor too large", name);
             const void* p[3] = {nullptr, nullptr, nullptr};
             for (int a = 0; a < NIN; ++a) p[a] = ins[a]->data;
             OpT<float> op(sargs);
-            if (out.dtype == diopi_dtype_bfloat16) {
-                ew_vec_kernel<bf16, NIN, OpT<float>><<<grid, threads, 0, stream>>>(static_cast<bf16*>(out.data), static_cast<const bf16*>(p[0]),
-                                                                                  static_cast<const bf16*>(p[1]), static_cast<const bf16*>(p[2]),
-                                                                                  out.numel, per, op);
-            } else if (out.dtype == diopi_dtype_float16) {
-                ew_vec_kernel<fp16, NIN, OpT<float>><<<grid, threads, 0, stream>>>(static_cast<fp16*>(out.data), static_cast<const fp16*>(p[0]),
-                                                                                  static_cast<const fp16*>(p[1]), static_cast<const fp16*>(p[2]),
-                                                                                  out.numel, per, op);
-            } else {
-                ew_vec_kernel<float, NIN, OpT<float>><<<grid, threads, 0, stream>>>(static_cast<float*>(out.data), static_cast<const float*>(p[0]),
-                                                                                   static_cast<const float*>(p[1]), static_cast<const float*>(p[2]),
-                                                                                   out.numel, per, op);
-            }
+            if (out.dtype == diopi_dtype_bfloat16) launch_vec<bf16, NIN, OpT<float>>(out, p, per, op, stream);
+            else if (out.dtype == diopi_dtype_float16) launch_vec<fp16, NIN, OpT<float>>(out, p, per, op, stream);
+            else launch_vec<float, NIN, OpT<float>>(out, p, per, op, stream);
             B200_LAUNCH_CHECK(name);
             return diopiSuccess;
         }

@@ -7,7 +7,9 @@
 //                                memory; two accumulators of BN columns each are double-buffered so the epilogue of
 //                                tile i overlaps the main loop of tile i+1
 //   warps 2..5  epilogue       - tcgen05.ld the accumulator (each warp its own 32-lane quarter), scale / add bias,
-//                                convert and store 16-byte vectors straight to global memory
+//                                convert, stage 32 x 128-byte pieces in swizzled shared memory and write them with TMA
+//                                stores (full 128-byte lines per row, ragged edges clipped by the hardware); outputs whose
+//                                pitch or base is not 16-byte aligned are stored straight from registers instead
 // Stages and accumulators are handed over with mbarriers; every wait is bounded (see gemm_sm100.cuh) and a
 // time-out is reported through the status word instead of hanging.
 //
@@ -43,10 +45,11 @@ struct TileCfg {
     static constexpr int kABytes = BM * BK * 2;
     static constexpr int kBBytes = BN * BK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStagesRaw = (kSmemLimit - 2048) / kStageBytes;
+    static constexpr int kStoreBytes = 4 /*warps*/ * 2 /*buffers*/ * 32 /*rows*/ * 128 /*bytes*/;  // epilogue staging
+    static constexpr int kStagesRaw = (kSmemLimit - 1024 - 512 - kStoreBytes) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
     static constexpr int kTmemCols = (2 * BN) < 32 ? 32 : (2 * BN);
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
 
 struct TcParams {
@@ -60,6 +63,7 @@ struct TcParams {
     uint32_t idesc;
     int b_mn_major;
     int c_vec_ok;
+    int tma_store;  // epilogue writes through map_c
     uint32_t* status;
 };
 
@@ -109,7 +113,8 @@ __device__ __forceinline__ void store_chunk(const TcParams& p, const uint32_t (&
 
 template <int BN, typename TOut>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
+               const TcParams p) {
     using Cfg = TileCfg<BN>;
     constexpr int STAGES = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -117,7 +122,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + STAGES * Cfg::kABytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::kStageBytes);
+    uint8_t* smem_c = smem + STAGES * Cfg::kStageBytes;  // [4 warps][2 buffers][32 rows x 128 bytes], 1024-byte aligned
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_c + Cfg::kStoreBytes);
     uint64_t* full_bar = bars;                     // [STAGES] producer -> MMA
     uint64_t* empty_bar = bars + STAGES;           // [STAGES] MMA -> producer
     uint64_t* acc_full = bars + 2 * STAGES;        // [2] MMA -> epilogue
@@ -143,6 +149,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         fence_proxy_async();
         prefetch_tensormap(&map_a);
         prefetch_tensormap(&map_b);
+        if (p.tma_store) prefetch_tensormap(&map_c);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, Cfg::kTmemCols);
@@ -216,6 +223,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ---------------- epilogue (warps 2..5) ----------------
         const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are the ones this warp may read
         int local = 0;
+        uint32_t store_seq = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
             int b, mb, nb;
@@ -226,19 +234,72 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after();
             const int row = mb * BM + quarter * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+            if (p.tma_store) {
+                // One piece = 32 rows x 128 bytes (64 two-byte or 32 four-byte columns), double-buffered per warp.
+                constexpr int PIECE_COLS = 128 / static_cast<int>(sizeof(TOut));
+                constexpr int LOADS = PIECE_COLS / 32;
+                uint8_t* stage_base = smem_c + (warp - 2) * (2 * 32 * 128);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                const int col0 = nb * BN + c * 32;
-                if (col0 >= p.N) break;  // warp-uniform
-                uint32_t r[32];
-                tmem_ld_32x32(t_row + c * 32, r);
-                tmem_ld_wait();
-                store_chunk<TOut>(p, r, b, row, col0);
+                for (int c = 0; c < BN / PIECE_COLS; ++c) {
+                    const int col0 = nb * BN + c * PIECE_COLS;
+                    if (col0 >= p.N) break;  // warp-uniform
+                    uint8_t* buf = stage_base + (store_seq & 1) * (32 * 128);
+                    // the store issued from this buffer two pieces ago must have finished reading it
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
+#pragma unroll
+                    for (int l = 0; l < LOADS; ++l) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(t_row + c * PIECE_COLS + l * 32, r);
+                        tmem_ld_wait();
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+                        if (p.bias != nullptr && row < p.M) {
+                            const TOut* brow = static_cast<const TOut*>(p.bias) + static_cast<int64_t>(b) * p.bias_sb + static_cast<int64_t>(row) * p.bias_sr;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const int col = col0 + l * 32 + j;
+                                if (col < p.N) v[j] += p.beta * to_f32(brow[static_cast<int64_t>(col) * p.bias_sc]);
+                            }
+                        }
+                        // 16-byte chunk k of row `lane` lives at chunk position k ^ (lane & 7): the 128-byte swizzle the
+                        // store's tensor map expects, and conflict-free for the warp's writes
+                        constexpr int V = 16 / static_cast<int>(sizeof(TOut));
+#pragma unroll
+                        for (int j = 0; j < 32; j += V) {
+                            Vec16<TOut> o;
+#pragma unroll
+                            for (int e = 0; e < V; ++e) o.v[e] = from_f32<TOut>(v[j + e]);
+                            const int chunk = (l * 32 + j) / V;
+                            *reinterpret_cast<uint4*>(buf + lane * 128 + ((chunk ^ (lane & 7)) * 16)) = *reinterpret_cast<const uint4*>(&o);
+                        }
+                    }
+                    fence_proxy_async();  // make the generic-proxy writes visible to the bulk copy engine
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_3d(&map_c, buf, col0, mb * BM + quarter * 32, b);
+                        tma_store_commit();
+                    }
+                    ++store_seq;
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    const int col0 = nb * BN + c * 32;
+                    if (col0 >= p.N) break;  // warp-uniform
+                    uint32_t r[32];
+                    tmem_ld_32x32(t_row + c * 32, r);
+                    tmem_ld_wait();
+                    store_chunk<TOut>(p, r, b, row, col0);
+                }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[acc]);
         }
+        // all stores of this warp must be complete before the CTA's shared memory goes away
+        if (p.tma_store && lane == 0) tma_store_wait_all<0>();
     }
 
     // ---------------- teardown ----------------
@@ -277,18 +338,20 @@ EncodeFn get_encode_fn() {
     return fn;
 }
 
-// 3-D map over [batch, rows, inner] with a [1, box_rows, 64] box and 128-byte swizzle.
-bool encode_map(CUtensorMap* map, bool is_bf16, const void* base, int64_t inner, int64_t rows, int64_t batch, int64_t row_pitch_elems,
+// 3-D map over [batch, rows, inner] with a [1, box_rows, 128 bytes] box and 128-byte swizzle.
+bool encode_map(CUtensorMap* map, diopiDtype_t dtype, const void* base, int64_t inner, int64_t rows, int64_t batch, int64_t row_pitch_elems,
                 int64_t batch_pitch_elems, int box_rows) {
     EncodeFn fn = get_encode_fn();
     if (fn == nullptr) return false;
+    const int es = dtype == diopi_dtype_float32 ? 4 : 2;
+    const CUtensorMapDataType dt = dtype == diopi_dtype_float32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                   : (dtype == diopi_dtype_bfloat16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
     const cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(batch)};
-    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_pitch_elems * 2), static_cast<cuuint64_t>(batch_pitch_elems * 2)};
-    const cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(box_rows), 1u};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_pitch_elems * es), static_cast<cuuint64_t>(batch_pitch_elems * es)};
+    const cuuint32_t box[3] = {static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(box_rows), 1u};
     const cuuint32_t estr[3] = {1u, 1u, 1u};
-    const CUresult r = fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides,
-                          box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult r = fn(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
 
@@ -309,7 +372,7 @@ uint32_t* status_word() {
 }
 
 template <int BN, typename TOut>
-cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int grid, cudaStream_t stream) {
+cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const TcParams& p, int grid, cudaStream_t stream) {
     using Cfg = TileCfg<BN>;
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -319,17 +382,18 @@ cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcPara
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    gemm_tc_kernel<BN, TOut><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(ma, mb, p);
+    gemm_tc_kernel<BN, TOut><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(ma, mb, mc, p);
     return cudaPeekAtLastError();
 }
 
 template <typename TOut>
-cudaError_t launch_tc_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int grid, cudaStream_t stream) {
+cudaError_t launch_tc_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const TcParams& p, int grid,
+                         cudaStream_t stream) {
     switch (bn) {
-        case 256: return launch_tc<256, TOut>(ma, mb, p, grid, stream);
-        case 128: return launch_tc<128, TOut>(ma, mb, p, grid, stream);
-        case 64: return launch_tc<64, TOut>(ma, mb, p, grid, stream);
-        default: return launch_tc<32, TOut>(ma, mb, p, grid, stream);
+        case 256: return launch_tc<256, TOut>(ma, mb, mc, p, grid, stream);
+        case 128: return launch_tc<128, TOut>(ma, mb, mc, p, grid, stream);
+        case 64: return launch_tc<64, TOut>(ma, mb, mc, p, grid, stream);
+        default: return launch_tc<32, TOut>(ma, mb, mc, p, grid, stream);
     }
 }
 
@@ -374,14 +438,14 @@ diopiError_t gemm_tc_launch(const GemmProblem& g, cudaStream_t stream) {
     while (bn > min_bn && (g.N <= bn / 2 || g.batch * m_blocks * ((g.N + bn - 1) / bn) < sms)) bn >>= 1;
     const int64_t n_blocks = (g.N + bn - 1) / bn;
 
-    CUtensorMap ma, mb;
-    B200_CHECK(encode_map(&ma, is_bf16, g.A, g.K, g.M, g.batch, g.a_sm, g.batch > 1 ? g.a_sb : g.a_sm * g.M, BM),
+    CUtensorMap ma, mb, mc;
+    B200_CHECK(encode_map(&ma, g.ab_dtype, g.A, g.K, g.M, g.batch, g.a_sm, g.batch > 1 ? g.a_sb : g.a_sm * g.M, BM),
                "gemm: cuTensorMapEncodeTiled failed for A");
     if (!b_mn) {
-        B200_CHECK(encode_map(&mb, is_bf16, g.B, g.K, g.N, g.batch, g.b_sn, g.batch > 1 ? g.b_sb : g.b_sn * g.N, bn),
+        B200_CHECK(encode_map(&mb, g.ab_dtype, g.B, g.K, g.N, g.batch, g.b_sn, g.batch > 1 ? g.b_sb : g.b_sn * g.N, bn),
                    "gemm: cuTensorMapEncodeTiled failed for B (K-major)");
     } else {
-        B200_CHECK(encode_map(&mb, is_bf16, g.B, g.N, g.K, g.batch, g.b_sk, g.batch > 1 ? g.b_sb : g.b_sk * g.K, BK),
+        B200_CHECK(encode_map(&mb, g.ab_dtype, g.B, g.N, g.K, g.batch, g.b_sk, g.batch > 1 ? g.b_sb : g.b_sk * g.K, BK),
                    "gemm: cuTensorMapEncodeTiled failed for B (MN-major)");
     }
     TcParams p;
@@ -394,14 +458,20 @@ diopiError_t gemm_tc_launch(const GemmProblem& g, cudaStream_t stream) {
     p.b_mn_major = b_mn ? 1 : 0;
     const int64_t c_es = dtype_size(g.c_dtype);
     p.c_vec_ok = ((reinterpret_cast<uintptr_t>(g.C) & 15u) == 0 && (g.c_sm * c_es) % 16 == 0 && (g.batch == 1 || (g.c_sb * c_es) % 16 == 0)) ? 1 : 0;
+    // TMA-store epilogue whenever the output obeys the 16-byte rules; the map is encoded even when unused (kernel parameter)
+    p.tma_store = (p.c_vec_ok && bn * c_es >= 128) ? 1 : 0;  // a piece is 128 bytes wide: narrower tiles store from registers
+    if (p.tma_store) {
+        p.tma_store = encode_map(&mc, g.c_dtype, g.C, g.N, g.M, g.batch, g.c_sm, g.batch > 1 ? g.c_sb : g.c_sm * g.M, 32) ? 1 : 0;
+    }
+    if (!p.tma_store) mc = ma;
     p.status = g.status_override != nullptr ? g.status_override : status_word();
     B200_CHECK(p.status != nullptr, "gemm: could not allocate the kernel status word");
     const int64_t total = static_cast<int64_t>(p.batch) * m_blocks * n_blocks;
     const int grid = static_cast<int>(total < sms ? total : sms);
     cudaError_t e;
-    if (g.c_dtype == diopi_dtype_bfloat16) e = launch_tc_bn<bf16>(bn, ma, mb, p, grid, stream);
-    else if (g.c_dtype == diopi_dtype_float16) e = launch_tc_bn<fp16>(bn, ma, mb, p, grid, stream);
-    else e = launch_tc_bn<float>(bn, ma, mb, p, grid, stream);
+    if (g.c_dtype == diopi_dtype_bfloat16) e = launch_tc_bn<bf16>(bn, ma, mb, mc, p, grid, stream);
+    else if (g.c_dtype == diopi_dtype_float16) e = launch_tc_bn<fp16>(bn, ma, mb, mc, p, grid, stream);
+    else e = launch_tc_bn<float>(bn, ma, mb, mc, p, grid, stream);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
         B200_FAIL("gemm: tcgen05 kernel launch failed: %s", cudaGetErrorString(e));

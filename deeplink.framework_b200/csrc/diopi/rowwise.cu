@@ -186,7 +186,8 @@ __global__ void __launch_bounds__(1024) softmax_row_kernel(const T* __restrict__
     for (int i = 0; i < VPT; ++i) {
 #pragma unroll
         for (int e = 0; e < V; ++e) {
-            f[i][e] = expf(f[i][e] - m);
+            // two-byte outputs round to 8 or 11 bits: the 2-ulp fast exponential is far inside that
+            f[i][e] = (sizeof(T) == 2) ? __expf(f[i][e] - m) : expf(f[i][e] - m);
             s += (static_cast<int64_t>(i) * blockDim.x + threadIdx.x < nvec) ? f[i][e] : 0.f;
         }
     }

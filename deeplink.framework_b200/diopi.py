@@ -72,7 +72,7 @@ class Handle:
 
     __slots__ = ("tensor", "ptr")
 
-    def __init__(self, t):
+    def __init__(self, t, keep=True):
         if t.dtype not in DTYPE:
             raise DiopiError("dtype %s has no diopi counterpart" % t.dtype)
         nd = t.dim()
@@ -80,7 +80,7 @@ class Handle:
         stride = (ctypes.c_int64 * max(nd, 1))(*t.stride())
         dev = diopi_device if t.is_cuda else diopi_host
         idx = t.device.index if t.is_cuda else 0
-        self.tensor = t
+        self.tensor = t if keep else None
         self.ptr = _host.minihostMakeTensor(ctypes.c_void_p(t.data_ptr()), nd, shape, stride, DTYPE[t.dtype], dev, idx or 0)
         if not self.ptr:
             raise DiopiError("could not create a tensor handle")
@@ -91,8 +91,23 @@ class Handle:
             self.ptr = None
 
 
+_HANDLE_CACHE = {}
+
+
 def handle(t):
-    return t if isinstance(t, Handle) else Handle(t)
+    """Handle for a torch tensor. Handles are pure metadata (pointer, shape, strides, dtype, device), so one is kept per
+    distinct description and re-used: with a caching allocator a steady-state loop sees the same descriptions every step.
+    Cached handles do not keep the tensor alive; the caller's reference does for the duration of the call."""
+    if isinstance(t, Handle):
+        return t
+    key = (t.data_ptr(), t.dtype, tuple(t.shape), t.stride(), t.device.index if t.is_cuda else -1)
+    h = _HANDLE_CACHE.get(key)
+    if h is None:
+        if len(_HANDLE_CACHE) >= 8192:
+            _HANDLE_CACHE.clear()
+        h = Handle(t, keep=False)
+        _HANDLE_CACHE[key] = h
+    return h
 
 
 class Context:

@@ -1,0 +1,240 @@
+"""Per-op sweep on one GPU: achieved HBM GB/s of the memory-bound DIOPI ops and TFLOP/s of the dense contractions.
+
+    python deeplink.framework_b200/opsweep.py                       # the whole sweep, one JSON line per case
+    python deeplink.framework_b200/opsweep.py --ops rmsnorm --tokens 16384 --iters 5    # one case (e.g. under a profiler)
+
+Memory-bound ops run on bf16 [T, 4096] tensors, T in {1, 64, 1024, 16384, 65536}, values N(0,1); the embedding gathers
+int64 ids uniform in [0, 32000) from a [32000, 4096] bf16 table. Each case cycles through enough distinct buffer sets that
+the working set exceeds the 126 MB L2, and is timed with CUDA events on the launching stream after warm-up. GB/s uses
+the algorithmic bytes of the op (stated per case in the output), the fraction is against the measured copy bandwidth in
+MEASURED_PEAKS.json when that file is present. GEMM cases are the layer's shapes (prefill and decode).
+"""
+import argparse
+import json
+import math
+import os
+import sys
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+sys.path.insert(0, ROOT)
+
+H = 4096
+L2_BYTES = 126 << 20
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def time_cases(fn_list, iters, stream):
+    """fn_list: one closure per buffer set; returns mean milliseconds per call."""
+    n = len(fn_list)
+    for i in range(max(3, min(n, 8))):
+        fn_list[i % n]()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(iters):
+        fn_list[i % n]()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def nsets(bytes_per_set):
+    return int(max(2, min(64, math.ceil(2.0 * L2_BYTES / max(bytes_per_set, 1)))))
+
+
+def mem_case(name, t, diopi, ctx, dev):
+    bf = torch.bfloat16
+    g = torch.Generator(device=dev)
+    g.manual_seed(t)
+
+    def rn(*shape, dtype=bf):
+        return torch.randn(shape, generator=g, device=dev, dtype=torch.float32).to(dtype)
+
+    n = t * H
+    es = 2
+    if name == "rmsnorm":
+        alg = 2 * es * n + es * H
+        k = nsets(alg)
+        w = rn(H)
+        xs, ys = [rn(t, H) for _ in range(k)], [torch.empty((t, H), dtype=bf, device=dev) for _ in range(k)]
+        fns = [lambda i=i: diopi.diopiRMSNorm(ctx, ys[i], None, xs[i], [H], w, None, 1e-6) for i in range(k)]
+    elif name == "layernorm":
+        alg = 2 * es * n + 2 * es * H + 2 * es * t
+        k = nsets(alg)
+        w, b = rn(H), rn(H)
+        xs, ys = [rn(t, H) for _ in range(k)], [torch.empty((t, H), dtype=bf, device=dev) for _ in range(k)]
+        ms, rs = torch.empty((t, 1), dtype=bf, device=dev), torch.empty((t, 1), dtype=bf, device=dev)
+        fns = [lambda i=i: diopi.diopiLayerNorm(ctx, ys[i], ms, rs, xs[i], w, b, [H], 1e-5) for i in range(k)]
+    elif name == "softmax":
+        alg = 2 * es * n
+        k = nsets(alg)
+        xs, ys = [rn(t, H) for _ in range(k)], [torch.empty((t, H), dtype=bf, device=dev) for _ in range(k)]
+        fns = [lambda i=i: diopi.diopiSoftmax(ctx, ys[i], xs[i], -1) for i in range(k)]
+    elif name == "rope":
+        alg = 2 * es * n + 2 * 4 * t * 64
+        k = nsets(alg)
+        inv = 1.0 / (10000.0 ** (torch.arange(0, 128, 2, device=dev).float() / 128))
+        ang = torch.outer(torch.arange(t, device=dev).float(), inv)
+        cos, sin = torch.cos(ang), torch.sin(ang)
+        xs, ys = [rn(t, 32, 128) for _ in range(k)], [torch.empty((t, 32, 128), dtype=bf, device=dev) for _ in range(k)]
+        fns = [lambda i=i: diopi.diopiRotaryEmbedding(ctx, ys[i], xs[i], cos, sin, False, False) for i in range(k)]
+    elif name == "silu_mul":
+        # as dispatched: silu (read + write) then mul (2 reads + write) = 5 * es * numel
+        alg = 5 * es * n
+        k = nsets(alg)
+        gs, us, ys = [rn(t, H) for _ in range(k)], [rn(t, H) for _ in range(k)], [torch.empty((t, H), dtype=bf, device=dev) for _ in range(k)]
+
+        def f(i):
+            diopi.diopiSilu(ctx, ys[i], gs[i])
+            diopi.diopiMul(ctx, ys[i], ys[i], us[i])
+        fns = [lambda i=i: f(i) for i in range(k)]
+    elif name == "add":
+        alg = 3 * es * n
+        k = nsets(alg)
+        a, b, ys = [rn(t, H) for _ in range(k)], [rn(t, H) for _ in range(k)], [torch.empty((t, H), dtype=bf, device=dev) for _ in range(k)]
+        fns = [lambda i=i: diopi.diopiAdd(ctx, ys[i], a[i], b[i], 1) for i in range(k)]
+    elif name == "div_scalar":
+        alg = 2 * es * n
+        k = nsets(alg)
+        a = [rn(t, H) for _ in range(k)]
+        fns = [lambda i=i: diopi.diopiDivInpScalar(ctx, a[i], 11.313708498984761, 0) for i in range(k)]
+    elif name == "mask_add":
+        # [T/2048, 2048, 2048]-style broadcast add of a [2048, 2048] block needs T*H % 2048^2 == 0; use a [H] row broadcast otherwise
+        alg = 2 * es * n
+        k = nsets(alg)
+        if t >= 1024 and t % 1024 == 0:
+            a = [rn(t // 1024, 1024, H) for _ in range(k)]  # like [batch*heads, S, S] scores + an [S, S] mask
+            blk = rn(1024, H)
+        else:
+            a = [rn(t, H) for _ in range(k)]
+            blk = rn(H)
+        fns = [lambda i=i: diopi.diopiAddInp(ctx, a[i], blk, 1) for i in range(k)]
+    elif name == "cast_up":
+        alg = 6 * n
+        k = nsets(alg)
+        xs, ys = [rn(t, H) for _ in range(k)], [torch.empty((t, H), dtype=torch.float32, device=dev) for _ in range(k)]
+        fns = [lambda i=i: diopi.diopiCopyInp(ctx, xs[i], ys[i]) for i in range(k)]
+    elif name == "cast_down":
+        alg = 6 * n
+        k = nsets(alg)
+        xs, ys = [rn(t, H, dtype=torch.float32) for _ in range(k)], [torch.empty((t, H), dtype=bf, device=dev) for _ in range(k)]
+        fns = [lambda i=i: diopi.diopiCopyInp(ctx, xs[i], ys[i]) for i in range(k)]
+    elif name == "transpose_copy":
+        # [B, S, 32, 128] -> [B, 32, S, 128] with B*S = T
+        alg = 2 * es * n
+        k = nsets(alg)
+        s = min(t, 2048)
+        b = max(t // s, 1)
+        xs, ys = [rn(b, s, 32, 128) for _ in range(k)], [torch.empty((b, 32, s, 128), dtype=bf, device=dev) for _ in range(k)]
+        fns = [lambda i=i: diopi.diopiCopyInp(ctx, xs[i].transpose(1, 2), ys[i]) for i in range(k)]
+    elif name == "embedding":
+        alg = 2 * es * n + 8 * t
+        k = nsets(alg)
+        table = rn(32000, H)
+        ids = [torch.randint(0, 32000, (t,), generator=g, device=dev, dtype=torch.int64) for _ in range(k)]
+        ys = [torch.empty((t, H), dtype=bf, device=dev) for _ in range(k)]
+        fns = [lambda i=i: diopi.diopiIndexSelect(ctx, ys[i], table, 0, ids[i]) for i in range(k)]
+    else:
+        raise SystemExit("unknown op " + name)
+    return fns, alg
+
+
+MEM_OPS = ["rmsnorm", "layernorm", "softmax", "rope", "silu_mul", "cast_up", "cast_down", "embedding", "add", "div_scalar", "mask_add",
+           "transpose_copy"]
+
+# (label, batch, M, N, K, B layout): the 7B-shaped layer's contractions
+GEMM_CASES = [
+    ("prefill q/k/v/o proj", 1, 16384, 4096, 4096, "nk"),
+    ("prefill gate/up proj", 1, 16384, 11008, 4096, "nk"),
+    ("prefill down proj", 1, 16384, 4096, 11008, "nk"),
+    ("prefill QK^T", 256, 2048, 2048, 128, "nk"),
+    ("prefill PV", 256, 2048, 128, 2048, "kn"),
+    ("decode q/k/v/o proj", 1, 64, 4096, 4096, "nk"),
+    ("decode gate/up proj", 1, 64, 11008, 4096, "nk"),
+    ("decode down proj", 1, 64, 4096, 11008, "nk"),
+    ("decode QK^T", 2048, 1, 4096, 128, "nk"),
+    ("decode PV", 2048, 1, 128, 4096, "kn"),
+]
+
+
+def gemm_case(case, diopi, ctx, dev):
+    label, batch, m, n, k, layout = case
+    bf = torch.bfloat16
+    g = torch.Generator(device=dev)
+    g.manual_seed(m + n + k)
+    per_set = 2 * (batch * (m * k + n * k + m * n))
+    sets = int(max(1, min(8, math.ceil(2.0 * L2_BYTES / per_set))))
+    fns = []
+    for _ in range(sets):
+        if batch == 1:
+            a = torch.randn((m, k), generator=g, device=dev, dtype=torch.float32).to(bf)
+            b = (torch.randn((n, k) if layout == "nk" else (k, n), generator=g, device=dev, dtype=torch.float32) * 0.05).to(bf)
+            out = torch.empty((m, n), dtype=bf, device=dev)
+            bv = b.t() if layout == "nk" else b
+            fns.append(lambda out=out, a=a, bv=bv: diopi.diopiMm(ctx, out, a, bv))
+        else:
+            a = torch.randn((batch, m, k), generator=g, device=dev, dtype=torch.float32).to(bf)
+            b = (torch.randn((batch, n, k) if layout == "nk" else (batch, k, n), generator=g, device=dev, dtype=torch.float32) * 0.05).to(bf)
+            out = torch.empty((batch, m, n), dtype=bf, device=dev)
+            bv = b.transpose(1, 2) if layout == "nk" else b
+            fns.append(lambda out=out, a=a, bv=bv: diopi.diopiBmm(ctx, out, a, bv))
+    flops = 2.0 * batch * m * n * k
+    return fns, flops, per_set
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ops", default="all", help="comma list of: %s, gemm" % ", ".join(MEM_OPS))
+    ap.add_argument("--tokens", default="1,64,1024,16384,65536")
+    ap.add_argument("--gemm", default="all", help="comma list of indices into the GEMM case table, or 'all'")
+    ap.add_argument("--iters", type=int, default=50)
+    args = ap.parse_args()
+
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    assert torch.cuda.is_available(), "the sweep needs a CUDA device"
+    pkg.install_caching_allocator()
+    dev = "cuda:0"
+    torch.cuda.set_device(0)
+    diopi = pkg.diopi
+    stream = torch.cuda.current_stream()
+    ctx = diopi.Context(stream=stream.cuda_stream, device=0)
+    hbm, tflops, src = peaks()
+    ops = MEM_OPS + ["gemm"] if args.ops == "all" else args.ops.split(",")
+    tokens = [int(x) for x in args.tokens.split(",")]
+    for op in ops:
+        if op == "gemm":
+            idx = range(len(GEMM_CASES)) if args.gemm == "all" else [int(x) for x in args.gemm.split(",")]
+            for i in idx:
+                fns, flops, per_set = gemm_case(GEMM_CASES[i], diopi, ctx, dev)
+                ms = time_cases(fns, max(5, args.iters // 2) if flops > 1e11 else args.iters, stream)
+                label, batch, m, n, k, layout = GEMM_CASES[i]
+                rec = {"op": "gemm", "case": label, "batch": batch, "m": m, "n": n, "k": k, "b_layout": layout, "ms": round(ms, 4),
+                       "tflops": round(flops / (ms * 1e-3) / 1e12, 2), "frac_of_%s_bf16_burst" % src: round(flops / (ms * 1e-3) / 1e12 / tflops, 4),
+                       "gbs": round(per_set / (ms * 1e-3) / 1e9, 1), "frac_of_%s_hbm" % src: round(per_set / (ms * 1e-3) / 1e9 / hbm, 4)}
+                print(json.dumps(rec), flush=True)
+                ctx.release_workspace()
+            continue
+        for t in tokens:
+            fns, alg = mem_case(op, t, diopi, ctx, dev)
+            ms = time_cases(fns, args.iters, stream)
+            gbs = alg / (ms * 1e-3) / 1e9
+            print(json.dumps({"op": op, "tokens": t, "hidden": H, "algorithmic_bytes": alg, "us": round(ms * 1e3, 2), "gbs": round(gbs, 1),
+                              "frac_of_%s_hbm" % src: round(gbs / hbm, 4)}), flush=True)
+            del fns
+            ctx.release_workspace()
+    assert diopi.gemm_status() == 0
+
+
+if __name__ == "__main__":
+    main()
