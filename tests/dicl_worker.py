@@ -1,0 +1,142 @@
+"""One rank of the DICL communicator test (run as a child process by test_dicl_gpu.py):
+    python tests/dicl_worker.py <rank> <world> <rendezvous dir>
+Expected values are closed-form, as in the reference's dipu/tests/python/individual_scripts/test_rt_ddp.py:103-476."""
+import os
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    rank, world, rdv = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    dv, DT = pkg.devapis, pkg.diopi.DTYPE
+    torch.cuda.set_device(rank)
+    dev = "cuda:%d" % rank
+    # rank 0 creates the unique id; it travels as plain bytes (here through a file, in DIPU through the c10d store)
+    path = os.path.join(rdv, "uid")
+    if rank == 0:
+        uid = dv.diclGetUniqueId()
+        with open(path + ".tmp", "wb") as f:
+            f.write(uid)
+        os.rename(path + ".tmp", path)
+    else:
+        t0 = time.time()
+        while not os.path.exists(path):
+            if time.time() - t0 > 60:
+                raise SystemExit("rank %d: no unique id after 60 s" % rank)
+            time.sleep(0.05)
+        uid = open(path, "rb").read()
+    assert len(uid) == dv.DICL_UNIQUE_ID_BYTES_SIZE
+    comm = dv.diclCommInitRank(world, uid, rank, rank)
+    stream = dv.getStreamFromPool(rank)
+    assert dv.diclGetCommAsyncError(comm) == dv.diclResult_t.DICL_SUCCESS
+    assert dv.diclGetCommName(comm).startswith("dicl_b200_")
+
+    def sync():
+        dv.syncStream(stream)
+
+    # all-reduce SUM / MAX / MIN on float, and on bool / uint8 which must stay [True, False, True]
+    x = torch.full((1000,), float(rank + 1), device=dev)
+    dv.diclAllReduce(x.data_ptr(), x.data_ptr(), x.numel(), DT[x.dtype], dv.ReduceOp.SUM, comm, stream)
+    sync()
+    assert torch.equal(x.cpu(), torch.full((1000,), float(world * (world + 1) // 2)))
+    for op, want in ((dv.ReduceOp.MAX, float(world)), (dv.ReduceOp.MIN, 1.0), (dv.ReduceOp.AVG, (world + 1) / 2.0)):
+        y = torch.full((257,), float(rank + 1), device=dev, dtype=torch.bfloat16)
+        dv.diclAllReduce(y.data_ptr(), y.data_ptr(), y.numel(), DT[y.dtype], op, comm, stream)
+        sync()
+        assert torch.equal(y.float().cpu(), torch.full((257,), want))
+    for dtype in (torch.bool, torch.uint8):
+        for op in (dv.ReduceOp.SUM, dv.ReduceOp.MAX, dv.ReduceOp.MIN):
+            b = torch.tensor([True, False, True], device=dev).to(dtype)
+            dv.diclAllReduce(b.data_ptr(), b.data_ptr(), 3, DT[dtype], op, comm, stream)
+            sync()
+            want = torch.tensor([True, False, True]).to(dtype)
+            if dtype == torch.uint8 and op == dv.ReduceOp.SUM:
+                want = want * world
+            assert torch.equal(b.cpu(), want), (dtype, op, b)
+    # broadcast from the last rank
+    z = torch.arange(16, device=dev, dtype=torch.int64) * (rank + 1)
+    dv.diclBroadcast(z.data_ptr(), z.data_ptr(), 16, DT[z.dtype], world - 1, comm, stream)
+    sync()
+    assert torch.equal(z.cpu(), torch.arange(16) * world)
+    # all-gather
+    g_in = torch.full((4,), float(rank), device=dev)
+    g_out = torch.empty((world * 4,), device=dev)
+    dv.diclAllGather(g_in.data_ptr(), g_out.data_ptr(), 4, DT[g_in.dtype], comm, stream)
+    sync()
+    assert torch.equal(g_out.cpu(), torch.arange(world).float().repeat_interleave(4))
+    # reduce to rank 0
+    r_in = torch.full((8,), float(rank + 1), device=dev)
+    r_out = torch.zeros((8,), device=dev)
+    dv.diclReduce(r_in.data_ptr(), r_out.data_ptr(), 8, DT[r_in.dtype], dv.ReduceOp.SUM, 0, comm, stream)
+    sync()
+    if rank == 0:
+        assert torch.equal(r_out.cpu(), torch.full((8,), float(world * (world + 1) // 2)))
+    # reduce-scatter
+    rs_in = torch.arange(world * 4, device=dev, dtype=torch.float32)
+    rs_out = torch.empty((4,), device=dev)
+    dv.diclReduceScatter(rs_in.data_ptr(), rs_out.data_ptr(), 4, DT[rs_in.dtype], dv.ReduceOp.SUM, comm, stream)
+    sync()
+    assert torch.equal(rs_out.cpu(), torch.arange(rank * 4, rank * 4 + 4).float() * world)
+    # send / recv around a ring
+    s_buf = torch.full((32,), float(rank), device=dev)
+    r_buf = torch.empty((32,), device=dev)
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    if rank % 2 == 0:
+        dv.diclSend(s_buf.data_ptr(), 32, DT[s_buf.dtype], nxt, comm, stream)
+        dv.diclRecv(r_buf.data_ptr(), 32, DT[r_buf.dtype], prv, comm, stream)
+    else:
+        dv.diclRecv(r_buf.data_ptr(), 32, DT[r_buf.dtype], prv, comm, stream)
+        dv.diclSend(s_buf.data_ptr(), 32, DT[s_buf.dtype], nxt, comm, stream)
+    sync()
+    assert torch.equal(r_buf.cpu(), torch.full((32,), float(prv)))
+    # all-to-all, equal and unequal splits
+    a_in = (torch.arange(world * 2, device=dev, dtype=torch.float32) + 100 * rank)
+    a_out = torch.empty_like(a_in)
+    dv.diclAllToAllEqualSplit(a_in.data_ptr(), a_out.data_ptr(), 2, DT[a_in.dtype], comm, stream)
+    sync()
+    want = torch.cat([torch.arange(rank * 2, rank * 2 + 2).float() + 100 * r for r in range(world)])
+    assert torch.equal(a_out.cpu(), want)
+    send_counts = [r + 1 for r in range(world)]           # rank sends r+1 elements to rank r
+    recv_counts = [rank + 1 for _ in range(world)]        # and receives rank+1 from everyone
+    sd = [sum(send_counts[:r]) for r in range(world)]
+    rd = [sum(recv_counts[:r]) for r in range(world)]
+    u_in = torch.full((sum(send_counts),), float(rank), device=dev)
+    u_out = torch.empty((sum(recv_counts),), device=dev)
+    dv.diclAllToAllUnequalSplit(u_in.data_ptr(), send_counts, sd, u_out.data_ptr(), recv_counts, rd, DT[u_in.dtype], comm, stream)
+    sync()
+    assert torch.equal(u_out.cpu(), torch.arange(world).float().repeat_interleave(rank + 1))
+
+    # tensor-parallel layer: every rank's output equals the unsharded CPU oracle
+    from oracle import llama_cpu
+    from dipu_b200 import layer as L
+    cfg = llama_cpu.LayerConfig(hidden=512, heads=8, kv_heads=8, head_dim=64, ffn=1376, eps=1e-6)
+    w = llama_cpu.make_weights(cfg, seed=77)
+    emb = llama_cpu.make_embedding(32000, 512, seed=77)
+    ids = llama_cpu.make_token_ids(2, 64, seed=77)
+    ref = llama_cpu.decoder_layer_prefill(cfg, w, emb, ids)
+
+    class Group:
+        def __init__(self):
+            self.rank, self.size, self.device, self.comm, self.stream = rank, world, rank, comm, stream
+            self.pre_event, self.post_event = dv.getEventFromPool(), dv.getEventFromPool()
+    grp = L.TpGroup.__new__(L.TpGroup)
+    grp.__dict__.update(Group().__dict__)
+    lay = L.DecoderLayer(cfg, w, dtype=torch.float32, device=dev, tp_rank=rank, tp_size=world, tp_group=grp)
+    y = lay.prefill(L.embed(emb.to(dev), ids.to(dev)), 2, 64)
+    torch.cuda.synchronize()
+    err = (y.cpu() - ref).abs().max().item()
+    assert err <= 2e-4, err
+
+    dv.diclCommDestroy(comm)
+    print("rank %d ok" % rank, flush=True)
+
+
+if __name__ == "__main__":
+    main()
