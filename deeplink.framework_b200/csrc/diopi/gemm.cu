@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(256) skinny_kmajor_kernel(const SkinnyParams p
     const T* A = static_cast<const T*>(p.A) + b * p.a_sb;
     const T* B = static_cast<const T*>(p.B) + b * p.b_sb;
     T* C = static_cast<T*>(p.C) + b * p.c_sb;
-    constexpr int R = 4;
+    constexpr int R = 4;  // B rows in flight per lane group (8 was measured slower: register pressure)
     const int64_t kvec = p.K / 8;
     // Every lane of the warp runs the same number of iterations so that the shuffles below stay warp-uniform.
     const int64_t nblocks = (p.N + R - 1) / R;
@@ -231,7 +231,8 @@ bool launch_skinny(const GemmProblem& g, cudaStream_t stream) {
         int lpr = 32;
         while (lpr > 1 && lpr * 8 > g.K) lpr >>= 1;
         const int groups_per_cta = 8 * (32 / lpr);
-        int64_t bx = (g.N + 4 * groups_per_cta - 1) / (4 * groups_per_cta);
+        const int rows_per_group = 4;
+        int64_t bx = (g.N + rows_per_group * groups_per_cta - 1) / (rows_per_group * groups_per_cta);
         const int64_t cap = (static_cast<int64_t>(sm_count()) * 16 + g.batch - 1) / g.batch;
         if (bx > cap) bx = cap;
         if (bx < 1) bx = 1;

@@ -64,6 +64,7 @@ struct TcParams {
     int b_mn_major;
     int c_vec_ok;
     int tma_store;  // epilogue writes through map_c
+    int rotate_k;   // start each tile's K loop at a tile-dependent block (see the producer)
     uint32_t* status;
 };
 
@@ -169,7 +170,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 int b, mb, nb;
                 tile_coords(tile, p, &b, &mb, &nb);
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                // When there is a single row-block (decode: M <= 128) every CTA would read the same A tile at the same moment
+                // and the L2 slice holding it becomes the bottleneck. Starting each tile's K loop at a different block
+                // spreads those reads over the whole A matrix; the sum is the same up to fp32 association.
+                const int rot = p.rotate_k ? static_cast<int>((static_cast<unsigned>(tile) * 7u) % static_cast<unsigned>(p.k_blocks)) : 0;
+                for (int it = 0; it < p.k_blocks; ++it) {
+                    int kb = it + rot;
+                    if (kb >= p.k_blocks) kb -= p.k_blocks;
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
                     mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
                     tma_load_3d(smem_a + stage * Cfg::kABytes, &map_a, &full_bar[stage], kb * BK, mb * BM, b);
@@ -464,6 +471,7 @@ diopiError_t gemm_tc_launch(const GemmProblem& g, cudaStream_t stream) {
         p.tma_store = encode_map(&mc, g.c_dtype, g.C, g.N, g.M, g.batch, g.c_sm, g.batch > 1 ? g.c_sb : g.c_sm * g.M, 32) ? 1 : 0;
     }
     if (!p.tma_store) mc = ma;
+    p.rotate_k = (m_blocks == 1 && p.k_blocks > 1) ? 1 : 0;
     p.status = g.status_override != nullptr ? g.status_override : status_word();
     B200_CHECK(p.status != nullptr, "gemm: could not allocate the kernel status word");
     const int64_t total = static_cast<int64_t>(p.batch) * m_blocks * n_blocks;
