@@ -327,6 +327,208 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+// ---- split-K variant for a single row-block (M <= 128: decode) -------------------------------------------------------------
+// With few rows the product is bound by streaming the weight matrix once; a tile per CTA leaves most SMs idle (N / BN
+// tiles) and shrinking BN makes every CTA re-read all of A. Here a cluster of S CTAs shares one 128 x BN output tile,
+// each CTA contracting its own slice of K (so A is read N/BN times in total, B exactly once, and tiles x S CTAs stream).
+// The fp32 partial tiles are exchanged through distributed shared memory: every CTA parks its accumulator in its own
+// shared memory (the drained pipeline stages), the cluster synchronises, CTA r sums columns [r*BN/S, (r+1)*BN/S) of all
+// S partials in rank order and writes them out. No global workspace, one launch, deterministic.
+struct SplitKParams {
+    int M, N, K, batch;
+    int n_blocks, k_blocks, kb_per_cta, splits;
+    int64_t ldc, stride_cb;
+    void* C;
+    const void* bias;
+    int64_t bias_sb, bias_sr, bias_sc;
+    float alpha, beta;
+    uint32_t idesc;
+    int b_mn_major;
+    uint32_t* status;
+};
+
+template <int BN, typename TOut>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const SplitKParams p) {
+    using Cfg = TileCfg<BN>;
+    constexpr int STAGES = Cfg::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * Cfg::kABytes;
+    float* partial = reinterpret_cast<float*>(smem);  // [128][BN] fp32 over the drained stages, 16-byte chunks swizzled per row
+    static_assert(STAGES * Cfg::kStageBytes >= BM * BN * 4, "stage memory must hold the fp32 partial tile");
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::kStageBytes + Cfg::kStoreBytes);
+    uint64_t* full_bar = bars;
+    uint64_t* empty_bar = bars + STAGES;
+    uint64_t* acc_full = bars + 2 * STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t ks = cluster_ctarank();           // this CTA's K slice
+    const int tile = blockIdx.x / p.splits;           // (batch, n-block) shared by the cluster
+    const int b = tile / p.n_blocks;
+    const int nb = tile - b * p.n_blocks;
+    const int kb0 = static_cast<int>(ks) * p.kb_per_cta;
+    const int kb1 = min(p.k_blocks, kb0 + p.kb_per_cta);
+    const int my_kb = max(kb1 - kb0, 0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, BN < 32 ? 32 : BN);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int it = 0; it < my_kb; ++it) {
+                const int kb = kb0 + it;
+                if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) break;
+                mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+                tma_load_3d(smem_a + stage * Cfg::kABytes, &map_a, &full_bar[stage], kb * BK, 0, b);
+                if (!p.b_mn_major) {
+                    tma_load_3d(smem_b + stage * Cfg::kBBytes, &map_b, &full_bar[stage], kb * BK, nb * BN, b);
+                } else {
+#pragma unroll
+                    for (int g = 0; g < BN / 64; ++g) {
+                        tma_load_3d(smem_b + stage * Cfg::kBBytes + g * (64 * BK * 2), &map_b, &full_bar[stage], nb * BN + g * 64, kb * BK, b);
+                    }
+                }
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int it = 0; it < my_kb; ++it) {
+                if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem_a + stage * Cfg::kABytes);
+                const uint32_t b_addr = smem_u32(smem_b + stage * Cfg::kBBytes);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    const uint64_t da = make_smem_desc_sw128(a_addr + k * (UMMA_K * 2), 16, 1024);
+                    const uint64_t db = p.b_mn_major ? make_smem_desc_sw128(b_addr + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                                     : make_smem_desc_sw128(b_addr + k * (UMMA_K * 2), 16, 1024);
+                    umma_f16_ss(tmem_base, da, db, p.idesc, (it | k) != 0 ? 1u : 0u);
+                }
+                umma_commit(&empty_bar[stage]);
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+            if (ok) {
+                if (my_kb > 0) umma_commit(acc_full);
+                else mbar_arrive(acc_full);  // empty K slice: nothing to wait for
+            }
+        }
+    } else {
+        // epilogue part 1: accumulator -> this CTA's shared memory (rows that exist only)
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        if (mbar_wait(acc_full, 0, abort_flag)) {
+            tc_fence_after();
+            if (quarter * 32 < p.M) {  // warp-uniform: this quarter holds real rows
+                const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    if (my_kb > 0) {
+                        tmem_ld_32x32(t_row + c * 32, r);
+                        tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = 0u;  // empty K slice: contributes zeros
+                    }
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const int chunk = (c * 32 + j) / 4;
+                        float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                        *reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(partial) + static_cast<size_t>(row) * (BN * 4) +
+                                                   ((chunk ^ (row & 7)) * 16)) = v;
+                    }
+                }
+            }
+            tc_fence_before();
+        }
+    }
+
+    // every thread of every CTA of the cluster passes here, also after a timed-out wait
+    __syncthreads();
+    __syncwarp();  // lanes that ran a role loop rejoin their warp before the warp-aligned cluster barrier
+    cluster_sync_all();
+
+    if (warp >= 2 && *abort_flag == 0) {
+        // epilogue part 2: this CTA owns columns [ks * BN/S, (ks+1) * BN/S) of the tile: sum them over the S partials
+        const int slice_cols = BN / p.splits;           // multiple of 4
+        const int chunks_per_row = slice_cols / 4;
+        const int rows = min(p.M, BM);
+        const int items = rows * chunks_per_row;
+        const uint32_t local_base = smem_u32(partial);
+        for (int i = threadIdx.x - 64; i < items; i += 128) {
+            const int row = i / chunks_per_row;
+            const int cc = i - row * chunks_per_row;
+            const int chunk = (static_cast<int>(ks) * slice_cols) / 4 + cc;
+            const uint32_t off = static_cast<uint32_t>(row) * (BN * 4) + ((chunk ^ (row & 7)) * 16);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < p.splits; ++s) {
+                const float4 v = ld_cluster_f4(map_to_cta(local_base + off, static_cast<uint32_t>(s)));
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            const int col = nb * BN + chunk * 4;
+            float o[4] = {acc.x * p.alpha, acc.y * p.alpha, acc.z * p.alpha, acc.w * p.alpha};
+            TOut* crow = static_cast<TOut*>(p.C) + static_cast<int64_t>(b) * p.stride_cb + static_cast<int64_t>(row) * p.ldc;
+            if (p.bias != nullptr) {
+                const TOut* brow = static_cast<const TOut*>(p.bias) + static_cast<int64_t>(b) * p.bias_sb + static_cast<int64_t>(row) * p.bias_sr;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (col + j < p.N) o[j] += p.beta * to_f32(brow[static_cast<int64_t>(col + j) * p.bias_sc]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (col + j < p.N) crow[col + j] = from_f32<TOut>(o[j]);
+            }
+        }
+    }
+
+    // no CTA may leave while its shared memory can still be read by a peer
+    __syncwarp();
+    cluster_sync_all();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (*abort_flag != 0) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+        if (threadIdx.x == 0) atomicExch(p.status, 1u);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, BN < 32 ? 32 : BN);
+    }
+}
+
 // ---- host side -------------------------------------------------------------------------------------------------------
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                               const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -404,6 +606,61 @@ cudaError_t launch_tc_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, c
     }
 }
 
+template <int BN, typename TOut>
+cudaError_t launch_splitk(const CUtensorMap& ma, const CUtensorMap& mb, const SplitKParams& p, int grid, cudaStream_t stream) {
+    using Cfg = TileCfg<BN>;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_splitk_kernel<BN, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(p.splits);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemm_tc_splitk_kernel<BN, TOut>, ma, mb, p);
+}
+
+template <typename TOut>
+cudaError_t launch_splitk_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const SplitKParams& p, int grid, cudaStream_t stream) {
+    switch (bn) {
+        case 256: return launch_splitk<256, TOut>(ma, mb, p, grid, stream);
+        case 128: return launch_splitk<128, TOut>(ma, mb, p, grid, stream);
+        default: return launch_splitk<64, TOut>(ma, mb, p, grid, stream);
+    }
+}
+
+// Split-K plan for a single row-block: tile width and cluster size. Returns false when plain tiling is the better choice.
+bool plan_splitk(const GemmProblem& g, int sms, int* bn_out, int* splits_out) {
+    if (g.M > BM) return false;
+    const int64_t k_blocks = (g.K + BK - 1) / BK;
+    int bn = 256;
+    for (; bn > 64; bn >>= 1) {
+        const int64_t nb = (g.N + bn - 1) / bn;
+        if (g.N > bn / 2 && nb * g.batch * 8 >= (sms * 3) / 5) break;  // widest tile that can still fill most SMs with 8-way split
+    }
+    const int64_t nb = (g.N + bn - 1) / bn;
+    int splits = 8;
+    while (splits > 1 && (nb * g.batch * splits > (sms * 5) / 4 || splits > k_blocks)) splits >>= 1;
+    // every CTA of the cluster needs a non-empty K slice except possibly the last ones; keep slices balanced
+    if (splits < 2) return false;
+    if (nb * g.batch >= sms / 2) return false;  // enough tiles already
+    *bn_out = bn;
+    *splits_out = splits;
+    return true;
+}
+
 }  // namespace
 
 bool gemm_tc_eligible(const GemmProblem& g) {
@@ -444,6 +701,44 @@ diopiError_t gemm_tc_launch(const GemmProblem& g, cudaStream_t stream) {
     const int min_bn = b_mn ? 64 : 32;
     while (bn > min_bn && (g.N <= bn / 2 || g.batch * m_blocks * ((g.N + bn - 1) / bn) < sms)) bn >>= 1;
     const int64_t n_blocks = (g.N + bn - 1) / bn;
+
+    int sk_bn = 0, sk_splits = 0;
+    if (plan_splitk(g, sms, &sk_bn, &sk_splits)) {
+        const bool b_mn_sk = b_mn;
+        CUtensorMap sa, sb;
+        B200_CHECK(encode_map(&sa, g.ab_dtype, g.A, g.K, g.M, g.batch, g.a_sm, g.batch > 1 ? g.a_sb : g.a_sm * g.M, BM),
+                   "gemm: cuTensorMapEncodeTiled failed for A");
+        if (!b_mn_sk) {
+            B200_CHECK(encode_map(&sb, g.ab_dtype, g.B, g.K, g.N, g.batch, g.b_sn, g.batch > 1 ? g.b_sb : g.b_sn * g.N, sk_bn),
+                       "gemm: cuTensorMapEncodeTiled failed for B (K-major)");
+        } else {
+            B200_CHECK(encode_map(&sb, g.ab_dtype, g.B, g.N, g.K, g.batch, g.b_sk, g.batch > 1 ? g.b_sb : g.b_sk * g.K, BK),
+                       "gemm: cuTensorMapEncodeTiled failed for B (MN-major)");
+        }
+        SplitKParams q;
+        q.M = static_cast<int>(g.M); q.N = static_cast<int>(g.N); q.K = static_cast<int>(g.K); q.batch = static_cast<int>(g.batch);
+        q.n_blocks = static_cast<int>((g.N + sk_bn - 1) / sk_bn);
+        q.k_blocks = static_cast<int>((g.K + BK - 1) / BK);
+        q.splits = sk_splits;
+        q.kb_per_cta = (q.k_blocks + sk_splits - 1) / sk_splits;
+        q.ldc = g.c_sm; q.stride_cb = g.c_sb; q.C = g.C;
+        q.bias = g.bias; q.bias_sb = g.bias_sb; q.bias_sr = g.bias_sm; q.bias_sc = g.bias_sn;
+        q.alpha = g.alpha; q.beta = g.beta;
+        q.idesc = make_idesc_f16(is_bf16 ? 1 : 0, b_mn_sk, BM, sk_bn);
+        q.b_mn_major = b_mn_sk ? 1 : 0;
+        q.status = g.status_override != nullptr ? g.status_override : status_word();
+        B200_CHECK(q.status != nullptr, "gemm: could not allocate the kernel status word");
+        const int grid_sk = q.batch * q.n_blocks * sk_splits;
+        cudaError_t ek;
+        if (g.c_dtype == diopi_dtype_bfloat16) ek = launch_splitk_bn<bf16>(sk_bn, sa, sb, q, grid_sk, stream);
+        else if (g.c_dtype == diopi_dtype_float16) ek = launch_splitk_bn<fp16>(sk_bn, sa, sb, q, grid_sk, stream);
+        else ek = launch_splitk_bn<float>(sk_bn, sa, sb, q, grid_sk, stream);
+        if (ek != cudaSuccess) {
+            (void)cudaGetLastError();
+            B200_FAIL("gemm: split-K tcgen05 kernel launch failed: %s", cudaGetErrorString(ek));
+        }
+        return diopiSuccess;
+    }
 
     CUtensorMap ma, mb, mc;
     B200_CHECK(encode_map(&ma, g.ab_dtype, g.A, g.K, g.M, g.batch, g.a_sm, g.batch > 1 ? g.a_sb : g.a_sm * g.M, BM),

@@ -87,6 +87,8 @@ _SIGS = {
     "b200_host_cache_empty": [],
     "b200_default_stream": [_i, ctypes.POINTER(_vp)], "b200_stream_from_pool": [_i, ctypes.POINTER(_vp)],
     "b200_event_from_pool": [ctypes.POINTER(_vp)], "b200_event_to_pool": [_vp], "b200_release_all_pools": [],
+    "b200_graph_begin_capture": [_vp], "b200_graph_end_capture": [_vp, ctypes.POINTER(_vp)], "b200_graph_launch": [_vp, _vp],
+    "b200_graph_destroy": [_vp],
     "b200_dicl_get_unique_id": [ctypes.POINTER(UniqueId)],
     "b200_dicl_comm_init_rank": [ctypes.POINTER(_vp), _i, ctypes.POINTER(UniqueId), _i, _i], "b200_dicl_comm_destroy": [_vp],
     "b200_dicl_get_comm_async_error": [_vp],
@@ -266,6 +268,25 @@ def getEventFromPool():
 
 def restoreEventToPool(event):
     _check(_v.b200_event_to_pool(event), "restoreEventToPool")
+
+
+# ---- stream capture (no counterpart in dipu::devapis) -------------------------------------------------------------------
+def graphBeginCapture(stream):
+    _check(_v.b200_graph_begin_capture(stream), "graphBeginCapture")
+
+
+def graphEndCapture(stream):
+    g = _vp()
+    _check(_v.b200_graph_end_capture(stream, ctypes.byref(g)), "graphEndCapture")
+    return g.value
+
+
+def graphLaunch(graph_exec, stream):
+    _check(_v.b200_graph_launch(graph_exec, stream), "graphLaunch")
+
+
+def graphDestroy(graph_exec):
+    _check(_v.b200_graph_destroy(graph_exec), "graphDestroy")
 
 
 # ---- memory --------------------------------------------------------------------------------------------------------

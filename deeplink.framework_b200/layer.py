@@ -46,17 +46,27 @@ class TpGroup:
         self.rank, self.size, self.device = rank, size, device
         self.comm = devapis.diclCommInitRank(size, unique_id, rank, device)
         self.stream = devapis.getStreamFromPool(device)
-        self.pre_event = devapis.getEventFromPool()
-        self.post_event = devapis.getEventFromPool()
 
     def all_reduce_(self, tensor, compute_stream):
         """In-place SUM all-reduce of a dense tensor; the compute stream waits for the result without a host block."""
-        devapis.recordEvent(self.pre_event, compute_stream)
-        devapis.streamWaitEvent(self.stream, self.pre_event)
+        self.wait(self.all_reduce_async_(tensor, compute_stream), compute_stream)
+
+    def all_reduce_async_(self, tensor, compute_stream):
+        """Starts an in-place SUM all-reduce on the communication stream once the compute stream has produced `tensor`;
+        returns the event that marks its completion. The compute stream keeps running until wait() is called."""
+        pre = devapis.getEventFromPool()
+        devapis.recordEvent(pre, compute_stream)
+        devapis.streamWaitEvent(self.stream, pre)
+        devapis.restoreEventToPool(pre)  # the wait was enqueued against this record; the event may be re-used
         devapis.diclAllReduce(tensor.data_ptr(), tensor.data_ptr(), tensor.numel(), diopi.DTYPE[tensor.dtype], devapis.ReduceOp.SUM, self.comm,
                               self.stream)
-        devapis.recordEvent(self.post_event, self.stream)
-        devapis.streamWaitEvent(compute_stream, self.post_event)
+        post = devapis.getEventFromPool()
+        devapis.recordEvent(post, self.stream)
+        return post
+
+    def wait(self, event, compute_stream):
+        devapis.streamWaitEvent(compute_stream, event)
+        devapis.restoreEventToPool(event)
 
     def close(self):
         devapis.syncStream(self.stream)
@@ -79,6 +89,7 @@ class DecoderLayer:
         self.interleaved = _cfg_get(cfg, "rope_layout", "half") == "interleaved"
         self.dtype, self.device = dtype, torch.device(device)
         self.tp_rank, self.tp_size, self.tp_group = tp_rank, tp_size, tp_group
+        self.overlap_comm = True  # prefill: interleave two half-batches so the all-reduces overlap compute
         d, r = self.head_dim, tp_rank
         hq, hk, f = self.heads, self.kv_heads, self.ffn
 
@@ -96,11 +107,18 @@ class DecoderLayer:
         self.ffn_norm = put(weights["ffn_norm"])
         self._tables = {}
         self._masks = {}
+        self._keep = None  # while capturing a graph: every temporary, so that its memory stays reserved for replays
         self.launches = 0  # DIOPI calls issued (each is at least one kernel launch or device copy)
 
     # ---- helpers ------------------------------------------------------------------------------------------
     def _empty(self, *shape, dtype=None):
-        return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
+        t = torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
+        if self._keep is not None:
+            self._keep.append(t)
+        return t
+
+    def _like(self, x):
+        return self._empty(*x.shape, dtype=x.dtype)
 
     def _call(self, fn, ctx, *args):
         self.launches += 1
@@ -127,7 +145,7 @@ class DecoderLayer:
         return self._masks[seq]
 
     def _rope(self, ctx, x, cos, sin):
-        out = torch.empty_like(x)
+        out = self._like(x)
         self._call(diopi.diopiRotaryEmbedding, ctx, out, x, cos, sin, False, self.interleaved)
         return out
 
@@ -145,25 +163,28 @@ class DecoderLayer:
         if self.tp_size > 1:
             self.tp_group.all_reduce_(t, ctx.stream)
 
-    def _ffn(self, ctx, h):
-        hn = torch.empty_like(h)
+    def _ffn_partial(self, ctx, h):
+        """RMSNorm -> gate / up -> SiLU * up -> down projection: this rank's partial sum (before the all-reduce)."""
+        hn = self._like(h)
         self._call(diopi.diopiRMSNorm, ctx, hn, None, h, [self.hidden], self.ffn_norm, None, self.eps)
         g = self._linear(ctx, hn, self.w1)
         u = self._linear(ctx, hn, self.w3)
         self._call(diopi.diopiSiluInp, ctx, g)
         self._call(diopi.diopiMulInp, ctx, g, u)
-        dn = self._linear(ctx, g, self.w2)
+        return self._linear(ctx, g, self.w2)
+
+    def _ffn(self, ctx, h, out=None):
+        dn = self._ffn_partial(ctx, h)
         self._all_reduce(ctx, dn)
-        out = torch.empty_like(h)
+        out = self._like(h) if out is None else out
         self._call(diopi.diopiAdd, ctx, out, h, dn, 1)
         return out
 
     # ---- prefill ---------------------------------------------------------------------------------------------------
-    def prefill(self, x, batch, seq, ctx=None):
-        """x [batch*seq, hidden] -> [batch*seq, hidden]; causal attention through bmm + softmax."""
-        ctx = ctx or diopi.Context()
+    def _attention_partial(self, ctx, x, batch, seq):
+        """RMSNorm -> q/k/v -> rotary -> causal attention through bmm + softmax -> o_proj: this rank's partial sum."""
         t, d, hq, hk = batch * seq, self.head_dim, self.heads, self.kv_heads
-        hn = torch.empty_like(x)
+        hn = self._like(x)
         self._call(diopi.diopiRMSNorm, ctx, hn, None, x, [self.hidden], self.attention_norm, None, self.eps)
         q = self._linear(ctx, hn, self.wq).view(t, hq, d)
         k = self._linear(ctx, hn, self.wk).view(t, hk, d)
@@ -186,13 +207,65 @@ class DecoderLayer:
         self._call(diopi.diopiBmm, ctx, av, scores, vt.view(batch * hq, seq, d))
         merged = self._empty(batch, seq, hq, d)
         self._call(diopi.diopiCopyInp, ctx, av.view(batch, hq, seq, d).transpose(1, 2), merged)
-        attn = self._linear(ctx, merged.view(t, hq * d), self.wo)
+        return self._linear(ctx, merged.view(t, hq * d), self.wo)
+
+    def prefill(self, x, batch, seq, ctx=None):
+        """x [batch*seq, hidden] -> [batch*seq, hidden]; causal attention through bmm + softmax."""
+        ctx = ctx or diopi.Context()
+        if self.tp_size > 1 and self.overlap_comm and batch % 2 == 0:
+            return self._prefill_overlapped(x, batch, seq, ctx)
+        attn = self._attention_partial(ctx, x, batch, seq)
         self._all_reduce(ctx, attn)
-        h = torch.empty_like(x)
+        h = self._like(x)
         self._call(diopi.diopiAdd, ctx, h, x, attn, 1)
         out = self._ffn(ctx, h)
         ctx.release_workspace()
         return out
+
+    def _prefill_overlapped(self, x, batch, seq, ctx):
+        """Tensor-parallel prefill with the four all-reduces hidden behind compute: the batch is cut into two halves
+        whose blocks are interleaved, so that while one half's partial sums travel over NVLink on the communication
+        stream the other half's attention / FFN runs on the compute stream. Same DIOPI calls, on half the rows each."""
+        grp, cs = self.tp_group, ctx.stream
+        half = batch // 2
+        rows = half * seq
+        xs = (x[:rows], x[rows:])
+        out = self._like(x)
+        outs = (out[:rows], out[rows:])
+        attn, ev_attn, h, dn, ev_dn = [None, None], [None, None], [None, None], [None, None], [None, None]
+        for i in range(2):
+            attn[i] = self._attention_partial(ctx, xs[i], half, seq)
+            ev_attn[i] = grp.all_reduce_async_(attn[i], cs)
+        for i in range(2):
+            grp.wait(ev_attn[i], cs)
+            h[i] = self._like(xs[i])
+            self._call(diopi.diopiAdd, ctx, h[i], xs[i], attn[i], 1)
+            dn[i] = self._ffn_partial(ctx, h[i])
+            ev_dn[i] = grp.all_reduce_async_(dn[i], cs)
+        for i in range(2):
+            grp.wait(ev_dn[i], cs)
+            self._call(diopi.diopiAdd, ctx, outs[i], h[i], dn[i], 1)
+        ctx.release_workspace()
+        return out
+
+    def capture_decode(self, x, k_cache, v_cache, position, ctx):
+        """Captures one decode step (every DIOPI call, the KV append and, under tensor parallelism, the all-reduces on the
+        communication stream) into a CUDA graph. Returns (replay, out): replay() enqueues the whole step with one launch;
+        it reads x / the caches in place and writes `out`. The step must have run at least once before (warm-up: the first
+        call of a kernel may set attributes or allocate its status word, which is not allowed while capturing)."""
+        self._keep = []
+        devapis.graphBeginCapture(ctx.stream)
+        try:
+            out = self.decode(x, k_cache, v_cache, position, ctx)
+        finally:
+            graph = devapis.graphEndCapture(ctx.stream)
+        keep = self._keep  # the graph holds raw addresses: the temporaries live as long as the replay closure
+        self._keep = None
+
+        def replay(_keep=keep):
+            devapis.graphLaunch(graph, ctx.stream)
+        replay.graph = graph
+        return replay, out
 
     # ---- decode ------------------------------------------------------------------------------------------------------
     def decode(self, x, k_cache, v_cache, position, ctx=None):
@@ -201,7 +274,7 @@ class DecoderLayer:
         ctx = ctx or diopi.Context()
         b, d, hq, hk = x.shape[0], self.head_dim, self.heads, self.kv_heads
         length = position + 1
-        hn = torch.empty_like(x)
+        hn = self._like(x)
         self._call(diopi.diopiRMSNorm, ctx, hn, None, x, [self.hidden], self.attention_norm, None, self.eps)
         q = self._linear(ctx, hn, self.wq).view(b, hq, d)
         k = self._linear(ctx, hn, self.wk).view(b, hk, d)
@@ -227,7 +300,7 @@ class DecoderLayer:
         self._call(diopi.diopiBmm, ctx, av, scores, vview)
         attn = self._linear(ctx, av.view(b, hq * d), self.wo)
         self._all_reduce(ctx, attn)
-        h = torch.empty_like(x)
+        h = self._like(x)
         self._call(diopi.diopiAdd, ctx, h, x, attn, 1)
         out = self._ffn(ctx, h)
         ctx.release_workspace()

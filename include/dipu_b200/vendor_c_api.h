@@ -154,6 +154,17 @@ B200_API b200Status_t b200_event_from_pool(b200Event_t* event);
 B200_API b200Status_t b200_event_to_pool(b200Event_t event);
 B200_API b200Status_t b200_release_all_pools(void);
 
+/* ---- stream capture into CUDA graphs ---------------------------------------------------------------------------------
+ * No counterpart in the reference (DIPU replays the eager op stream from the host every step). A latency-bound step such as
+ * single-token decode is captured once - every DIOPI call, copy and collective enqueued on `stream` between begin and end,
+ * including work forked to other streams through events - and replayed with one launch, which removes the per-op host cost.
+ * Nothing that synchronises or allocates through the driver may run while capturing: warm the step up first. */
+typedef struct CUgraphExec_st* b200GraphExec_t;
+B200_API b200Status_t b200_graph_begin_capture(b200Stream_t stream);
+B200_API b200Status_t b200_graph_end_capture(b200Stream_t stream, b200GraphExec_t* exec);
+B200_API b200Status_t b200_graph_launch(b200GraphExec_t exec, b200Stream_t stream);
+B200_API b200Status_t b200_graph_destroy(b200GraphExec_t exec);
+
 /* ---- DICL communicator: diclapis.h:20-82 ------------------------------------------------------------------
  * dtype: a diopiDtype_t value (include/diopi/diopirt.h); bool travels as uint8 like the reference's NCCL map
  * (vendor/cuda/communiatorimpl.cpp:44-52). op: b200ReduceOp_t, same order as c10d::ReduceOp (communiatorimpl.cpp:35-41). */

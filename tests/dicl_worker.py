@@ -125,14 +125,15 @@ def main():
     class Group:
         def __init__(self):
             self.rank, self.size, self.device, self.comm, self.stream = rank, world, rank, comm, stream
-            self.pre_event, self.post_event = dv.getEventFromPool(), dv.getEventFromPool()
     grp = L.TpGroup.__new__(L.TpGroup)
     grp.__dict__.update(Group().__dict__)
     lay = L.DecoderLayer(cfg, w, dtype=torch.float32, device=dev, tp_rank=rank, tp_size=world, tp_group=grp)
-    y = lay.prefill(L.embed(emb.to(dev), ids.to(dev)), 2, 64)
-    torch.cuda.synchronize()
-    err = (y.cpu() - ref).abs().max().item()
-    assert err <= 2e-4, err
+    for overlap in (True, False):  # all-reduces overlapped with the other half-batch's compute, and the plain order
+        lay.overlap_comm = overlap
+        y = lay.prefill(L.embed(emb.to(dev), ids.to(dev)), 2, 64)
+        torch.cuda.synchronize()
+        err = (y.cpu() - ref).abs().max().item()
+        assert err <= 2e-4, (overlap, err)
 
     dv.diclCommDestroy(comm)
     print("rank %d ok" % rank, flush=True)

@@ -108,6 +108,30 @@ def test_tc_mm_nmajor(diopi, ctx, m, n, k):
     assert diopi.gemm_status() == 0
 
 
+@pytest.mark.parametrize("m,n,k,nk", [(64, 4096, 4096, True), (64, 11008, 4096, True), (64, 4096, 11008, True), (16, 512, 4096, True),
+                                      (100, 1376, 512, True), (128, 264, 72, True), (64, 4096, 1024, False), (33, 136, 200, False),
+                                      (64, 64, 4096, True), (8, 4096, 328, False)])
+def test_tc_split_k_single_row_block(diopi, ctx, m, n, k, nk):
+    """M <= 128 (decode): a cluster of CTAs splits K and sums the partial tiles through distributed shared memory."""
+    a = rnd((m, k), torch.bfloat16, seed=m + k)
+    b = rnd((n, k) if nk else (k, n), torch.bfloat16, seed=n, scale=0.05)
+    ref = a.float() @ (b.float().t() if nk else b.float())
+    bd = b.to(DEV)
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=DEV)
+    diopi.diopiMm(ctx, out, a.to(DEV), bd.t() if nk else bd)
+    check_lowp(out, ref)
+    # deterministic: a second run gives the same bits
+    out2 = torch.empty((m, n), dtype=torch.bfloat16, device=DEV)
+    diopi.diopiMm(ctx, out2, a.to(DEV), bd.t() if nk else bd)
+    assert torch.equal(out, out2)
+    # bias / scale epilogue and fp32 output
+    bias = rnd((n,), torch.float32, seed=5)
+    o32 = torch.empty((m, n), dtype=torch.float32, device=DEV)
+    diopi.diopiAddmm(ctx, o32, bias.to(DEV), a.to(DEV), bd.t() if nk else bd, 0.5, 2.0)
+    check_lowp(o32, 0.5 * bias + 2.0 * ref, rel_l2=1e-4, max_rel=1e-4)
+    assert diopi.gemm_status() == 0
+
+
 def test_tc_linearity_and_identity(diopi, ctx):
     """Size-independent properties at a large shape: A*I == A bit for bit, and (A1 + A2)*B == A1*B + A2*B within rounding."""
     m, n = 4096, 4096

@@ -89,6 +89,39 @@ def test_bf16_decode_layer(pkg, kv_heads):
     assert torch.equal(kd.cpu()[:, :, mask], kc.to(bf)[:, :, mask])
 
 
+def test_decode_step_replayed_from_a_graph(pkg):
+    """A decode step captured into a CUDA graph through the vendor runtime and replayed gives the eager result bit for bit,
+    also after the inputs changed in place."""
+    from dipu_b200 import diopi
+    from dipu_b200 import layer as L
+    cfg = llama_cpu.LayerConfig(hidden=1024, heads=8, kv_heads=8, head_dim=128, ffn=2752, eps=1e-6)
+    w = llama_cpu.make_weights(cfg, seed=51)
+    bf = torch.bfloat16
+    kc, vc = llama_cpu.make_kv_cache(cfg, 4, 256, seed=51)
+    kd, vd = kc.to(bf).to(DEV), vc.to(bf).to(DEV)
+    rng = np.random.default_rng(52)
+    x = torch.from_numpy(rng.standard_normal((4, 1024), dtype=np.float32) * 0.5).to(bf).to(DEV)
+    lay = L.DecoderLayer(cfg, w, dtype=bf, device=DEV)
+    torch.cuda.synchronize()
+    # the legacy NULL stream cannot be captured: run on the runtime's default stream (a created stream, as in DIPU)
+    stream = torch.cuda.ExternalStream(pkg.devapis.getDefaultStream(0), device=DEV)
+    with torch.cuda.stream(stream):
+        ctx = diopi.Context(stream=stream.cuda_stream, device=0)
+        eager = lay.decode(x, kd, vd, 200, ctx).clone()
+        replay, out = lay.capture_decode(x, kd, vd, 200, ctx)
+        replay()
+        stream.synchronize()
+        assert torch.equal(out, eager)
+        x.mul_(-0.5)  # new input in the same buffer: the replay must read it
+        eager2 = lay.decode(x, kd, vd, 200, ctx).clone()
+        replay()
+        stream.synchronize()
+        assert torch.equal(out, eager2) and not torch.equal(eager, eager2)
+        pkg.devapis.graphDestroy(replay.graph)
+    torch.cuda.synchronize()
+    assert pkg.diopi.gemm_status() == 0
+
+
 def test_tp_shards_sum_to_unsharded_layer_on_one_gpu(pkg):
     """Two tensor-parallel ranks emulated one after the other on one GPU: the row-parallel partial sums of the attention
     block, added where the all-reduce would add them, reproduce the unsharded attention output. (w2 is zeroed so that a
