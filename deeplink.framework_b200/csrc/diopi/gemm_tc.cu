@@ -254,14 +254,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     // the store issued from this buffer two pieces ago must have finished reading it
                     if (lane == 0) tma_store_wait_read<1>();
                     __syncwarp();
+                    // all TMEM loads of the piece are issued before the single wait: their latencies overlap
+                    uint32_t r[LOADS][32];
+#pragma unroll
+                    for (int l = 0; l < LOADS; ++l) tmem_ld_32x32(t_row + c * PIECE_COLS + l * 32, r[l]);
+                    tmem_ld_wait();
 #pragma unroll
                     for (int l = 0; l < LOADS; ++l) {
-                        uint32_t r[32];
-                        tmem_ld_32x32(t_row + c * PIECE_COLS + l * 32, r);
-                        tmem_ld_wait();
                         float v[32];
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[l][j]) * p.alpha;
                         if (p.bias != nullptr && row < p.M) {
                             const TOut* brow = static_cast<const TOut*>(p.bias) + static_cast<int64_t>(b) * p.bias_sb + static_cast<int64_t>(row) * p.bias_sr;
 #pragma unroll
