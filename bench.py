@@ -97,10 +97,10 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(sm), "power_w_max": max(self.power) if self.power else None}
 
 
-def make_device_weights(cfg, device, dtype):
+def make_device_weights(cfg, device, dtype, seed=SEED):
     """Full (unsharded) N(0, 0.02) weights, identical on every rank (same seed), generated on the device."""
     g = torch.Generator(device=device)
-    g.manual_seed(SEED)
+    g.manual_seed(seed)
 
     def n(*shape):
         return (torch.randn(shape, generator=g, device=device, dtype=torch.float32) * 0.02).to(dtype)
@@ -189,6 +189,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the secondary decode measurement")
     ap.add_argument("--no-caching-allocator", action="store_true", help="let torch use its own allocator for tensors")
+    ap.add_argument("--workload", default="7b", choices=["7b", "70b"],
+                    help="7b: one Llama-2-7B-shaped layer, batch 8 x seq 2048 (default). 70b: a stack of four Llama-2-70B-shaped "
+                         "layers (GQA 64/8), batch 4 x seq 4096, meant for --gpus 2/4/8")
     ap.add_argument("--overlap", default="auto", choices=["auto", "on", "off"],
                     help="tensor-parallel prefill: interleave two half-batches so the all-reduces overlap compute")
     args = ap.parse_args()
@@ -222,14 +225,24 @@ def main():
         dist.broadcast_object_list(uid, src=0)  # the unique id travels through the store as bytes, as in ProcessGroupDICL
         tp_group = L.TpGroup(rank, world, uid[0], local_rank)
 
-    cfg = Cfg()
     dtype = torch.bfloat16
-    batch, seq = args.batch, args.seq
+    if args.workload == "70b":
+        cfg = Cfg(hidden=8192, heads=64, kv_heads=8, head_dim=128, ffn=28672)
+        batch, seq, n_layers = 4, 4096, 4
+        args.no_decode = True
+        args.no_cpu_baseline = True
+    else:
+        cfg = Cfg()
+        batch, seq, n_layers = args.batch, args.seq, 1
     tokens = batch * seq
-    weights = make_device_weights(cfg, device, dtype)
-    lay = L.DecoderLayer(cfg, weights, dtype=dtype, device=device, tp_rank=rank, tp_size=world, tp_group=tp_group)
-    del weights
-    lay.overlap_comm = (world >= 4) if args.overlap == "auto" else (args.overlap == "on")
+    layers = []
+    for li in range(n_layers):
+        weights = make_device_weights(cfg, device, dtype, seed=SEED + 100 * li)
+        layers.append(L.DecoderLayer(cfg, weights, dtype=dtype, device=device, tp_rank=rank, tp_size=world, tp_group=tp_group))
+        del weights
+    for l_ in layers:
+        l_.overlap_comm = (world >= 4) if args.overlap == "auto" else (args.overlap == "on")
+    lay = layers[0]
     g = torch.Generator(device=device)
     g.manual_seed(SEED + 1)
     table = (torch.randn((VOCAB, cfg.hidden), generator=g, device=device, dtype=torch.float32) * 0.02).to(dtype)
@@ -262,8 +275,13 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.item()
 
+    def run_layers(h):
+        for l_ in layers:
+            h = l_.prefill(h, batch, seq, ctx)
+        return h
+
     def step_resident():
-        return lay.prefill(x, batch, seq, ctx)
+        return run_layers(x)
 
     e2e_state = {"i": 0}
 
@@ -274,7 +292,7 @@ def main():
         e2e_state["i"] += 1
         devapis.memCopyH2DAsync(stream.cuda_stream, ids_host.numel() * 8, ids_dev.data_ptr(), ids_host.data_ptr())  # this step's input
         h = L.embed(table, ids_dev, ctx)
-        y = lay.prefill(h, batch, seq, ctx)
+        y = run_layers(h)
         if rank != 0:
             return y  # the layer output is replicated after the all-reduce: one rank returns it to the host
         devapis.recordEvent(copy_events[i], stream.cuda_stream)
@@ -296,7 +314,8 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    lay.launches = 0
+    for l_ in layers:
+        l_.launches = 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(args.steps):
@@ -304,7 +323,7 @@ def main():
     e1.record(stream)
     barrier()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
-    launches = lay.launches
+    launches = sum(l_.launches for l_ in layers)
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end-to-end timing (host buffers in, host buffers out) ----
@@ -325,22 +344,26 @@ def main():
 
     # ---- per-op device times: the same step with events around every DIOPI call ----
     per_op = {}
-    orig_call = lay._call
 
-    def timed_call(fn, c, *a):
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record(stream)
-        r = orig_call(fn, c, *a)
-        e.record(stream)
-        per_op.setdefault(fn.__name__, []).append((s, e, a))
-        return r
+    def make_timed(orig_call):
+        def timed_call(fn, c, *a):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(stream)
+            r = orig_call(fn, c, *a)
+            e.record(stream)
+            per_op.setdefault(fn.__name__, []).append((s, e, a))
+            return r
+        return timed_call
 
-    lay._call = timed_call
+    originals = [l_._call for l_ in layers]
+    for l_ in layers:
+        l_._call = make_timed(l_._call)
     reps = 3
     for _ in range(reps):
         step_resident()
     torch.cuda.synchronize()
-    lay._call = orig_call
+    for l_, o_ in zip(layers, originals):
+        l_._call = o_
     peaks = measured_peaks()
     ops = {}
     mm_flops, mm_ms, bmm_flops, bmm_ms = 0.0, 0.0, 0.0, 0.0
@@ -384,15 +407,20 @@ def main():
 
     if rank == 0:
         lin, attn = layer_flops(cfg, batch, seq, world)
+        lin, attn = lin * n_layers, attn * n_layers
+        workload = ("llama2-7b-shaped decoder layer, prefill, batch %d x seq %d, bmm+softmax attention" % (batch, seq)) if args.workload == "7b" \
+            else ("stack of 4 llama2-70b-shaped decoder layers (GQA 64/8), prefill, batch %d x seq %d, bmm+softmax attention" % (batch, seq))
         value = tokens * args.steps / (ms_total * 1e-3)
         e2e_value = tokens * args.steps / (ms_e2e * 1e-3)
         line = {
             "metric": "decoder-layer tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": "llama2-7b-shaped decoder layer, prefill, batch %d x seq %d, bmm+softmax attention" % (batch, seq),
+            "config": {"workload": workload, "layers": n_layers, "kv_heads": cfg.kv_heads,
                        "hidden": cfg.hidden, "heads": cfg.heads, "head_dim": cfg.head_dim, "ffn": cfg.ffn, "tokens_per_step": tokens,
-                       "parallelism": "tp%d" % world, "overlap_allreduce": bool(lay.overlap_comm and world > 1), "l2": "inputs larger than L2: weights 405 MB + >=134 MB per activation, no flush",
+                       "parallelism": "tp%d" % world, "overlap_allreduce": bool(lay.overlap_comm and world > 1), "l2": "inputs larger than L2: weights %d MB per layer and rank + %d MB per activation tensor, no flush"
+                             % ((2 * (2 * cfg.hidden * cfg.heads * cfg.head_dim + 2 * cfg.hidden * cfg.kv_heads * cfg.head_dim
+                                      + 3 * cfg.hidden * cfg.ffn) // world) >> 20, (tokens * cfg.hidden * 2) >> 20),
                        "allocator": "torch default" if args.no_caching_allocator else "b200 caching allocator (pluggable)"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": ids_host.numel() * 8,
                     "d2h_bytes_per_step": out_host[0].numel() * out_host[0].element_size(),

@@ -4,6 +4,8 @@
                                  stream and event pools, DICL communicator (NCCL bound at run time)
     lib/libdiopirt_minihost.so   a small DIOPI host (the diopirt callbacks over plain tensor structs)
     lib/libdiopi_impl.so         the DIOPI operator library: hand-written sm_100a kernels
+    lib/libdipu_vendor_b200_torchabi.so   the vendor contract with DIPU's exact C++ signatures (namespace dipu::devapis, torch
+                                 types in the arguments): thin wrappers over the C-ABI runtime, built when torch's headers are present
 
 Objects go to build/ (ignored by git), libraries to lib/ next to this file so that they travel with the tree.
 Run as a script or call build().
@@ -77,6 +79,39 @@ def _link(name, objs, extra):
     return out
 
 
+def _build_torch_abi(vendor_lib, verbose):
+    """csrc/torch_abi/*.cpp: the files a DIPU tree would compile as csrc_dipu/vendor/b200/. Needs torch's C++ headers."""
+    try:
+        import torch
+        from torch.utils.cpp_extension import include_paths
+        incs = include_paths()
+        torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    except Exception:
+        return None
+    srcs = sorted(os.path.join(CSRC, "torch_abi", f) for f in os.listdir(os.path.join(CSRC, "torch_abi")) if f.endswith(".cpp"))
+    objs = []
+    newest_hdr = max(os.path.getmtime(h) for h in _headers())
+    for src in srcs:
+        obj = os.path.join(OBJ, "torch_abi_" + os.path.basename(src) + ".o")
+        if not (os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(src), newest_hdr, os.path.getmtime(__file__))):
+            cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-fvisibility=hidden", "-c", src, "-o", obj, "-I", os.path.join(ROOT, "include"),
+                   "-I", "/usr/local/cuda/include"] + ["-I" + p for p in incs]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError("g++ failed for %s:\n%s\n%s" % (src, r.stdout, r.stderr))
+            if verbose:
+                print("compiled", os.path.relpath(src, ROOT), flush=True)
+        objs.append(obj)
+    out = os.path.join(LIB, "libdipu_vendor_b200_torchabi.so")
+    if not (os.path.exists(out) and all(os.path.getmtime(out) >= os.path.getmtime(o) for o in objs)):
+        cmd = ["g++", "-shared", "-o", out] + objs + ["-L", LIB, "-l:libdipu_vendor_b200.so", "-L", torch_lib, "-lc10", "-ltorch_cpu",
+                                                       "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + torch_lib]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("link failed for %s:\n%s\n%s" % (out, r.stdout, r.stderr))
+    return out
+
+
 def build(verbose=False):
     os.makedirs(OBJ, exist_ok=True)
     os.makedirs(LIB, exist_ok=True)
@@ -84,6 +119,7 @@ def build(verbose=False):
     for sub, extra in (("vendor", ["-I", _nccl_include()]), ("minihost", []), ("diopi", [])):
         for src in _sources(sub):
             jobs.append((sub, src, extra))
+    # csrc/torch_abi is compiled separately (g++ against torch's headers), see _build_torch_abi
     objs = {"vendor": [], "minihost": [], "diopi": []}
     with concurrent.futures.ThreadPoolExecutor(max_workers=max(1, os.cpu_count() or 1)) as ex:
         futs = {ex.submit(_compile, src, extra): (sub, src) for sub, src, extra in jobs}
@@ -99,7 +135,11 @@ def build(verbose=False):
           ["-L", LIB, "-l:libdipu_vendor_b200.so", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"])
     # the diopirt callbacks stay undefined here: the host that loads this library provides them (DIPU, or the minihost)
     _link("libdiopi_impl.so", objs["diopi"], [])
-    return [vendor, os.path.join(LIB, "libdiopirt_minihost.so"), os.path.join(LIB, "libdiopi_impl.so")]
+    built = [vendor, os.path.join(LIB, "libdiopirt_minihost.so"), os.path.join(LIB, "libdiopi_impl.so")]
+    abi = _build_torch_abi(vendor, verbose)
+    if abi:
+        built.append(abi)
+    return built
 
 
 if __name__ == "__main__":

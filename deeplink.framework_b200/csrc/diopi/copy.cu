@@ -180,6 +180,21 @@ bool try_word_copy(const TensorView& src, const TensorView& dst, cudaStream_t st
         wi.sstride[d] = it.stride[1][d] / epw;
         wi.nrows *= it.shape[d];
     }
+    // Few long rows (an expand of whole [S, D] planes, say) would leave most of the GPU idle: cut the inner run into
+    // pieces of at most 512 words by adding an outer dimension that walks the pieces.
+    if (wi.row_words > 512 && wi.ndim < kMaxDims) {
+        int64_t pieces = 1;
+        while (wi.row_words / pieces > 512 && (wi.row_words / pieces) % 2 == 0) pieces *= 2;
+        if (pieces > 1) {
+            const int64_t piece_words = wi.row_words / pieces;
+            wi.shape[wi.ndim] = pieces;
+            wi.sstride[wi.ndim] = piece_words;
+            wi.dstride[wi.ndim] = piece_words;
+            ++wi.ndim;
+            wi.nrows *= pieces;
+            wi.row_words = piece_words;
+        }
+    }
     if ((wi.nrows + 3) / 4 * 32 / 256 + 1 > 0x7fffffffLL) return false;
     switch (word) {
         case 16: launch_word_copy<uint4>(src.data, dst.data, wi, stream); break;

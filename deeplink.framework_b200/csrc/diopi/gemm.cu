@@ -270,6 +270,11 @@ bool skinny_eligible(const GemmProblem& g) {
 diopiError_t run_gemm(diopiContextHandle_t ctx, const char* name, const GemmProblem& g) {
     if (g.batch == 0 || g.M == 0 || g.N == 0) return diopiSuccess;
     cudaStream_t stream = stream_of(ctx);
+    // Few-row products (decode attention over the KV cache) are bandwidth-bound either way; the tensor-core kernel is
+    // tried first because its TMA pipeline streams B faster than per-thread loads do (measured 82 % / 103 % of the copy
+    // bandwidth for q*K^T / p*V at batch 64, cache length 4096, against 72 % / 63 % for the kernels below). The skinny
+    // kernels serve operands that do not meet the TMA alignment rules.
+    if (g.K > 0 && gemm_tc_eligible(g)) return gemm_tc_launch(g, stream);
     if (g.K > 0 && skinny_eligible(g)) {
         bool ok = (g.ab_dtype == diopi_dtype_bfloat16) ? launch_skinny<bf16>(g, stream) : launch_skinny<fp16>(g, stream);
         if (ok) {
@@ -277,8 +282,6 @@ diopiError_t run_gemm(diopiContextHandle_t ctx, const char* name, const GemmProb
             return diopiSuccess;
         }
     }
-    if (g.K > 0 && gemm_tc_eligible(g)) return gemm_tc_launch(g, stream);
-
     B200_CHECK(is_floating(g.ab_dtype) && is_floating(g.c_dtype), "%s: only floating dtypes are supported (got %s -> %s)", name,
                dtype_name(g.ab_dtype), dtype_name(g.c_dtype));
     B200_CHECK(g.batch <= 65535, "%s: batch %lld too large for the general kernel", name, (long long)g.batch);

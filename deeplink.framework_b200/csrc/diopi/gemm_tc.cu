@@ -241,7 +241,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after();
             const int row = mb * BM + quarter * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-            if (p.tma_store) {
+            if (mb * BM + quarter * 32 >= p.M) {
+                // this warp's 32 accumulator rows lie beyond the matrix (few-row products): nothing to read or store
+            } else if (p.tma_store) {
                 // One piece = 32 rows x 128 bytes (64 two-byte or 32 four-byte columns), double-buffered per warp.
                 constexpr int PIECE_COLS = 128 / static_cast<int>(sizeof(TOut));
                 constexpr int LOADS = PIECE_COLS / 32;

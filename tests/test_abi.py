@@ -73,3 +73,25 @@ def test_missing_library_is_an_import_error(tmp_path):
     else:
         raise AssertionError("loading without the libraries must fail")
     assert ctypes.sizeof(ctypes.c_void_p) == 8
+
+
+def test_torch_abi_library_has_dipu_devapis_signatures(pkg):
+    """The wrappers carry DIPU's mangled names: what `libtorch_dipu.so` links when built with -DDEVICE=b200."""
+    import subprocess
+    import torch  # noqa: F401  (libc10 / libtorch_cpu must be loadable)
+    lib = os.path.join(ROOT, "deeplink.framework_b200", "lib", "libdipu_vendor_b200_torchabi.so")
+    assert os.path.exists(lib), "build first"
+    syms = subprocess.run(["nm", "-DC", "--defined-only", lib], capture_output=True, text=True, check=True).stdout
+    for want in ("dipu::devapis::mallocDevice(void**, unsigned long, bool)",
+                 "dipu::devapis::createStream(CUstream_st**, bool)",
+                 "dipu::devapis::destroyStream(CUstream_st*, signed char)",
+                 "dipu::devapis::getEventStatus(CUevent_st*)",
+                 "dipu::devapis::memCopyD2DAsync(CUstream_st*, unsigned long, signed char, void*, signed char, void const*)",
+                 "dipu::devapis::diclAllReduce(void const*, void*, unsigned long, c10::ScalarType, c10d::ReduceOp const&, b200Comm*, CUstream_st*)",
+                 "dipu::devapis::diclCommInitRank(b200Comm**, int, b200UniqueId, int, int)",
+                 "dipu::devapis::diclAllToAllUnequalSplit(", "dipu::devapis::diclGetCommName(", "dipu::devapis::DICL_UNIQUE_ID_BYTES_SIZE"):
+        assert want in syms, want
+    handle = ctypes.CDLL(lib)
+    count = getattr(handle, "_ZN4dipu7devapis14getDeviceCountEv")
+    count.restype = ctypes.c_int
+    assert count() >= 0

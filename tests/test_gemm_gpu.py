@@ -178,9 +178,11 @@ def test_tc_addmm_epilogue(diopi, ctx):
 
 
 @pytest.mark.parametrize("m", [1, 2, 4, 8])
-def test_skinny_decode_attention(diopi, ctx, m):
-    """q*K^T and p*V over a KV cache, [B*h, m, D] x [B*h, D, L] and [B*h, m, L] x [B*h, L, D], cache slices with a capacity stride."""
-    bh, cap, length, d = 48, 640, 513, 128
+@pytest.mark.parametrize("length", [513, 512])
+def test_decode_attention_few_rows(diopi, ctx, m, length):
+    """q*K^T and p*V over a KV cache, [B*h, m, D] x [B*h, D, L] and [B*h, m, L] x [B*h, L, D], cache slices with a capacity stride.
+    Length 512 meets the TMA rules (tensor-core kernel); 513 makes the probability rows unaligned (skinny / general kernels)."""
+    bh, cap, d = 48, 640, 128
     kc, vc = rnd((bh, cap, d), torch.bfloat16, seed=1), rnd((bh, cap, d), torch.bfloat16, seed=2)
     q = rnd((bh, m, d), torch.bfloat16, seed=3)
     kd, vd = kc.to(DEV), vc.to(DEV)
