@@ -400,6 +400,26 @@ def main():
                 "peak_source": "%s bf16 cuBLAS, sustained (kernel timed inside a long step)" % peaks["source"],
                 "flops_per_launch": mm_flops / max(mm_calls, 1), "ms_per_launch": mm_ms / max(mm_calls, 1), "traffic": None}
 
+    # ---- variant: attention scores through one baddbmm (scale and mask-add in the GEMM epilogue) ----
+    # `value` above is the reference block's literal op order (bmm, div, add, softmax, bmm). A model written with
+    # torch.baddbmm(mask, q, k^T, alpha=1/sqrt(d)) reaches diopiBaddbmm instead; timed here with the same K steps.
+    for l_ in layers:
+        l_.scores_by_baddbmm = True
+    for _ in range(3):
+        step_resident()
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step_resident()
+    e1.record(stream)
+    barrier()
+    ms_badd = max_over_ranks(e0.elapsed_time(e1))
+    for l_ in layers:
+        l_.scores_by_baddbmm = False
+    variants = {"attention_scores_by_baddbmm": {"value": tokens * args.steps / (ms_badd * 1e-3), "unit": "tokens/s",
+                                                "ms_per_step": ms_badd / args.steps,
+                                                "note": "diopiBaddbmm(mask, q, k^T, beta=1, alpha=1/sqrt(d)) replaces diopiBmm + diopiDivInpScalar + diopiAddInp"}}
+
     # ---- secondary measurement: the same layer in decode (batch 64, KV length 4096) ----
     decode = None
     if not args.no_decode:
@@ -430,6 +450,7 @@ def main():
             "roofline": roofline,
             "layer_tflops": round((lin + attn) * args.steps / (ms_total * 1e-3) / 1e12, 1),
             "ops": ops,
+            "variants": variants,
             "decode": decode,
             "gemm_status": diopi.gemm_status(),
         }

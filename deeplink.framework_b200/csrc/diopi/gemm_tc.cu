@@ -65,6 +65,7 @@ struct TcParams {
     int c_vec_ok;
     int tma_store;  // epilogue writes through map_c
     int rotate_k;   // start each tile's K loop at a tile-dependent block (see the producer)
+    int bias_vec_ok;  // additive input: unit column stride, 16-byte aligned rows
     uint32_t* status;
 };
 
@@ -268,10 +269,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[l][j]) * p.alpha;
                         if (p.bias != nullptr && row < p.M) {
                             const TOut* brow = static_cast<const TOut*>(p.bias) + static_cast<int64_t>(b) * p.bias_sb + static_cast<int64_t>(row) * p.bias_sr;
+                            const int cbase = col0 + l * 32;
+                            if (p.bias_vec_ok && cbase + 32 <= p.N) {
+                                // dense row of the additive input (a [S, S] mask, a full matrix): 16-byte loads
+                                constexpr int BV = 16 / static_cast<int>(sizeof(TOut));
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                const int col = col0 + l * 32 + j;
-                                if (col < p.N) v[j] += p.beta * to_f32(brow[static_cast<int64_t>(col) * p.bias_sc]);
+                                for (int j = 0; j < 32; j += BV) {
+                                    const Vec16<TOut> bv = ld16(brow + cbase + j);
+#pragma unroll
+                                    for (int e = 0; e < BV; ++e) v[j + e] += p.beta * to_f32(bv.v[e]);
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) {
+                                    const int col = cbase + j;
+                                    if (col < p.N) v[j] += p.beta * to_f32(brow[static_cast<int64_t>(col) * p.bias_sc]);
+                                }
                             }
                         }
                         // 16-byte chunk k of row `lane` lives at chunk position k ^ (lane & 7): the 128-byte swizzle the
@@ -771,6 +784,8 @@ diopiError_t gemm_tc_launch(const GemmProblem& g, cudaStream_t stream) {
     }
     if (!p.tma_store) mc = ma;
     p.rotate_k = (m_blocks == 1 && p.k_blocks > 1) ? 1 : 0;
+    p.bias_vec_ok = (g.bias != nullptr && g.bias_sn == 1 && (reinterpret_cast<uintptr_t>(g.bias) & 15u) == 0 && (g.bias_sm * c_es) % 16 == 0 &&
+                     (g.bias_sb * c_es) % 16 == 0) ? 1 : 0;
     p.status = g.status_override != nullptr ? g.status_override : status_word();
     B200_CHECK(p.status != nullptr, "gemm: could not allocate the kernel status word");
     const int64_t total = static_cast<int64_t>(p.batch) * m_blocks * n_blocks;

@@ -90,6 +90,7 @@ class DecoderLayer:
         self.dtype, self.device = dtype, torch.device(device)
         self.tp_rank, self.tp_size, self.tp_group = tp_rank, tp_size, tp_group
         self.overlap_comm = True  # prefill: interleave two half-batches so the all-reduces overlap compute
+        self.scores_by_baddbmm = False  # prefill attention scores through one baddbmm instead of bmm, div, add
         d, r = self.head_dim, tp_rank
         hq, hk, f = self.heads, self.kv_heads, self.ffn
 
@@ -199,9 +200,15 @@ class DecoderLayer:
         self._call(diopi.diopiCopyInp, ctx, v.transpose(1, 2), vt)
         kt, vt = self._expand_kv(ctx, kt), self._expand_kv(ctx, vt)
         scores = self._empty(batch * hq, seq, seq)
-        self._call(diopi.diopiBmm, ctx, scores, qt.view(batch * hq, seq, d), kt.view(batch * hq, seq, d).transpose(1, 2))
-        self._call(diopi.diopiDivInpScalar, ctx, scores, math.sqrt(d), diopi.RoundModeNone)
-        self._call(diopi.diopiAddInp, ctx, scores, self._mask_for(ctx, seq), 1)
+        if self.scores_by_baddbmm:
+            # torch.baddbmm(mask, q, k^T, beta=1, alpha=1/sqrt(d)): scale and mask-add ride in the GEMM epilogue
+            self._call(diopi.diopiBaddbmm, ctx, scores, self._mask_for(ctx, seq), qt.view(batch * hq, seq, d),
+                       kt.view(batch * hq, seq, d).transpose(1, 2), 1.0, 1.0 / math.sqrt(d))
+        else:
+            # the reference block's order: matmul, / sqrt(d), + mask (dicp/test/model/llama/model.py:146-149)
+            self._call(diopi.diopiBmm, ctx, scores, qt.view(batch * hq, seq, d), kt.view(batch * hq, seq, d).transpose(1, 2))
+            self._call(diopi.diopiDivInpScalar, ctx, scores, math.sqrt(d), diopi.RoundModeNone)
+            self._call(diopi.diopiAddInp, ctx, scores, self._mask_for(ctx, seq), 1)
         self._call(diopi.diopiSoftmax, ctx, scores, scores, -1)
         av = self._empty(batch * hq, seq, d)
         self._call(diopi.diopiBmm, ctx, av, scores, vt.view(batch * hq, seq, d))

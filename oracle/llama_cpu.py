@@ -146,7 +146,7 @@ def stepwise(dtype):
     return lambda t: t.to(dtype).to(torch.float32)
 
 
-def attention_prefill(cfg, w, x, batch, seq, step=_identity):
+def attention_prefill(cfg, w, x, batch, seq, step=_identity, scores_by_baddbmm=False):
     t = batch * seq
     d = cfg.head_dim
     q = step(x @ w["wq"].t()).view(t, cfg.heads, d)
@@ -157,8 +157,12 @@ def attention_prefill(cfg, w, x, batch, seq, step=_identity):
     k = step(rotary(cfg, k, cos, sin)).view(batch, seq, cfg.kv_heads, d).transpose(1, 2)
     v = v.transpose(1, 2)
     k, v = _expand_kv(cfg, k), _expand_kv(cfg, v)
-    scores = step(step(torch.matmul(q, k.transpose(2, 3))) / math.sqrt(d))
-    scores = step(scores + causal_mask(seq))
+    if scores_by_baddbmm:
+        # torch.baddbmm(mask, q, k^T, beta=1, alpha=1/sqrt(d)): one rounding after scale and mask
+        scores = step(causal_mask(seq) + torch.matmul(q, k.transpose(2, 3)) * (1.0 / math.sqrt(d)))
+    else:
+        scores = step(step(torch.matmul(q, k.transpose(2, 3))) / math.sqrt(d))
+        scores = step(scores + causal_mask(seq))
     probs = step(torch.softmax(scores.float(), dim=-1))
     out = step(torch.matmul(probs, v)).transpose(1, 2).contiguous().view(t, cfg.heads * d)
     return step(out @ w["wo"].t())
@@ -169,15 +173,15 @@ def feed_forward(w, x, step=_identity):
     return step(step(gate * step(x @ w["w3"].t())) @ w["w2"].t())
 
 
-def decoder_layer_prefill_from_hidden(cfg, w, x, batch, seq, step=_identity):
-    h = step(x + attention_prefill(cfg, w, step(rms_norm(x, w["attention_norm"], cfg.eps)), batch, seq, step))
+def decoder_layer_prefill_from_hidden(cfg, w, x, batch, seq, step=_identity, scores_by_baddbmm=False):
+    h = step(x + attention_prefill(cfg, w, step(rms_norm(x, w["attention_norm"], cfg.eps)), batch, seq, step, scores_by_baddbmm))
     return step(h + feed_forward(w, step(rms_norm(h, w["ffn_norm"], cfg.eps)), step))
 
 
-def decoder_layer_prefill(cfg, w, embedding, ids, step=_identity):
+def decoder_layer_prefill(cfg, w, embedding, ids, step=_identity, scores_by_baddbmm=False):
     """ids [B, S] int64 -> layer output [B*S, hidden] float32."""
     batch, seq = ids.shape
-    return decoder_layer_prefill_from_hidden(cfg, w, embedding[ids.reshape(-1)], batch, seq, step)
+    return decoder_layer_prefill_from_hidden(cfg, w, embedding[ids.reshape(-1)], batch, seq, step, scores_by_baddbmm)
 
 
 def decoder_layer_decode(cfg, w, x, k_cache, v_cache, position, step=_identity):

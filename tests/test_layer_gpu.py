@@ -34,8 +34,9 @@ def test_c1_fp32_layer_matches_reference_block(pkg):
     np.testing.assert_allclose(y.cpu().numpy().reshape(1, 128, 512), g["y"], rtol=1e-3, atol=2e-5)
 
 
+@pytest.mark.parametrize("baddbmm", [False, True])
 @pytest.mark.parametrize("kv_heads", [8, 2])
-def test_bf16_prefill_layer(pkg, kv_heads):
+def test_bf16_prefill_layer(pkg, kv_heads, baddbmm):
     from dipu_b200 import layer as L
     cfg = llama_cpu.LayerConfig(hidden=1024, heads=8, kv_heads=kv_heads, head_dim=128, ffn=2752, eps=1e-6)
     w = llama_cpu.make_weights(cfg, seed=21)
@@ -43,8 +44,9 @@ def test_bf16_prefill_layer(pkg, kv_heads):
     ids = llama_cpu.make_token_ids(2, 256, seed=21)
     wr, er = llama_cpu.round_weights(w, torch.bfloat16), llama_cpu.round_tensor(emb, torch.bfloat16)
     ref32 = llama_cpu.decoder_layer_prefill(cfg, wr, er, ids)
-    ref16 = llama_cpu.decoder_layer_prefill(cfg, wr, er, ids, step=llama_cpu.stepwise(torch.bfloat16))
+    ref16 = llama_cpu.decoder_layer_prefill(cfg, wr, er, ids, step=llama_cpu.stepwise(torch.bfloat16), scores_by_baddbmm=baddbmm)
     lay = L.DecoderLayer(cfg, w, dtype=torch.bfloat16, device=DEV)
+    lay.scores_by_baddbmm = baddbmm  # attention scores by one baddbmm (scale and mask in the GEMM epilogue) or bmm, div, add
     y = lay.prefill(L.embed(emb.to(torch.bfloat16).to(DEV), ids.to(DEV)), 2, 256)
     torch.cuda.synchronize()
     assert pkg.diopi.gemm_status() == 0
