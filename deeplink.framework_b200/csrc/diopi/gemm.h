@@ -3,6 +3,8 @@
 
 #include "common.h"
 
+struct CUtensorMap_st;  // the driver API's tensor-map descriptor (cuda.h)
+
 namespace b200 {
 
 // C[b,m,n] = alpha * sum_k A[b,m,k] * B[b,k,n] + beta * bias[b,m,n]; all strides in elements.
@@ -27,5 +29,14 @@ struct GemmProblem {
 // tcgen05 / TMEM / TMA kernel (bf16 or fp16 operands, fp32 accumulation).
 bool gemm_tc_eligible(const GemmProblem& g);
 diopiError_t gemm_tc_launch(const GemmProblem& g, cudaStream_t stream);
+
+// CTA-pair variant (cta_group::2, 256 x 256 tiles) for large products; gemm_tc_launch hands over to it when it applies.
+bool gemm_tc2_applies(const GemmProblem& g);
+diopiError_t gemm_tc2_launch(const GemmProblem& g, cudaStream_t stream);
+
+// Shared by the tensor-core translation units.
+bool tc_encode_map(::CUtensorMap_st* map, diopiDtype_t dtype, const void* base, int64_t inner, int64_t rows, int64_t batch, int64_t row_pitch_elems,
+                   int64_t batch_pitch_elems, int box_rows);
+uint32_t* tc_status_word();
 
 }  // namespace b200

@@ -680,6 +680,12 @@ bool plan_splitk(const GemmProblem& g, int sms, int* bn_out, int* splits_out) {
 
 }  // namespace
 
+bool tc_encode_map(::CUtensorMap_st* map, diopiDtype_t dtype, const void* base, int64_t inner, int64_t rows, int64_t batch, int64_t row_pitch_elems,
+                   int64_t batch_pitch_elems, int box_rows) {
+    return encode_map(reinterpret_cast<CUtensorMap*>(map), dtype, base, inner, rows, batch, row_pitch_elems, batch_pitch_elems, box_rows);
+}
+uint32_t* tc_status_word() { return status_word(); }
+
 bool gemm_tc_eligible(const GemmProblem& g) {
     if (!(g.ab_dtype == diopi_dtype_bfloat16 || g.ab_dtype == diopi_dtype_float16)) return false;
     if (!(g.c_dtype == g.ab_dtype || g.c_dtype == diopi_dtype_float32)) return false;
@@ -719,6 +725,7 @@ diopiError_t gemm_tc_launch(const GemmProblem& g, cudaStream_t stream) {
     while (bn > min_bn && (g.N <= bn / 2 || g.batch * m_blocks * ((g.N + bn - 1) / bn) < sms)) bn >>= 1;
     const int64_t n_blocks = (g.N + bn - 1) / bn;
 
+    if (gemm_tc2_applies(g)) return gemm_tc2_launch(g, stream);
     int sk_bn = 0, sk_splits = 0;
     if (plan_splitk(g, sms, &sk_bn, &sk_splits)) {
         const bool b_mn_sk = b_mn;

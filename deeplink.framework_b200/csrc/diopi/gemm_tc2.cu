@@ -1,0 +1,378 @@
+// Dense contraction on CTA pairs (tcgen05 cta_group::2): C[b] = alpha * A[b] * B[b] + beta * bias, for large products.
+//
+// Two CTAs on neighbouring SMs (a cluster of 2) own one 256 x 256 output tile. Each CTA loads only its half of the
+// operands per K step - A rows [r*128, r*128+128) and B rows (N) [r*128, r*128+128), 32 KiB instead of the 48 KiB a
+// single CTA needs for a 128 x 256 tile - so the same shared memory holds 6 stages instead of 4 (more latency cover)
+// and each operand byte staged feeds twice the math. One thread of the leader CTA (cluster rank 0) issues
+// tcgen05.mma.cta_group::2 with M = 256: the hardware reads A and B from both CTAs' shared memory at the same offsets
+// and accumulates 128 rows x 256 fp32 columns into each CTA's tensor memory. Each CTA runs its own epilogue on its rows.
+//
+// Hand-over (all waits bounded, see gemm_sm100.cuh):
+//   full[s]   (leader's)  both CTAs' TMA loads count their bytes on the leader's barrier; the leader arms it with the
+//                         pair's total byte count. Plain per-CTA loads: no cluster multicast anywhere.
+//   empty[s]  (each CTA)  the leader commits the MMAs that read stage s to its own and to the partner's barrier
+//   acc_full  (each CTA)  the leader commits the tile's last MMA to both CTAs' barriers
+//   acc_empty (leader's)  the 8 epilogue warps of the pair arrive (the partner's remotely) when an accumulator is drained
+#include <cuda.h>
+
+#include <cstdlib>
+
+#include "device_utils.cuh"
+#include "gemm.h"
+#include "gemm_sm100.cuh"
+
+namespace b200 {
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128;      // rows per CTA
+constexpr int BN = 256;      // tile columns (128 of them staged per CTA)
+constexpr int BNH = BN / 2;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr int kGroupM = 8;   // in units of 256-row pair blocks
+constexpr int kABytes = BM * BK * 2;
+constexpr int kBBytes = BNH * BK * 2;
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kStoreBytes = 4 * 2 * 32 * 128;
+constexpr int kStages = 6;
+constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 + 512;
+static_assert(kSmemBytes <= 232448, "shared memory budget");
+
+struct PairParams {
+    int M, N, K, batch;
+    int m_pairs, n_blocks, k_blocks;
+    int64_t ldc, stride_cb;
+    void* C;
+    const void* bias;
+    int64_t bias_sb, bias_sr, bias_sc;
+    float alpha, beta;
+    uint32_t idesc;
+    int b_mn_major;
+    int bias_vec_ok;
+    uint32_t* status;
+};
+
+__device__ __forceinline__ void pair_tile_coords(int tile, const PairParams& p, int* b, int* mp, int* nb) {
+    const int per_batch = p.m_pairs * p.n_blocks;
+    *b = tile / per_batch;
+    const int t = tile - *b * per_batch;
+    const int group_sz = kGroupM * p.n_blocks;
+    const int g = t / group_sz;
+    const int first = g * kGroupM;
+    const int rows = min(p.m_pairs - first, kGroupM);
+    const int r = t - g * group_sz;
+    *mp = first + r % rows;
+    *nb = r / rows;
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
+                    const PairParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + kStages * kABytes;
+    uint8_t* smem_c = smem + kStages * kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_c + kStoreBytes);
+    uint64_t* full_bar = bars;                    // [kStages] used in the leader only
+    uint64_t* empty_bar = bars + kStages;         // [kStages] one set per CTA
+    uint64_t* acc_full = bars + 2 * kStages;      // [2] one set per CTA
+    uint64_t* acc_empty = bars + 2 * kStages + 2; // [2] used in the leader only
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();  // 0 = leader
+    const int cluster_id = blockIdx.x >> 1;
+    const int num_clusters = gridDim.x >> 1;
+    const int total_tiles = p.batch * p.m_pairs * p.n_blocks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full_bar[s], 1);   // the leader's arrive.expect_tx; bytes from both CTAs
+            mbar_init(&empty_bar[s], 1);  // one commit from the leader
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_empty[a], 8);  // 4 epilogue warps in each CTA of the pair
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        prefetch_tensormap(&map_c);
+    }
+    __syncthreads();
+    // barriers of both CTAs must exist before either CTA signals the other's
+    cluster_sync_all();
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // shared::cluster addresses of the leader's barriers and of the partner's copies of the per-CTA ones
+    const uint32_t leader_full0 = map_to_cta(smem_u32(&full_bar[0]), 0);
+    const uint32_t leader_acc_empty0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs: each loads its own halves) ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < total_tiles && ok; tile += num_clusters) {
+                int b, mp, nb;
+                pair_tile_coords(tile, p, &b, &mp, &nb);
+                const int row0 = mp * (2 * BM) + static_cast<int>(rank) * BM;
+                const int col0 = nb * BN + static_cast<int>(rank) * BNH;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+                    if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kStageBytes);
+                    const uint32_t bar = leader_full0 + stage * 8;
+                    tma_load_3d_pair(smem_a + stage * kABytes, &map_a, bar, kb * BK, row0, b);
+                    if (!p.b_mn_major) {
+                        tma_load_3d_pair(smem_b + stage * kBBytes, &map_b, bar, kb * BK, col0, b);
+                    } else {
+#pragma unroll
+                        for (int g = 0; g < BNH / 64; ++g) {
+                            tma_load_3d_pair(smem_b + stage * kBBytes + g * (64 * BK * 2), &map_b, bar, col0 + g * 64, kb * BK, b);
+                        }
+                    }
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (lane == 0 && rank == 0) {
+            const uint32_t peer_empty0 = map_to_cta(smem_u32(&empty_bar[0]), 1);
+            const uint32_t peer_acc_full0 = map_to_cta(smem_u32(&acc_full[0]), 1);
+            const uint32_t own_empty0 = map_to_cta(smem_u32(&empty_bar[0]), 0);
+            const uint32_t own_acc_full0 = map_to_cta(smem_u32(&acc_full[0]), 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < total_tiles && ok; tile += num_clusters, ++local) {
+                const int acc = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1u;
+                if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem_a + stage * kABytes);
+                    const uint32_t b_addr = smem_u32(smem_b + stage * kBBytes);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t da = make_smem_desc_sw128(a_addr + k * (UMMA_K * 2), 16, 1024);
+                        const uint64_t db = p.b_mn_major ? make_smem_desc_sw128(b_addr + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                                         : make_smem_desc_sw128(b_addr + k * (UMMA_K * 2), 16, 1024);
+                        umma_f16_ss_pair(d_tmem, da, db, p.idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    // the stage is free in both CTAs once these MMAs have read it
+                    umma_commit_pair(own_empty0 + stage * 8);
+                    umma_commit_pair(peer_empty0 + stage * 8);
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) {
+                    umma_commit_pair(own_acc_full0 + acc * 8);
+                    umma_commit_pair(peer_acc_full0 + acc * 8);
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5 of both CTAs, each CTA on its own 128 rows) ----------------
+        const int quarter = warp & 3;
+        int local = 0;
+        uint32_t store_seq = 0;
+        bool ok = true;
+        constexpr int PIECE_COLS = 128 / static_cast<int>(sizeof(TOut));
+        constexpr int LOADS = PIECE_COLS / 32;
+        uint8_t* stage_base = smem_c + (warp - 2) * (2 * 32 * 128);
+        for (int tile = cluster_id; tile < total_tiles && ok; tile += num_clusters, ++local) {
+            int b, mp, nb;
+            pair_tile_coords(tile, p, &b, &mp, &nb);
+            const int acc = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1u;
+            if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const int row_base = mp * (2 * BM) + static_cast<int>(rank) * BM + quarter * 32;
+            const int row = row_base + lane;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+            if (row_base < p.M) {
+#pragma unroll 1
+                for (int c = 0; c < BN / PIECE_COLS; ++c) {
+                    const int col0 = nb * BN + c * PIECE_COLS;
+                    if (col0 >= p.N) break;  // warp-uniform
+                    uint8_t* buf = stage_base + (store_seq & 1) * (32 * 128);
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
+                    uint32_t r[LOADS][32];
+#pragma unroll
+                    for (int l = 0; l < LOADS; ++l) tmem_ld_32x32(t_row + c * PIECE_COLS + l * 32, r[l]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int l = 0; l < LOADS; ++l) {
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[l][j]) * p.alpha;
+                        if (p.bias != nullptr && row < p.M) {
+                            const TOut* brow = static_cast<const TOut*>(p.bias) + static_cast<int64_t>(b) * p.bias_sb + static_cast<int64_t>(row) * p.bias_sr;
+                            const int cbase = col0 + l * 32;
+                            if (p.bias_vec_ok && cbase + 32 <= p.N) {
+                                constexpr int BV = 16 / static_cast<int>(sizeof(TOut));
+#pragma unroll
+                                for (int j = 0; j < 32; j += BV) {
+                                    const Vec16<TOut> bv = ld16(brow + cbase + j);
+#pragma unroll
+                                    for (int e = 0; e < BV; ++e) v[j + e] += p.beta * to_f32(bv.v[e]);
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) {
+                                    const int col = cbase + j;
+                                    if (col < p.N) v[j] += p.beta * to_f32(brow[static_cast<int64_t>(col) * p.bias_sc]);
+                                }
+                            }
+                        }
+                        constexpr int V = 16 / static_cast<int>(sizeof(TOut));
+#pragma unroll
+                        for (int j = 0; j < 32; j += V) {
+                            Vec16<TOut> o;
+#pragma unroll
+                            for (int e = 0; e < V; ++e) o.v[e] = from_f32<TOut>(v[j + e]);
+                            const int chunk = (l * 32 + j) / V;
+                            *reinterpret_cast<uint4*>(buf + lane * 128 + ((chunk ^ (lane & 7)) * 16)) = *reinterpret_cast<const uint4*>(&o);
+                        }
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_3d(&map_c, buf, col0, row_base, b);
+                        tma_store_commit();
+                    }
+                    ++store_seq;
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_acc_empty0 + acc * 8);
+        }
+        if (lane == 0) tma_store_wait_all<0>();
+    }
+
+    // ---------------- teardown: every thread of both CTAs comes through here, also after a timed-out wait ----------------
+    tc_fence_before();
+    __syncthreads();
+    __syncwarp();
+    cluster_sync_all();  // the partner's shared / tensor memory is in use by the leader's MMAs until both are done
+    tc_fence_after();
+    if (*abort_flag != 0) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+        if (threadIdx.x == 0) atomicExch(p.status, 1u);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+}
+
+template <typename TOut>
+cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const PairParams& p, int grid, cudaStream_t stream) {
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<TOut>, ma, mb, mc, p);
+}
+
+}  // namespace
+
+// Large products with a TMA-storable output: at least two 256-row blocks and enough 256 x 256 tiles to fill the SM pairs.
+bool gemm_tc2_applies(const GemmProblem& g) {
+    static const bool disabled = std::getenv("B200_GEMM_NO_PAIR") != nullptr;
+    if (disabled) return false;
+    if (g.M < 256 || g.N < 256 || g.K < 256) return false;
+    const int64_t c_es = dtype_size(g.c_dtype);
+    const bool c_ok = (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0 && (g.c_sm * c_es) % 16 == 0 && (g.batch == 1 || (g.c_sb * c_es) % 16 == 0);
+    if (!c_ok) return false;
+    const int64_t tiles = g.batch * ((g.M + 255) / 256) * ((g.N + 255) / 256);
+    return tiles >= sm_count() / 2 && tiles <= 0x3fffffffLL;
+}
+
+diopiError_t gemm_tc2_launch(const GemmProblem& g, cudaStream_t stream) {
+    const bool is_bf16 = g.ab_dtype == diopi_dtype_bfloat16;
+    const bool b_mn = g.b_sk != 1;
+    CUtensorMap ma, mb, mc;
+    B200_CHECK(tc_encode_map(&ma, g.ab_dtype, g.A, g.K, g.M, g.batch, g.a_sm, g.batch > 1 ? g.a_sb : g.a_sm * g.M, BM),
+               "gemm: cuTensorMapEncodeTiled failed for A");
+    if (!b_mn) {
+        B200_CHECK(tc_encode_map(&mb, g.ab_dtype, g.B, g.K, g.N, g.batch, g.b_sn, g.batch > 1 ? g.b_sb : g.b_sn * g.N, BNH),
+                   "gemm: cuTensorMapEncodeTiled failed for B (K-major)");
+    } else {
+        B200_CHECK(tc_encode_map(&mb, g.ab_dtype, g.B, g.N, g.K, g.batch, g.b_sk, g.batch > 1 ? g.b_sb : g.b_sk * g.K, BK),
+                   "gemm: cuTensorMapEncodeTiled failed for B (MN-major)");
+    }
+    B200_CHECK(tc_encode_map(&mc, g.c_dtype, g.C, g.N, g.M, g.batch, g.c_sm, g.batch > 1 ? g.c_sb : g.c_sm * g.M, 32),
+               "gemm: cuTensorMapEncodeTiled failed for C");
+    PairParams p;
+    p.M = static_cast<int>(g.M); p.N = static_cast<int>(g.N); p.K = static_cast<int>(g.K); p.batch = static_cast<int>(g.batch);
+    p.m_pairs = static_cast<int>((g.M + 2 * BM - 1) / (2 * BM));
+    p.n_blocks = static_cast<int>((g.N + BN - 1) / BN);
+    p.k_blocks = static_cast<int>((g.K + BK - 1) / BK);
+    p.ldc = g.c_sm; p.stride_cb = g.c_sb; p.C = g.C;
+    p.bias = g.bias; p.bias_sb = g.bias_sb; p.bias_sr = g.bias_sm; p.bias_sc = g.bias_sn;
+    p.alpha = g.alpha; p.beta = g.beta;
+    p.idesc = make_idesc_f16(is_bf16 ? 1 : 0, b_mn, 2 * BM, BN);
+    p.b_mn_major = b_mn ? 1 : 0;
+    const int64_t c_es = dtype_size(g.c_dtype);
+    p.bias_vec_ok = (g.bias != nullptr && g.bias_sn == 1 && (reinterpret_cast<uintptr_t>(g.bias) & 15u) == 0 && (g.bias_sm * c_es) % 16 == 0 &&
+                     (g.bias_sb * c_es) % 16 == 0) ? 1 : 0;
+    p.status = g.status_override != nullptr ? g.status_override : tc_status_word();
+    B200_CHECK(p.status != nullptr, "gemm: could not allocate the kernel status word");
+    const int64_t total = static_cast<int64_t>(p.batch) * p.m_pairs * p.n_blocks;
+    int64_t clusters = sm_count() / 2;
+    if (clusters > total) clusters = total;
+    const int grid = static_cast<int>(clusters * 2);
+    cudaError_t e;
+    if (g.c_dtype == diopi_dtype_bfloat16) e = launch_pair<bf16>(ma, mb, mc, p, grid, stream);
+    else if (g.c_dtype == diopi_dtype_float16) e = launch_pair<fp16>(ma, mb, mc, p, grid, stream);
+    else e = launch_pair<float>(ma, mb, mc, p, grid, stream);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        B200_FAIL("gemm: tcgen05 pair kernel launch failed: %s", cudaGetErrorString(e));
+    }
+    return diopiSuccess;
+}
+
+}  // namespace b200

@@ -132,6 +132,38 @@ def test_tc_split_k_single_row_block(diopi, ctx, m, n, k, nk):
     assert diopi.gemm_status() == 0
 
 
+@pytest.mark.parametrize("m,n,k,nk,batch", [(2048, 4096, 512, True, 1), (3000, 2600, 264, True, 1), (2048, 4096, 320, False, 1),
+                                            (1000, 4136, 256, False, 1), (512, 512, 256, True, 40), (512, 640, 256, False, 24)])
+def test_tc_cta_pair_tiles(diopi, ctx, m, n, k, nk, batch):
+    """Products large enough for the CTA-pair kernel (256 x 256 tiles over two SMs): ragged edges, both B layouts, batches,
+    scaled / biased epilogue, fp32 output."""
+    shape_a = (batch, m, k) if batch > 1 else (m, k)
+    shape_b = ((batch, n, k) if nk else (batch, k, n)) if batch > 1 else ((n, k) if nk else (k, n))
+    a = rnd(shape_a, torch.bfloat16, seed=m + k)
+    b = rnd(shape_b, torch.bfloat16, seed=n, scale=0.05)
+    bt = b.float().transpose(-1, -2) if nk else b.float()
+    ref = torch.matmul(a.float(), bt)
+    ad, bd = a.to(DEV), b.to(DEV)
+    bv = bd.transpose(-1, -2) if nk else bd
+    out = torch.empty(ref.shape, dtype=torch.bfloat16, device=DEV)
+    if batch > 1:
+        diopi.diopiBmm(ctx, out, ad, bv)
+    else:
+        diopi.diopiMm(ctx, out, ad, bv)
+    check_lowp(out, ref)
+    if batch == 1:
+        bias = rnd((m, n), torch.float32, seed=7)
+        o32 = torch.empty((m, n), dtype=torch.float32, device=DEV)
+        diopi.diopiAddmm(ctx, o32, bias.to(DEV), ad, bv, 0.5, 2.0)
+        check_lowp(o32, 0.5 * bias + 2.0 * ref, rel_l2=1e-4, max_rel=1e-4)
+    else:
+        mask = rnd((m, n), torch.bfloat16, seed=8)
+        ob = torch.empty(ref.shape, dtype=torch.bfloat16, device=DEV)
+        diopi.diopiBaddbmm(ctx, ob, mask.to(DEV), ad, bv, 1.0, 0.25)
+        check_lowp(ob, mask.float() + 0.25 * ref)
+    assert diopi.gemm_status() == 0
+
+
 def test_tc_linearity_and_identity(diopi, ctx):
     """Size-independent properties at a large shape: A*I == A bit for bit, and (A1 + A2)*B == A1*B + A2*B within rounding."""
     m, n = 4096, 4096
