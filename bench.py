@@ -420,6 +420,24 @@ def main():
                                                 "ms_per_step": ms_badd / args.steps,
                                                 "note": "diopiBaddbmm(mask, q, k^T, beta=1, alpha=1/sqrt(d)) replaces diopiBmm + diopiDivInpScalar + diopiAddInp"}}
 
+    # ---- variant: attention through the fused operator (diopiMultiHeadAttention: no score tensor, no transposes) ----
+    for l_ in layers:
+        l_.fused_attention = True
+    for _ in range(3):
+        step_resident()
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step_resident()
+    e1.record(stream)
+    barrier()
+    ms_fused = max_over_ranks(e0.elapsed_time(e1))
+    for l_ in layers:
+        l_.fused_attention = False
+    variants["fused_attention"] = {"value": tokens * args.steps / (ms_fused * 1e-3), "unit": "tokens/s", "ms_per_step": ms_fused / args.steps,
+                                   "note": "diopiMultiHeadAttention (causal) replaces the transposes, diopiBmm, diopiDivInpScalar, diopiAddInp, "
+                                           "diopiSoftmax, diopiBmm of the attention core"}
+
     # ---- secondary measurement: the same layer in decode (batch 64, KV length 4096) ----
     decode = None
     if not args.no_decode:

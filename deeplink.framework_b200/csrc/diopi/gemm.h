@@ -37,6 +37,14 @@ diopiError_t gemm_tc2_launch(const GemmProblem& g, cudaStream_t stream);
 // Shared by the tensor-core translation units.
 bool tc_encode_map(::CUtensorMap_st* map, diopiDtype_t dtype, const void* base, int64_t inner, int64_t rows, int64_t batch, int64_t row_pitch_elems,
                    int64_t batch_pitch_elems, int box_rows);
+// dims = {inner, d1, d2, d3} (innermost first), pitch_elems = pitches of d1, d2, d3; box = {128 bytes, box1, box2, 1}.
+bool tc_encode_map4(::CUtensorMap_st* map, diopiDtype_t dtype, const void* base, const int64_t dims[4], const int64_t pitch_elems[3], int box1,
+                    int box2);
 uint32_t* tc_status_word();
+
+// Fused attention (attention.cu).
+bool attention_prefill_applies(const TensorView& q, const TensorView& k, const TensorView& v, const TensorView& out);
+diopiError_t attention_prefill_launch(const TensorView& q, const TensorView& k, const TensorView& v, const TensorView& out, const TensorView* lse,
+                                      bool causal, double scale, cudaStream_t stream);
 
 }  // namespace b200

@@ -684,6 +684,24 @@ bool tc_encode_map(::CUtensorMap_st* map, diopiDtype_t dtype, const void* base, 
                    int64_t batch_pitch_elems, int box_rows) {
     return encode_map(reinterpret_cast<CUtensorMap*>(map), dtype, base, inner, rows, batch, row_pitch_elems, batch_pitch_elems, box_rows);
 }
+// 4-D map over a [d3, d2, d1, inner] view (pitches in elements) with a [1, box2, box1, 128 bytes] box and 128-byte swizzle.
+bool tc_encode_map4(::CUtensorMap_st* map, diopiDtype_t dtype, const void* base, const int64_t dims[4], const int64_t pitch_elems[3], int box1,
+                    int box2) {
+    EncodeFn fn = get_encode_fn();
+    if (fn == nullptr) return false;
+    const int es = dtype == diopi_dtype_float32 ? 4 : 2;
+    const CUtensorMapDataType dt = dtype == diopi_dtype_float32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                   : (dtype == diopi_dtype_bfloat16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+    const cuuint64_t d[4] = {static_cast<cuuint64_t>(dims[0]), static_cast<cuuint64_t>(dims[1]), static_cast<cuuint64_t>(dims[2]),
+                             static_cast<cuuint64_t>(dims[3])};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(pitch_elems[0] * es), static_cast<cuuint64_t>(pitch_elems[1] * es),
+                                   static_cast<cuuint64_t>(pitch_elems[2] * es)};
+    const cuuint32_t box[4] = {static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(box1), static_cast<cuuint32_t>(box2), 1u};
+    const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    const CUresult r = fn(reinterpret_cast<CUtensorMap*>(map), dt, 4, const_cast<void*>(base), d, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
 uint32_t* tc_status_word() { return status_word(); }
 
 bool gemm_tc_eligible(const GemmProblem& g) {

@@ -155,6 +155,7 @@ SIGNATURES = {
     "diopiMm": "Ttt", "diopiAddmm": "Ttttss", "diopiBmm": "Ttt", "diopiBaddbmm": "Ttttdd", "diopiBaddbmmInp": "Tttdd", "diopiMatmul": "Ttt",
     "diopiLinear": "Tttt",
     "diopiRMSNorm": "TTtzttd", "diopiRotaryEmbedding": "Ttttbb",
+    "diopiMultiHeadAttention": "TTTdbbdTttt",
 }
 
 _CTYPES = {"T": ctypes.c_void_p, "t": ctypes.c_void_p, "s": ctypes.POINTER(_Scalar), "i": ctypes.c_int64, "d": ctypes.c_double,

@@ -91,6 +91,7 @@ class DecoderLayer:
         self.tp_rank, self.tp_size, self.tp_group = tp_rank, tp_size, tp_group
         self.overlap_comm = True  # prefill: interleave two half-batches so the all-reduces overlap compute
         self.scores_by_baddbmm = False  # prefill attention scores through one baddbmm instead of bmm, div, add
+        self.fused_attention = False  # prefill attention through the fused operator (no score tensor, no transposes)
         d, r = self.head_dim, tp_rank
         hq, hk, f = self.heads, self.kv_heads, self.ffn
 
@@ -193,6 +194,11 @@ class DecoderLayer:
         cos, sin = self._tables_for(("prefill", seq), torch.arange(seq))
         q = self._rope(ctx, q, cos, sin).view(batch, seq, hq, d)
         k = self._rope(ctx, k, cos, sin).view(batch, seq, hk, d)
+        if self.fused_attention and d == 128 and self.dtype in (torch.bfloat16, torch.float16):
+            # one call on the [B, S, h, D] views: grouped heads share K / V inside the kernel, output lands merged
+            merged = self._empty(batch, seq, hq, d)
+            self._call(diopi.diopiMultiHeadAttention, ctx, q, k, v, 0.0, True, False, 1.0 / math.sqrt(d), merged, None, None, None)
+            return self._linear(ctx, merged.view(t, hq * d), self.wo)
         # [B, S, h, D] -> [B, h, S, D]: .transpose(1, 2).contiguous() is a copy_ from a strided view
         qt, kt, vt = self._empty(batch, hq, seq, d), self._empty(batch, hk, seq, d), self._empty(batch, hk, seq, d)
         self._call(diopi.diopiCopyInp, ctx, q.transpose(1, 2), qt)

@@ -192,9 +192,37 @@ def gemm_case(case, diopi, ctx, dev):
     return fns, flops, per_set
 
 
+# (label, batch, seq, heads, kv_heads, causal): fused attention, head dim 128
+ATTENTION_CASES = [
+    ("prefill 7B causal", 8, 2048, 32, 32, True),
+    ("prefill 7B full", 8, 2048, 32, 32, False),
+    ("prefill 70B-shaped TP8 shard causal", 4, 4096, 8, 1, True),
+    ("prefill long causal", 1, 16384, 32, 32, True),
+]
+
+
+def attention_case(case, diopi, ctx, dev):
+    label, b, s, h, hk, causal = case
+    bf = torch.bfloat16
+    g = torch.Generator(device=dev)
+    g.manual_seed(b * s + h)
+    per_set = 2 * b * s * 128 * (2 * h + 2 * hk)
+    sets = int(max(1, min(8, math.ceil(2.0 * L2_BYTES / per_set))))
+    fns = []
+    for _ in range(sets):
+        q = torch.randn((b, s, h, 128), generator=g, device=dev, dtype=torch.float32).to(bf)
+        k = torch.randn((b, s, hk, 128), generator=g, device=dev, dtype=torch.float32).to(bf)
+        v = torch.randn((b, s, hk, 128), generator=g, device=dev, dtype=torch.float32).to(bf)
+        out = torch.empty_like(q)
+        fns.append(lambda q=q, k=k, v=v, out=out: diopi.diopiMultiHeadAttention(ctx, q, k, v, 0.0, causal, False, 128 ** -0.5, out, None, None, None))
+    # products actually needed: 4*d flop per visible (query, key) pair
+    pairs = b * h * (s * (s + 1) // 2 if causal else s * s)
+    return fns, 4.0 * 128 * pairs, per_set
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ops", default="all", help="comma list of: %s, gemm" % ", ".join(MEM_OPS))
+    ap.add_argument("--ops", default="all", help="comma list of: %s, gemm, attention" % ", ".join(MEM_OPS))
     ap.add_argument("--tokens", default="1,64,1024,16384,65536")
     ap.add_argument("--gemm", default="all", help="comma list of indices into the GEMM case table, or 'all'")
     ap.add_argument("--iters", type=int, default=50)
@@ -210,9 +238,20 @@ def main():
     stream = torch.cuda.current_stream()
     ctx = diopi.Context(stream=stream.cuda_stream, device=0)
     hbm, tflops, src = peaks()
-    ops = MEM_OPS + ["gemm"] if args.ops == "all" else args.ops.split(",")
+    ops = MEM_OPS + ["gemm", "attention"] if args.ops == "all" else args.ops.split(",")
     tokens = [int(x) for x in args.tokens.split(",")]
     for op in ops:
+        if op == "attention":
+            for case in ATTENTION_CASES:
+                fns, flops, per_set = attention_case(case, diopi, ctx, dev)
+                ms = time_cases(fns, max(5, args.iters // 2), stream)
+                rec = {"op": "attention", "case": case[0], "batch": case[1], "seq": case[2], "heads": case[3], "kv_heads": case[4], "causal": case[5],
+                       "ms": round(ms, 4), "tflops_visible_pairs": round(flops / (ms * 1e-3) / 1e12, 2),
+                       "frac_of_%s_bf16_burst" % src: round(flops / (ms * 1e-3) / 1e12 / tflops, 4), "gbs": round(per_set / (ms * 1e-3) / 1e9, 1)}
+                print(json.dumps(rec), flush=True)
+                del fns
+                ctx.release_workspace()
+            continue
         if op == "gemm":
             idx = range(len(GEMM_CASES)) if args.gemm == "all" else [int(x) for x in args.gemm.split(",")]
             for i in idx:

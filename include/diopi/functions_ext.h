@@ -34,6 +34,18 @@ DIOPI_API diopiError_t diopiRotaryEmbedding(diopiContextHandle_t ctx, diopiTenso
                                             diopiConstTensorHandle_t cos, diopiConstTensorHandle_t sin, const bool conj,
                                             const bool interleaved);
 
+/* Fused scaled-dot-product attention (inference): out = softmax(scale * q k^T [+ causal mask]) v.
+ * Fused form of the bmm / div / add(mask) / softmax / bmm sequence of dicp/test/model/llama/model.py:146-150; the
+ * reference's CPU restatement of the fused operator is dicp/dicp/vendor/AscendGraph/ext_ops.py:52-86.
+ * Prototype provisional ("signature unpinned": the DIOPI header is not part of the reference snapshot).
+ * q [batch, seq_q, heads, dim]; k, v [batch, seq_kv, kv_heads, dim] with heads % kv_heads == 0 (grouped heads share
+ * K / V); out like q; views with any pitches and a unit innermost pitch are taken as they are (no copies).
+ * is_causal: key j is visible to query i iff j <= i + (seq_kv - seq_q). dropout_p must be 0, return_debug_mask false,
+ * gen and debug_attn_mask NULL. softmax_lse: optional float32 [batch, heads, seq_q], log of the softmax denominator. */
+DIOPI_API diopiError_t diopiMultiHeadAttention(diopiContextHandle_t ctx, diopiTensorHandle_t q, diopiTensorHandle_t k, diopiTensorHandle_t v,
+                                               double dropout_p, bool is_causal, bool return_debug_mask, double scale, diopiTensorHandle_t out,
+                                               diopiTensorHandle_t softmax_lse, diopiGeneratorHandle_t gen, diopiTensorHandle_t debug_attn_mask);
+
 #ifdef __cplusplus
 }
 #endif

@@ -133,6 +133,29 @@ def _expand_kv(cfg, t):
     return t if g == 1 else t.repeat_interleave(g, dim=1)
 
 
+def fused_attention(q, k, v, causal, scale=None):
+    """The fused attention operator restated on CPU in fp32: q [B, Sq, H, D], k / v [B, Skv, Hkv, D] -> [B, Sq, H, D].
+    Follows dicp/dicp/vendor/AscendGraph/ext_ops.py:52-86 (prompt_attention_inference: scores / sqrt(d), additive
+    causal mask, softmax, times V, heads of a group sharing K / V) and dicp/test/model/llama/model.py:146-150.
+    With Sq != Skv the causal mask is aligned to the last key: key j is visible to query i iff j <= i + Skv - Sq
+    (ext_ops.py:89-126, flash_attention_inference, is the Sq = 1 case: every cached key is visible).
+    Returns (out, lse) with lse [B, H, Sq] the natural log of the softmax denominator."""
+    b, sq, h, d = q.shape
+    skv, hk = k.shape[1], k.shape[2]
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    qf = q.float().transpose(1, 2)
+    kf = k.float().transpose(1, 2).repeat_interleave(h // hk, dim=1)
+    vf = v.float().transpose(1, 2).repeat_interleave(h // hk, dim=1)
+    scores = torch.matmul(qf, kf.transpose(2, 3)) * scale
+    if causal:
+        i = torch.arange(sq).view(sq, 1)
+        j = torch.arange(skv).view(1, skv)
+        scores = scores.masked_fill(j > i + (skv - sq), float("-inf"))
+    lse = torch.logsumexp(scores, dim=-1)
+    out = torch.matmul(torch.softmax(scores, dim=-1), vf).transpose(1, 2).contiguous()
+    return out, lse
+
+
 # ---- the layer --------------------------------------------------------------------------------------------------------
 # `step` is applied wherever the eager op stream materialises a tensor. The identity gives the fp32 oracle. Rounding to
 # bf16 there (step=stepwise(torch.bfloat16)) gives what the reference's literal CPU fallback produces on bf16 tensors:
