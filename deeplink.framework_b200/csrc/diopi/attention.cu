@@ -513,6 +513,362 @@ bool attention_prefill_applies(const TensorView& q, const TensorView& k, const T
 
 }  // namespace b200
 
+// ---- decode: one query row per (batch, head) against a long key / value cache ------------------------------------------------
+// Bound by reading K and V once from HBM (2 * Skv * 256 bytes per K/V head); the arithmetic is a few flop per byte, so it
+// runs on the CUDA cores with every load a full 16-byte vector. This is the fused form of
+// dicp/dicp/vendor/AscendGraph/ext_ops.py:89-126 (flash_attention_inference: bmm, / sqrt(d), softmax, bmm per sequence).
+//
+// A CTA owns one (batch, K/V head, slice of keys) and up to GT query heads of the group that shares that K/V head.
+// Eight lanes cover one key row (16 elements = 32 bytes each), so a warp handles four keys per step and the CTA's eight
+// warps 32; each lane keeps a running maximum, denominator and a 16-column slice of the output per head, merged across
+// lanes (shuffles) and warps (shared memory) at the end. With more than one key slice the partial results go to a
+// workspace and a second kernel merges them.
+namespace b200 {
+namespace {
+
+constexpr int kDecThreads = 256;
+constexpr int kDecKeysPerStep = 32;   // 8 warps x 4 keys
+
+struct DecodeParams {
+    const void* q;
+    const void* k;
+    const void* v;
+    void* out;
+    int64_t q_sb, q_sh;            // element pitches
+    int64_t k_sb, k_ss, k_sh;
+    int64_t v_sb, v_ss, v_sh;
+    int64_t o_sb, o_sh;
+    int Hq, Hkv, group;            // group = Hq / Hkv
+    int Skv;
+    int splits, keys_per_split;    // keys_per_split is a multiple of kDecKeysPerStep
+    float scale_log2;
+    float* part;                   // [B * Hq, splits, 130] (m, l, 128 columns) when splits > 1
+    float* lse;                    // optional
+    int64_t lse_sb, lse_sh;
+};
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]);
+template <>
+__device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4& w, float (&f)[8]) {
+    // bf16 -> fp32 is a 16-bit shift
+    f[0] = __uint_as_float(w.x << 16); f[1] = __uint_as_float(w.x & 0xffff0000u);
+    f[2] = __uint_as_float(w.y << 16); f[3] = __uint_as_float(w.y & 0xffff0000u);
+    f[4] = __uint_as_float(w.z << 16); f[5] = __uint_as_float(w.z & 0xffff0000u);
+    f[6] = __uint_as_float(w.w << 16); f[7] = __uint_as_float(w.w & 0xffff0000u);
+}
+template <>
+__device__ __forceinline__ void unpack8<__half>(const uint4& w, float (&f)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&w);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __half22float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+
+__device__ __forceinline__ uint4 ldg16_stream(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.cs.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
+
+// Merge (m_b, l_b, acc_b) into (m_a, l_a, acc_a): two partial softmax results over disjoint key sets.
+template <int N>
+__device__ __forceinline__ void merge_partial(float& m_a, float& l_a, float (&acc_a)[N], float m_b, float l_b, const float (&acc_b)[N]) {
+    const float m = fmaxf(m_a, m_b);
+    const float fa = (m_a == -INFINITY) ? 0.f : fast_exp2(m_a - m);
+    const float fb = (m_b == -INFINITY) ? 0.f : fast_exp2(m_b - m);
+    l_a = l_a * fa + l_b * fb;
+#pragma unroll
+    for (int i = 0; i < N; ++i) acc_a[i] = acc_a[i] * fa + acc_b[i] * fb;
+    m_a = m;
+}
+
+template <typename T, int GT, int U>
+__global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const DecodeParams p) {
+    __shared__ float red[8][GT][130];
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int sub = lane >> 3;   // which of the warp's four keys
+    const int col = lane & 7;    // 16-column slice of the row
+    const int head_tiles = p.group / GT;
+    int idx = blockIdx.x;
+    const int ht = idx % head_tiles;
+    idx /= head_tiles;
+    const int hk = idx % p.Hkv;
+    const int b = idx / p.Hkv;
+    const int h0 = hk * p.group + ht * GT;
+    const int split = blockIdx.y;
+    const int key_begin = split * p.keys_per_split;
+    const int key_end = min(p.Skv, key_begin + p.keys_per_split);
+
+    float qf[GT][16];
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+        const T* qrow = static_cast<const T*>(p.q) + static_cast<int64_t>(b) * p.q_sb + static_cast<int64_t>(h0 + g) * p.q_sh + col * 16;
+        float lo[8], hi[8];
+        unpack8<T>(*reinterpret_cast<const uint4*>(qrow), lo);
+        unpack8<T>(*reinterpret_cast<const uint4*>(qrow + 8), hi);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            qf[g][i] = lo[i] * p.scale_log2;
+            qf[g][8 + i] = hi[i] * p.scale_log2;
+        }
+    }
+    float m_run[GT], l_run[GT], acc[GT][16];
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+        m_run[g] = -INFINITY;
+        l_run[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[g][i] = 0.f;
+    }
+    const T* kbase = static_cast<const T*>(p.k) + static_cast<int64_t>(b) * p.k_sb + static_cast<int64_t>(hk) * p.k_sh + col * 16;
+    const T* vbase = static_cast<const T*>(p.v) + static_cast<int64_t>(b) * p.v_sb + static_cast<int64_t>(hk) * p.v_sh + col * 16;
+
+    // the loop bound is warp-uniform (the shuffles below need the whole warp); lanes past the end are masked
+    for (int base0 = key_begin + warp * 4; base0 < key_end; base0 += kDecKeysPerStep * U) {
+        const int key0 = base0 + sub;
+        uint4 kw[U][2], vw[U][2];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int key = key0 + u * kDecKeysPerStep;
+            const int kc = min(key, key_end - 1);  // clamp: rows past the end are loaded from a valid address and masked
+            const T* kr = kbase + static_cast<int64_t>(kc) * p.k_ss;
+            kw[u][0] = ldg16_stream(kr);
+            kw[u][1] = ldg16_stream(kr + 8);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int key = key0 + u * kDecKeysPerStep;
+            const int kc = min(key, key_end - 1);
+            const T* vr = vbase + static_cast<int64_t>(kc) * p.v_ss;
+            vw[u][0] = ldg16_stream(vr);
+            vw[u][1] = ldg16_stream(vr + 8);
+        }
+        float sc[U][GT];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            float kf[16];
+            {
+                float lo[8], hi[8];
+                unpack8<T>(kw[u][0], lo);
+                unpack8<T>(kw[u][1], hi);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { kf[i] = lo[i]; kf[8 + i] = hi[i]; }
+            }
+            const bool valid = key0 + u * kDecKeysPerStep < key_end;
+#pragma unroll
+            for (int g = 0; g < GT; ++g) {
+                float d = 0.f;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) d = fmaf(qf[g][i], kf[i], d);
+                d += __shfl_xor_sync(0xffffffffu, d, 1);
+                d += __shfl_xor_sync(0xffffffffu, d, 2);
+                d += __shfl_xor_sync(0xffffffffu, d, 4);
+                sc[u][g] = valid ? d : -INFINITY;
+            }
+        }
+        float pr[U][GT];
+#pragma unroll
+        for (int g = 0; g < GT; ++g) {
+            float mx = sc[0][g];
+#pragma unroll
+            for (int u = 1; u < U; ++u) mx = fmaxf(mx, sc[u][g]);
+            const float m_new = fmaxf(m_run[g], mx);
+            const float base = (m_new == -INFINITY) ? 0.f : m_new;
+            const float factor = (m_run[g] == -INFINITY) ? 0.f : fast_exp2(m_run[g] - base);
+            m_run[g] = m_new;
+            float add = 0.f;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                pr[u][g] = fast_exp2(sc[u][g] - base);
+                add += pr[u][g];
+            }
+            l_run[g] = l_run[g] * factor + add;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[g][i] *= factor;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            float vf[16];
+            {
+                float lo[8], hi[8];
+                unpack8<T>(vw[u][0], lo);
+                unpack8<T>(vw[u][1], hi);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { vf[i] = lo[i]; vf[8 + i] = hi[i]; }
+            }
+#pragma unroll
+            for (int g = 0; g < GT; ++g) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[g][i] = fmaf(pr[u][g], vf[i], acc[g][i]);
+            }
+        }
+    }
+
+    // ---- merge the four key sub-groups of the warp (lanes 8 and 16 apart hold the same columns) ----
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+#pragma unroll
+        for (int off = 8; off <= 16; off <<= 1) {
+            const float m_o = __shfl_xor_sync(0xffffffffu, m_run[g], off);
+            const float l_o = __shfl_xor_sync(0xffffffffu, l_run[g], off);
+            float a_o[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) a_o[i] = __shfl_xor_sync(0xffffffffu, acc[g][i], off);
+            merge_partial<16>(m_run[g], l_run[g], acc[g], m_o, l_o, a_o);
+        }
+        if (sub == 0) {
+            if (col == 0) {
+                red[warp][g][0] = m_run[g];
+                red[warp][g][1] = l_run[g];
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) red[warp][g][2 + col * 16 + i] = acc[g][i];
+        }
+    }
+    __syncthreads();
+    // ---- merge the eight warps: one thread per (head, column) ----
+    for (int item = threadIdx.x; item < GT * 128; item += kDecThreads) {
+        const int g = item >> 7;
+        const int c = item & 127;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) m = fmaxf(m, red[w][g][0]);
+        float l = 0.f, a = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            const float mw = red[w][g][0];
+            const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - m);
+            l += red[w][g][1] * f;
+            a += red[w][g][2 + c] * f;
+        }
+        const int h = h0 + g;
+        if (p.splits == 1) {
+            T* orow = static_cast<T*>(p.out) + static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(h) * p.o_sh;
+            orow[c] = from_f32<T>(l > 0.f ? a / l : 0.f);
+            if (c == 0 && p.lse != nullptr) {
+                p.lse[static_cast<int64_t>(b) * p.lse_sb + static_cast<int64_t>(h) * p.lse_sh] = l > 0.f ? m * 0.6931471805599453f + logf(l) : -INFINITY;
+            }
+        } else {
+            float* dst = p.part + (static_cast<int64_t>(b * p.Hq + h) * p.splits + split) * 130;
+            if (c == 0) {
+                dst[0] = m;
+                dst[1] = l;
+            }
+            dst[2 + c] = a;
+        }
+    }
+}
+
+// Merges the key slices of one (batch, head): 128 threads, one per output column.
+template <typename T>
+__global__ void __launch_bounds__(128) attn_decode_merge_kernel(const DecodeParams p) {
+    const int bh = blockIdx.x;
+    const int b = bh / p.Hq;
+    const int h = bh - b * p.Hq;
+    const int c = threadIdx.x;
+    const float* src = p.part + static_cast<int64_t>(bh) * p.splits * 130;
+    float m = -INFINITY;
+    for (int s = 0; s < p.splits; ++s) m = fmaxf(m, src[s * 130]);
+    float l = 0.f, a = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+        const float ms = src[s * 130];
+        const float f = (ms == -INFINITY) ? 0.f : fast_exp2(ms - m);
+        l += src[s * 130 + 1] * f;
+        a += src[s * 130 + 2 + c] * f;
+    }
+    T* orow = static_cast<T*>(p.out) + static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(h) * p.o_sh;
+    orow[c] = from_f32<T>(l > 0.f ? a / l : 0.f);
+    if (c == 0 && p.lse != nullptr) {
+        p.lse[static_cast<int64_t>(b) * p.lse_sb + static_cast<int64_t>(h) * p.lse_sh] = l > 0.f ? m * 0.6931471805599453f + logf(l) : -INFINITY;
+    }
+}
+
+template <typename T>
+void launch_decode(const DecodeParams& p, int gt, int batch, dim3 grid, cudaStream_t stream) {
+    switch (gt) {
+        case 4: attn_decode_kernel<T, 4, 2><<<grid, kDecThreads, 0, stream>>>(p); break;
+        case 2: attn_decode_kernel<T, 2, 4><<<grid, kDecThreads, 0, stream>>>(p); break;
+        default: attn_decode_kernel<T, 1, 4><<<grid, kDecThreads, 0, stream>>>(p); break;
+    }
+    if (p.splits > 1) attn_decode_merge_kernel<T><<<p.Hq * batch, 128, 0, stream>>>(p);
+}
+
+bool rows_viewable(const TensorView& t) {
+    if (t.ndim != 4 || t.stride[3] != 1 || !t.aligned(16)) return false;
+    for (int d = 0; d < 3; ++d) {
+        if (t.shape[d] != 1 && (t.stride[d] < 0 || (t.stride[d] * 2) % 16 != 0)) return false;
+    }
+    return true;
+}
+
+}  // namespace
+
+bool attention_decode_applies(const TensorView& q, const TensorView& k, const TensorView& v, const TensorView& out) {
+    if (!(q.dtype == diopi_dtype_bfloat16 || q.dtype == diopi_dtype_float16)) return false;
+    if (k.dtype != q.dtype || v.dtype != q.dtype || out.dtype != q.dtype) return false;
+    if (q.shape[1] != 1 || q.shape[3] != 128) return false;
+    return rows_viewable(q) && rows_viewable(k) && rows_viewable(v) && rows_viewable(out);
+}
+
+diopiError_t attention_decode_launch(diopiContextHandle_t ctx, const TensorView& q, const TensorView& k, const TensorView& v, const TensorView& out,
+                                     const TensorView* lse, double scale, cudaStream_t stream) {
+    DecodeParams p = {};
+    p.q = q.data; p.k = k.data; p.v = v.data; p.out = out.data;
+    p.q_sb = q.stride[0]; p.q_sh = q.stride[2];
+    p.k_sb = k.stride[0]; p.k_ss = k.stride[1]; p.k_sh = k.stride[2];
+    p.v_sb = v.stride[0]; p.v_ss = v.stride[1]; p.v_sh = v.stride[2];
+    p.o_sb = out.stride[0]; p.o_sh = out.stride[2];
+    const int B = static_cast<int>(q.shape[0]);
+    p.Hq = static_cast<int>(q.shape[2]);
+    p.Hkv = static_cast<int>(k.shape[2]);
+    p.group = p.Hq / p.Hkv;
+    p.Skv = static_cast<int>(k.shape[1]);
+    p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
+    if (lse != nullptr) {
+        p.lse = static_cast<float*>(lse->data);
+        p.lse_sb = lse->stride[0];
+        p.lse_sh = lse->stride[1];
+    }
+    const int gt = p.group % 4 == 0 ? 4 : (p.group % 2 == 0 ? 2 : 1);
+    const int64_t ctas = static_cast<int64_t>(B) * p.Hkv * (p.group / gt);
+    B200_CHECK(ctas > 0 && ctas < 0x7fffffffLL, "attention: grid out of range");
+    // enough CTAs for about four per SM, but no slice shorter than 256 keys
+    const int sms = sm_count();
+    int splits = 1;
+    if (ctas < 4 * sms) {
+        const int64_t want = (4 * static_cast<int64_t>(sms) + ctas - 1) / ctas;
+        const int64_t most = (p.Skv + 255) / 256;
+        splits = static_cast<int>(want < most ? want : most);
+        if (splits < 1) splits = 1;
+        if (splits > 65535) splits = 65535;
+    }
+    int per = (p.Skv + splits - 1) / splits;
+    per = (per + kDecKeysPerStep - 1) / kDecKeysPerStep * kDecKeysPerStep;
+    splits = (p.Skv + per - 1) / per;
+    p.splits = splits;
+    p.keys_per_split = per;
+    if (splits > 1) {
+        diopiTensorHandle_t ws = nullptr;
+        const int64_t bytes = static_cast<int64_t>(B) * p.Hq * splits * 130 * static_cast<int64_t>(sizeof(float));
+        B200_CHECK(diopiRequireBuffer(ctx, &ws, bytes, diopi_device) == diopiSuccess && ws != nullptr, "attention: workspace allocation failed");
+        void* ptr = nullptr;
+        B200_CHECK(diopiGetTensorData(ws, &ptr) == diopiSuccess && ptr != nullptr, "attention: workspace has no data pointer");
+        p.part = static_cast<float*>(ptr);
+    }
+    const dim3 grid(static_cast<unsigned>(ctas), static_cast<unsigned>(splits));
+    if (q.dtype == diopi_dtype_bfloat16) launch_decode<__nv_bfloat16>(p, gt, B, grid, stream);
+    else launch_decode<__half>(p, gt, B, grid, stream);
+    B200_LAUNCH_CHECK("attention decode");
+    return diopiSuccess;
+}
+
+}  // namespace b200
+
 // q [B, Sq, Hq, D], k / v [B, Skv, Hkv, D], out [B, Sq, Hq, D]; any pitches with a unit innermost one.
 extern "C" DIOPI_API diopiError_t diopiMultiHeadAttention(diopiContextHandle_t ctx, diopiTensorHandle_t q, diopiTensorHandle_t k, diopiTensorHandle_t v,
                                                          double dropout_p, bool is_causal, bool return_debug_mask, double scale,
@@ -549,6 +905,7 @@ extern "C" DIOPI_API diopiError_t diopiMultiHeadAttention(diopiContextHandle_t c
         lse = &vl;
     }
     cudaStream_t stream = b200::stream_of(ctx);
+    if (b200::attention_decode_applies(vq, vk, vv, vo)) return b200::attention_decode_launch(ctx, vq, vk, vv, vo, lse, scale, stream);
     B200_CHECK(b200::attention_prefill_applies(vq, vk, vv, vo),
                "diopiMultiHeadAttention: needs bf16 / fp16 operands of one dtype, head dim 128, unit innermost pitch, other pitches "
                "multiples of 8 elements and 16-byte aligned bases");

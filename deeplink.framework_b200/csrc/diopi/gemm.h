@@ -47,4 +47,8 @@ bool attention_prefill_applies(const TensorView& q, const TensorView& k, const T
 diopiError_t attention_prefill_launch(const TensorView& q, const TensorView& k, const TensorView& v, const TensorView& out, const TensorView* lse,
                                       bool causal, double scale, cudaStream_t stream);
 
+bool attention_decode_applies(const TensorView& q, const TensorView& k, const TensorView& v, const TensorView& out);
+diopiError_t attention_decode_launch(diopiContextHandle_t ctx, const TensorView& q, const TensorView& k, const TensorView& v, const TensorView& out,
+                                     const TensorView* lse, double scale, cudaStream_t stream);
+
 }  // namespace b200

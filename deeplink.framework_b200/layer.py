@@ -299,6 +299,18 @@ class DecoderLayer:
         self._call(diopi.diopiCopyInp, ctx, k, k_cache[:, :, position, :])
         self._call(diopi.diopiCopyInp, ctx, v, v_cache[:, :, position, :])
         keys, vals = k_cache[:, :, :length, :], v_cache[:, :, :length, :]
+        if self.fused_attention and d == 128 and self.dtype in (torch.bfloat16, torch.float16):
+            # one call on views of the cache ([B, L, kv heads, D] by pitches): K and V are read once, grouped heads share them
+            av = self._empty(b, 1, hq, d)
+            self._call(diopi.diopiMultiHeadAttention, ctx, q.view(b, 1, hq, d), keys.transpose(1, 2), vals.transpose(1, 2), 0.0, False, False,
+                       1.0 / math.sqrt(d), av, None, None, None)
+            attn = self._linear(ctx, av.view(b, hq * d), self.wo)
+            self._all_reduce(ctx, attn)
+            h = self._like(x)
+            self._call(diopi.diopiAdd, ctx, h, x, attn, 1)
+            out = self._ffn(ctx, h)
+            ctx.release_workspace()
+            return out
         if hq != hk:
             keys, vals = self._expand_kv(ctx, keys), self._expand_kv(ctx, vals)
         cap = keys.shape[2] if hq != hk else k_cache.shape[2]

@@ -169,13 +169,19 @@ def stepwise(dtype):
     return lambda t: t.to(dtype).to(torch.float32)
 
 
-def attention_prefill(cfg, w, x, batch, seq, step=_identity, scores_by_baddbmm=False):
+def attention_prefill(cfg, w, x, batch, seq, step=_identity, scores_by_baddbmm=False, fused=False):
     t = batch * seq
     d = cfg.head_dim
     q = step(x @ w["wq"].t()).view(t, cfg.heads, d)
     k = step(x @ w["wk"].t()).view(t, cfg.kv_heads, d)
     v = step(x @ w["wv"].t()).view(batch, seq, cfg.kv_heads, d)
     cos, sin = rope_tables(d, torch.arange(seq), cfg.rope_base)
+    if fused:
+        # the attention core as ONE materialising op (the fused operator): rounding only where it writes its output
+        qb = step(rotary(cfg, q, cos, sin)).view(batch, seq, cfg.heads, d)
+        kb = step(rotary(cfg, k, cos, sin)).view(batch, seq, cfg.kv_heads, d)
+        out = step(fused_attention(qb, kb, v, True)[0]).view(t, cfg.heads * d)
+        return step(out @ w["wo"].t())
     q = step(rotary(cfg, q, cos, sin)).view(batch, seq, cfg.heads, d).transpose(1, 2)
     k = step(rotary(cfg, k, cos, sin)).view(batch, seq, cfg.kv_heads, d).transpose(1, 2)
     v = v.transpose(1, 2)
@@ -196,18 +202,18 @@ def feed_forward(w, x, step=_identity):
     return step(step(gate * step(x @ w["w3"].t())) @ w["w2"].t())
 
 
-def decoder_layer_prefill_from_hidden(cfg, w, x, batch, seq, step=_identity, scores_by_baddbmm=False):
-    h = step(x + attention_prefill(cfg, w, step(rms_norm(x, w["attention_norm"], cfg.eps)), batch, seq, step, scores_by_baddbmm))
+def decoder_layer_prefill_from_hidden(cfg, w, x, batch, seq, step=_identity, scores_by_baddbmm=False, fused=False):
+    h = step(x + attention_prefill(cfg, w, step(rms_norm(x, w["attention_norm"], cfg.eps)), batch, seq, step, scores_by_baddbmm, fused))
     return step(h + feed_forward(w, step(rms_norm(h, w["ffn_norm"], cfg.eps)), step))
 
 
-def decoder_layer_prefill(cfg, w, embedding, ids, step=_identity, scores_by_baddbmm=False):
+def decoder_layer_prefill(cfg, w, embedding, ids, step=_identity, scores_by_baddbmm=False, fused=False):
     """ids [B, S] int64 -> layer output [B*S, hidden] float32."""
     batch, seq = ids.shape
-    return decoder_layer_prefill_from_hidden(cfg, w, embedding[ids.reshape(-1)], batch, seq, step, scores_by_baddbmm)
+    return decoder_layer_prefill_from_hidden(cfg, w, embedding[ids.reshape(-1)], batch, seq, step, scores_by_baddbmm, fused)
 
 
-def decoder_layer_decode(cfg, w, x, k_cache, v_cache, position, step=_identity):
+def decoder_layer_decode(cfg, w, x, k_cache, v_cache, position, step=_identity, fused=False):
     """One new token per sequence. x [B, hidden]; caches [B, kv_heads, L, D] whose slot `position` is overwritten by the
     new token's key / value; attention covers slots 0..position. Returns (out [B, hidden], k_cache, v_cache)."""
     b = x.shape[0]
@@ -223,6 +229,13 @@ def decoder_layer_decode(cfg, w, x, k_cache, v_cache, position, step=_identity):
     v_cache = v_cache.clone()
     k_cache[:, :, position, :] = k
     v_cache[:, :, position, :] = v
+    if fused:
+        kb = k_cache[:, :, : position + 1, :].transpose(1, 2)
+        vb = v_cache[:, :, : position + 1, :].transpose(1, 2)
+        ctx = step(fused_attention(q.unsqueeze(1), kb, vb, False)[0]).reshape(b, cfg.heads * d)
+        h = step(x + step(ctx @ w["wo"].t()))
+        out = step(h + feed_forward(w, step(rms_norm(h, w["ffn_norm"], cfg.eps)), step))
+        return out, k_cache, v_cache
     keys = _expand_kv(cfg, k_cache[:, :, : position + 1, :])
     vals = _expand_kv(cfg, v_cache[:, :, : position + 1, :])
     scores = step(step(torch.matmul(q.unsqueeze(2), keys.transpose(2, 3))) / math.sqrt(d))  # [B, heads, 1, L]

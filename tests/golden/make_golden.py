@@ -14,6 +14,9 @@ stub that answers "cpu") and records, for seeded inputs:
     ext_ops.npz      the half-split rotary and the fused rms_norm exactly as written in
                      dicp/dicp/vendor/AscendGraph/ext_ops.py:24-33,47-49 (that file cannot be imported without
                      torch_dipu, so the two three-line function bodies are exec'd from its source text)
+    ext_attention.npz  the fused attention operators of the same file (prompt_attention_inference :66-86,
+                     flash_attention_inference :100-126), exec'd the same way, on bf16-representable inputs
+                     (`python tests/golden/make_golden.py attention` regenerates only this file)
 
 Weights are NOT stored (12 MB): they are regenerated from the numpy seed by oracle.llama_cpu.make_weights, and a
 checksum of them is stored instead. The tests never read the reference checkout; only this script does.
@@ -56,6 +59,39 @@ def load_ext_ops_bodies():
         m = re.search(r"^def %s\(.*?(?=^\S)" % fn, src, re.S | re.M)
         exec(m.group(0), ns)
     return ns["lightllm_rotary_emb_impl"], ns["lightllm_rms_norm_impl"]
+
+
+def load_ext_attention_bodies():
+    import math
+    import torch.nn.functional as F
+    src = open(os.path.join(REF, "dicp", "dicp", "vendor", "AscendGraph", "ext_ops.py")).read()
+    ns = {"torch": torch, "math": math, "F": F}
+    for fn in ("lightllm_prompt_attention_inference_impl", "lightllm_flash_attention_inference_impl"):
+        m = re.search(r"^def %s\(.*?(?=^\S)" % fn, src, re.S | re.M)
+        exec(m.group(0), ns)
+    return ns["lightllm_prompt_attention_inference_impl"], ns["lightllm_flash_attention_inference_impl"]
+
+
+def make_attention_golden():
+    """ext_attention.npz: the reference's fused attention operators (ext_ops.py:66-86 prompt_attention_inference,
+    ext_ops.py:100-126 flash_attention_inference) on inputs that are exactly representable in bf16."""
+    torch.set_num_threads(1)
+    prompt, flash = load_ext_attention_bodies()
+    rng = np.random.default_rng(17)
+
+    def rn(*shape):
+        return torch.from_numpy(rng.standard_normal(shape, dtype=np.float32)).to(torch.bfloat16).float()
+
+    seq, heads, dim = 160, 4, 128
+    pq, pk, pv = rn(1, seq, heads * dim), rn(1, seq, heads * dim), rn(1, seq, heads * dim)
+    pout = prompt(pq, pk, pv, torch.tensor(seq), heads, dim, heads)          # [seq, heads, dim]
+    batch, cap = 3, 200
+    lens = [200, 77, 150]
+    fq, fk, fv = rn(batch, heads, dim), rn(cap, heads, dim), rn(cap, heads, dim)
+    fout = flash(fq, fk, fv, lens, cap, heads, heads, dim)                   # [batch, heads, dim]
+    np.savez_compressed(os.path.join(HERE, "ext_attention.npz"), prompt_q=pq.numpy(), prompt_k=pk.numpy(), prompt_v=pv.numpy(),
+                        prompt_out=pout.numpy(), flash_q=fq.numpy(), flash_k=fk.numpy(), flash_v=fv.numpy(),
+                        flash_lens=np.array(lens, dtype=np.int64), flash_out=fout.numpy())
 
 
 def weights_checksum(w):
@@ -119,4 +155,8 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) > 1 and sys.argv[1] == "attention":
+        make_attention_golden()   # only ext_attention.npz
+    else:
+        main()
+        make_attention_golden()

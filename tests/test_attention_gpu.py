@@ -85,6 +85,26 @@ def test_prefill_attention_large_scores(pkg, ctx):
     _check(pkg, ctx, q, k, v, False, q.to(DEV), k.to(DEV), v.to(DEV), scale=0.5)
 
 
+@pytest.mark.parametrize("b,length,h,hk", [(4, 300, 8, 8), (3, 1000, 8, 2), (2, 129, 8, 4), (1, 5000, 2, 2), (2, 1, 4, 4), (5, 33, 6, 2),
+                                           (1, 20000, 8, 1)])
+def test_decode_attention(pkg, ctx, b, length, h, hk):
+    """One query per sequence against a cache kept as [B, kv heads, capacity, D]: the kernel takes the [B, L, kv heads, D]
+    view of the filled part by its pitches. Few sequences exercise the split over keys and the merge kernel."""
+    cap = length + 17
+    q, k, v = _inputs(b, 1, cap, h, hk, 128, seed=length + h, dtype=torch.bfloat16)
+    kc = k.transpose(1, 2).contiguous().to(DEV)   # [B, hk, cap, D]
+    vc = v.transpose(1, 2).contiguous().to(DEV)
+    kd = kc[:, :, :length, :].transpose(1, 2)
+    vd = vc[:, :, :length, :].transpose(1, 2)
+    _check(pkg, ctx, q, k[:, :length], v[:, :length], False, q.to(DEV), kd, vd)
+
+
+def test_decode_attention_fp16_causal_flag(pkg, ctx):
+    """With one query the causal flag changes nothing: every cached key is visible."""
+    q, k, v = _inputs(3, 1, 700, 4, 4, 128, seed=2, dtype=torch.float16)
+    _check(pkg, ctx, q, k, v, True, q.to(DEV), k.to(DEV), v.to(DEV))
+
+
 def test_attention_rejects_what_it_cannot_run(pkg, ctx):
     q = torch.zeros(1, 16, 2, 64, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(pkg.diopi.DiopiError, match="head dim 128"):
@@ -95,3 +115,29 @@ def test_attention_rejects_what_it_cannot_run(pkg, ctx):
         pkg.diopi.diopiMultiHeadAttention(ctx, q, k, k, 0.0, True, False, 0.1, torch.empty_like(q), None, None, None)
     with pytest.raises(pkg.diopi.DiopiError, match="dropout"):
         pkg.diopi.diopiMultiHeadAttention(ctx, k, k, k, 0.1, True, False, 0.1, torch.empty_like(k), None, None, None)
+
+
+def test_attention_against_reference_golden(pkg, ctx):
+    """Inputs and outputs recorded from the reference's own fused operators (ext_ops.py:66-86,100-126): the inputs are
+    exactly representable in bf16, so only the kernel's arithmetic differs."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ext_attention.npz"))
+    seq, heads, dim = 160, 4, 128
+    bf = torch.bfloat16
+    q, k, v = (torch.from_numpy(g[n]).view(1, seq, heads, dim).to(bf).to(DEV) for n in ("prompt_q", "prompt_k", "prompt_v"))
+    out = torch.empty_like(q)
+    pkg.diopi.diopiMultiHeadAttention(ctx, q, k, v, 0.0, True, False, dim ** -0.5, out, None, None, None)
+    ref = torch.from_numpy(g["prompt_out"])
+    got = out[0].float().cpu()
+    assert (got - ref).abs().max().item() <= 2e-2 and ((got - ref).norm() / ref.norm()).item() <= 5e-3
+    fq, fk, fv = (torch.from_numpy(g[n]).to(bf).to(DEV) for n in ("flash_q", "flash_k", "flash_v"))
+    for i, length in enumerate(g["flash_lens"]):
+        length = int(length)
+        o = torch.empty(1, 1, heads, dim, dtype=bf, device=DEV)
+        pkg.diopi.diopiMultiHeadAttention(ctx, fq[i].view(1, 1, heads, dim), fk[:length].view(1, length, heads, dim),
+                                          fv[:length].view(1, length, heads, dim), 0.0, False, False, dim ** -0.5, o, None, None, None)
+        ref = torch.from_numpy(g["flash_out"][i])
+        got = o.view(heads, dim).float().cpu()
+        assert (got - ref).abs().max().item() <= 2e-2 and ((got - ref).norm() / ref.norm()).item() <= 5e-3
+    torch.cuda.synchronize()
+    assert pkg.diopi.gemm_status() == 0

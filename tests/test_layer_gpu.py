@@ -34,9 +34,10 @@ def test_c1_fp32_layer_matches_reference_block(pkg):
     np.testing.assert_allclose(y.cpu().numpy().reshape(1, 128, 512), g["y"], rtol=1e-3, atol=2e-5)
 
 
-@pytest.mark.parametrize("baddbmm", [False, True])
+@pytest.mark.parametrize("mode", ["literal", "baddbmm", "fused"])
 @pytest.mark.parametrize("kv_heads", [8, 2])
-def test_bf16_prefill_layer(pkg, kv_heads, baddbmm):
+def test_bf16_prefill_layer(pkg, kv_heads, mode):
+    baddbmm = mode == "baddbmm"
     from dipu_b200 import layer as L
     cfg = llama_cpu.LayerConfig(hidden=1024, heads=8, kv_heads=kv_heads, head_dim=128, ffn=2752, eps=1e-6)
     w = llama_cpu.make_weights(cfg, seed=21)
@@ -44,23 +45,30 @@ def test_bf16_prefill_layer(pkg, kv_heads, baddbmm):
     ids = llama_cpu.make_token_ids(2, 256, seed=21)
     wr, er = llama_cpu.round_weights(w, torch.bfloat16), llama_cpu.round_tensor(emb, torch.bfloat16)
     ref32 = llama_cpu.decoder_layer_prefill(cfg, wr, er, ids)
-    ref16 = llama_cpu.decoder_layer_prefill(cfg, wr, er, ids, step=llama_cpu.stepwise(torch.bfloat16), scores_by_baddbmm=baddbmm)
+    ref16 = llama_cpu.decoder_layer_prefill(cfg, wr, er, ids, step=llama_cpu.stepwise(torch.bfloat16), scores_by_baddbmm=baddbmm,
+                                            fused=mode == "fused")
     lay = L.DecoderLayer(cfg, w, dtype=torch.bfloat16, device=DEV)
     lay.scores_by_baddbmm = baddbmm  # attention scores by one baddbmm (scale and mask in the GEMM epilogue) or bmm, div, add
+    lay.fused_attention = mode == "fused"  # the attention core through diopiMultiHeadAttention
     y = lay.prefill(L.embed(emb.to(torch.bfloat16).to(DEV), ids.to(DEV)), 2, 256)
     torch.cuda.synchronize()
     assert pkg.diopi.gemm_status() == 0
     # against the op-by-op bf16 CPU path (what the reference's CPU fallback computes on bf16 tensors): the stated tolerance
     max_abs, rel = _err(y, ref16)
-    assert max_abs <= 2e-2 and rel <= 5e-3, (max_abs, rel)
+    # The fused operator rounds its probabilities at another point than any CPU evaluation can (unnormalised, against a
+    # running maximum); every later bf16 rounding of the layer then falls differently. Two CPU evaluations of this layer
+    # that differ only in where the probabilities are rounded are 6.9e-3 apart on this input, so the whole-layer bound for
+    # the fused mode is the one used against fp32; the operator itself is held to 5e-3 in test_attention_gpu.py.
+    assert max_abs <= 2e-2 and rel <= (1e-2 if mode == "fused" else 5e-3), (max_abs, rel)
     # against the all-fp32 CPU layer: ~25 chained bf16 roundings compound, so the whole-layer relative bound is 1e-2
     # (the CPU bf16 path itself sits at 7.6e-3 from fp32 on this input); the max-abs bound is the stated one
     max_abs, rel = _err(y, ref32)
     assert max_abs <= 2e-2 and rel <= 1e-2, (max_abs, rel)
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("kv_heads", [8, 4])
-def test_bf16_decode_layer(pkg, kv_heads):
+def test_bf16_decode_layer(pkg, kv_heads, fused):
     from dipu_b200 import layer as L
     cfg = llama_cpu.LayerConfig(hidden=1024, heads=8, kv_heads=kv_heads, head_dim=128, ffn=2752, eps=1e-6)
     w = llama_cpu.make_weights(cfg, seed=31)
@@ -71,8 +79,9 @@ def test_bf16_decode_layer(pkg, kv_heads):
     bf = torch.bfloat16
     args = (cfg, llama_cpu.round_weights(w, bf), llama_cpu.round_tensor(x, bf), llama_cpu.round_tensor(kc, bf), llama_cpu.round_tensor(vc, bf), pos)
     ref, kref, vref = llama_cpu.decoder_layer_decode(*args)
-    ref16, _, _ = llama_cpu.decoder_layer_decode(*args, step=llama_cpu.stepwise(bf))
+    ref16, _, _ = llama_cpu.decoder_layer_decode(*args, step=llama_cpu.stepwise(bf), fused=fused)
     lay = L.DecoderLayer(cfg, w, dtype=bf, device=DEV)
+    lay.fused_attention = fused
     kd, vd = kc.to(bf).to(DEV), vc.to(bf).to(DEV)
     y = lay.decode(x.to(bf).to(DEV), kd, vd, pos)
     torch.cuda.synchronize()

@@ -112,3 +112,30 @@ def test_tensor_parallel_shards_sum_to_full_layer():
     ff = llama_cpu.feed_forward(w, hn)
     fparts = [llama_cpu.feed_forward(llama_cpu.shard_weights(cfg, w, r, 2), hn) for r in range(2)]
     np.testing.assert_allclose((fparts[0] + fparts[1]).numpy(), ff.numpy(), rtol=1e-4, atol=1e-6)
+
+
+def test_fused_attention_matches_reference_ext_ops():
+    """The restated fused attention against the reference's own prompt_attention_inference / flash_attention_inference
+    (dicp/dicp/vendor/AscendGraph/ext_ops.py:66-86,100-126), recorded in ext_attention.npz."""
+    g = np.load(os.path.join(GOLD, "ext_attention.npz"))
+    seq, heads, dim = 160, 4, 128
+    q, k, v = (torch.from_numpy(g[n]).view(1, seq, heads, dim) for n in ("prompt_q", "prompt_k", "prompt_v"))
+    out, lse = llama_cpu.fused_attention(q, k, v, True)
+    np.testing.assert_allclose(out[0].numpy(), g["prompt_out"], rtol=1e-5, atol=2e-6)
+    assert lse.shape == (1, heads, seq)
+    fq, fk, fv = (torch.from_numpy(g[n]) for n in ("flash_q", "flash_k", "flash_v"))
+    for i, length in enumerate(g["flash_lens"]):
+        length = int(length)
+        out, _ = llama_cpu.fused_attention(fq[i].view(1, 1, heads, dim), fk[:length].view(1, length, heads, dim),
+                                           fv[:length].view(1, length, heads, dim), False)
+        np.testing.assert_allclose(out.view(heads, dim).numpy(), g["flash_out"][i], rtol=1e-5, atol=2e-6)
+
+
+def test_fused_attention_equals_op_by_op_attention():
+    """The fused restatement and the bmm / softmax sequence of the layer agree in fp32 (grouped heads included)."""
+    cfg = llama_cpu.LayerConfig(hidden=256, heads=4, kv_heads=2, head_dim=64, ffn=512, eps=1e-6)
+    w = llama_cpu.make_weights(cfg, seed=3)
+    x = torch.from_numpy(np.random.default_rng(4).standard_normal((2 * 40, 256), dtype=np.float32))
+    a = llama_cpu.attention_prefill(cfg, w, x, 2, 40)
+    b = llama_cpu.attention_prefill(cfg, w, x, 2, 40, fused=True)
+    torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
