@@ -77,27 +77,50 @@ struct WordIter {
 };
 
 // The tensor is a set of dense inner runs ("rows") of row_words words each, placed by the outer strides. A group of
-// GROUP lanes walks one row; the outer index is decomposed once per row, not once per word. Each group keeps four rows
-// in flight.
-template <typename W, int GROUP>
+// GROUP lanes walks one row. Each group keeps ROWS consecutive rows in flight; the outer index is decomposed once per
+// group (in 32-bit arithmetic when the row count allows) and the following rows are reached by stepping the last outer
+// dimension, with a full decomposition only where a row crosses into the next slice.
+template <typename I>
+__device__ __forceinline__ void decompose_row(const WordIter& it, I row, int64_t* s, int64_t* d, I* c_last) {
+    I rem = row;
+    int64_t so = 0, dof = 0;
+    I c = 0;
+    for (int k = it.ndim - 1; k >= 0; --k) {
+        const I sh = static_cast<I>(it.shape[k]);
+        const I q = rem / sh;
+        c = rem - q * sh;
+        if (k == it.ndim - 1) *c_last = c;
+        rem = q;
+        so += static_cast<int64_t>(c) * it.sstride[k];
+        dof += static_cast<int64_t>(c) * it.dstride[k];
+    }
+    *s = so;
+    *d = dof;
+}
+
+template <typename W, int GROUP, int ROWS, typename I>
 __global__ void __launch_bounds__(256) strided_word_copy_kernel(const W* __restrict__ src, W* __restrict__ dst, const WordIter it) {
-    constexpr int ROWS = 4;
     const int lane = threadIdx.x % GROUP;
     const int64_t group = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) / GROUP;
     const int64_t row0 = group * ROWS;
+    if (row0 >= it.nrows) return;
     int64_t so[ROWS], d_o[ROWS];
+    I c_last = 0;
+    decompose_row<I>(it, static_cast<I>(row0), &so[0], &d_o[0], &c_last);
+    const int last = it.ndim - 1;
+    const int64_t room = last >= 0 ? it.shape[last] - static_cast<int64_t>(c_last) : 1;  // rows left in this slice, this one included
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-        int64_t rem = row0 + r, s = 0, d = 0;
-        for (int k = it.ndim - 1; k >= 0; --k) {
-            const int64_t q = rem / it.shape[k];
-            const int64_t c = rem - q * it.shape[k];
-            rem = q;
-            s += c * it.sstride[k];
-            d += c * it.dstride[k];
+    for (int r = 1; r < ROWS; ++r) {
+        if (r < room) {
+            so[r] = so[0] + r * it.sstride[last];
+            d_o[r] = d_o[0] + r * it.dstride[last];
+        } else if (row0 + r < it.nrows) {
+            I dummy;
+            decompose_row<I>(it, static_cast<I>(row0 + r), &so[r], &d_o[r], &dummy);
+        } else {
+            so[r] = so[0];
+            d_o[r] = d_o[0];
         }
-        so[r] = s;
-        d_o[r] = d;
     }
     for (int64_t w = lane; w < it.row_words; w += GROUP) {
         W val[ROWS];
@@ -112,22 +135,108 @@ __global__ void __launch_bounds__(256) strided_word_copy_kernel(const W* __restr
     }
 }
 
+template <typename W, int GROUP>
+void launch_word_copy_g(const W* s, W* d, const WordIter& wi, cudaStream_t stream) {
+    // rows that one pass of the group covers: more rows in flight per thread; long rows: fewer (the inner loop iterates)
+    const bool short_rows = wi.row_words <= GROUP;
+    const int rows = short_rows ? 8 : 4;
+    const int64_t groups = (wi.nrows + rows - 1) / rows;
+    const int64_t threads = groups * GROUP;
+    const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
+    const bool small = wi.nrows < 0x7fffffffLL;
+    if (short_rows) {
+        if (small) strided_word_copy_kernel<W, GROUP, 8, uint32_t><<<grid, 256, 0, stream>>>(s, d, wi);
+        else strided_word_copy_kernel<W, GROUP, 8, int64_t><<<grid, 256, 0, stream>>>(s, d, wi);
+    } else {
+        if (small) strided_word_copy_kernel<W, GROUP, 4, uint32_t><<<grid, 256, 0, stream>>>(s, d, wi);
+        else strided_word_copy_kernel<W, GROUP, 4, int64_t><<<grid, 256, 0, stream>>>(s, d, wi);
+    }
+}
+
+// Rows whose two innermost outer dimensions are swapped between source and destination (a [.., S, H, row] ->
+// [.., H, S, row] transpose materialisation): walking the rows in destination order reads 256-byte pieces that lie a
+// whole source slice apart, and walking them in source order writes such pieces. Here a CTA takes a tile of TA x TB rows
+// (TA along the dimension that is dense in the source, TB along the one that is dense in the destination), so that both
+// sides see runs of several KiB; every word still goes straight from its source to its destination address.
+template <typename W, int GROUP>
+__global__ void __launch_bounds__(256) tiled_row_copy_kernel(const W* __restrict__ src, W* __restrict__ dst, const WordIter it, const int tiles_a,
+                                                            const int tiles_b) {
+    constexpr int TA = 8, TB = 16, NG = 256 / GROUP, PER = TA * TB / NG;
+    const int lane = threadIdx.x % GROUP;
+    const int g = threadIdx.x / GROUP;
+    const int da = it.ndim - 2, db = it.ndim - 1;
+    unsigned tile = blockIdx.x;
+    const unsigned ta = tile % tiles_a;
+    tile /= tiles_a;
+    const unsigned tb = tile % tiles_b;
+    unsigned rem = tile / tiles_b;
+    int64_t so = 0, dof = 0;
+    for (int k = it.ndim - 3; k >= 0; --k) {
+        const unsigned sh = static_cast<unsigned>(it.shape[k]);
+        const unsigned q = rem / sh;
+        const unsigned c = rem - q * sh;
+        rem = q;
+        so += static_cast<int64_t>(c) * it.sstride[k];
+        dof += static_cast<int64_t>(c) * it.dstride[k];
+    }
+    const int A = static_cast<int>(it.shape[da]), B = static_cast<int>(it.shape[db]);
+    int64_t s_off[PER], d_off[PER];
+    bool ok[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int id = g + NG * i;          // row of the tile: a runs fastest
+        const int a = ta * TA + id % TA;
+        const int b = tb * TB + id / TA;
+        ok[i] = a < A && b < B;
+        s_off[i] = so + static_cast<int64_t>(a) * it.sstride[da] + static_cast<int64_t>(b) * it.sstride[db];
+        d_off[i] = dof + static_cast<int64_t>(a) * it.dstride[da] + static_cast<int64_t>(b) * it.dstride[db];
+    }
+    for (int64_t w = lane; w < it.row_words; w += GROUP) {
+        W val[PER];
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            if (ok[i]) val[i] = src[s_off[i] + w];
+        }
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            if (ok[i]) dst[d_off[i] + w] = val[i];
+        }
+    }
+}
+
+// True when the tiled kernel was launched.
+template <typename W>
+bool try_tiled_row_copy(const W* s, W* d, const WordIter& wi, cudaStream_t stream) {
+    if (wi.ndim < 2 || wi.row_words < 4 || wi.row_words > 64) return false;
+    const int da = wi.ndim - 2, db = wi.ndim - 1;
+    // destination order has db innermost; the source has da innermost: a swap
+    if (!(wi.sstride[da] < wi.sstride[db] && wi.dstride[db] < wi.dstride[da])) return false;
+    if (wi.shape[da] < 8 || wi.shape[db] < 16 || wi.shape[da] > 0x3fffffff || wi.shape[db] > 0x3fffffff) return false;
+    const int64_t tiles_a = (wi.shape[da] + 7) / 8, tiles_b = (wi.shape[db] + 15) / 16;
+    int64_t outer = 1;
+    for (int k = 0; k < wi.ndim - 2; ++k) outer *= wi.shape[k];
+    const int64_t tiles = outer * tiles_a * tiles_b;
+    if (tiles <= 0 || tiles > 0x7fffffffLL) return false;
+    const unsigned grid = static_cast<unsigned>(tiles);
+    if (wi.row_words <= 16) tiled_row_copy_kernel<W, 16><<<grid, 256, 0, stream>>>(s, d, wi, static_cast<int>(tiles_a), static_cast<int>(tiles_b));
+    else tiled_row_copy_kernel<W, 32><<<grid, 256, 0, stream>>>(s, d, wi, static_cast<int>(tiles_a), static_cast<int>(tiles_b));
+    return true;
+}
+
 template <typename W>
 void launch_word_copy(const void* src, void* dst, const WordIter& wi, cudaStream_t stream) {
     int group = 32;
     while (group > 1 && group / 2 >= wi.row_words) group >>= 1;
-    const int64_t groups = (wi.nrows + 3) / 4;
-    const int64_t threads = groups * group;
-    const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
     const W* s = static_cast<const W*>(src);
     W* d = static_cast<W*>(dst);
+    if (sizeof(W) == 16 && try_tiled_row_copy<W>(s, d, wi, stream)) return;
     switch (group) {
-        case 32: strided_word_copy_kernel<W, 32><<<grid, 256, 0, stream>>>(s, d, wi); break;
-        case 16: strided_word_copy_kernel<W, 16><<<grid, 256, 0, stream>>>(s, d, wi); break;
-        case 8: strided_word_copy_kernel<W, 8><<<grid, 256, 0, stream>>>(s, d, wi); break;
-        case 4: strided_word_copy_kernel<W, 4><<<grid, 256, 0, stream>>>(s, d, wi); break;
-        case 2: strided_word_copy_kernel<W, 2><<<grid, 256, 0, stream>>>(s, d, wi); break;
-        default: strided_word_copy_kernel<W, 1><<<grid, 256, 0, stream>>>(s, d, wi); break;
+        case 32: launch_word_copy_g<W, 32>(s, d, wi, stream); break;
+        case 16: launch_word_copy_g<W, 16>(s, d, wi, stream); break;
+        case 8: launch_word_copy_g<W, 8>(s, d, wi, stream); break;
+        case 4: launch_word_copy_g<W, 4>(s, d, wi, stream); break;
+        case 2: launch_word_copy_g<W, 2>(s, d, wi, stream); break;
+        default: launch_word_copy_g<W, 1>(s, d, wi, stream); break;
     }
 }
 

@@ -60,6 +60,17 @@ def test_copy_transpose_materialisation_bit_exact(diopi, ctx):
     out = torch.empty((2, 4, 33, 128), dtype=torch.bfloat16, device=DEV)
     diopi.diopiCopyInp(ctx, xd.transpose(1, 2), out)
     assert torch.equal(out.cpu(), x.transpose(1, 2).contiguous())
+    # shapes that reach the tiled kernel (>= 8 heads, >= 16 positions), ragged against its 8 x 16 tiles, both directions,
+    # 64- and 128-element rows, and a leading batch dimension
+    for shape in ((3, 50, 12, 128), (1, 17, 9, 64), (2, 256, 32, 128), (1, 16, 8, 256)):
+        x = rnd(shape, torch.bfloat16, seed=sum(shape))
+        xd = x.to(DEV)
+        out = torch.empty((shape[0], shape[2], shape[1], shape[3]), dtype=torch.bfloat16, device=DEV)
+        diopi.diopiCopyInp(ctx, xd.transpose(1, 2), out)
+        assert torch.equal(out.cpu(), x.transpose(1, 2).contiguous())
+        back = torch.empty(shape, dtype=torch.bfloat16, device=DEV)
+        diopi.diopiCopyInp(ctx, out.transpose(1, 2), back)
+        assert torch.equal(back.cpu(), x)
     # odd inner extent: falls back to narrower words
     y = rnd((5, 7, 3), torch.float32, seed=4)
     o2 = torch.empty((3, 7, 5), dtype=torch.float32, device=DEV)
