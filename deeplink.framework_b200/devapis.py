@@ -100,18 +100,27 @@ _SIGS = {
     "b200_dicl_all_to_all_unequal_split": [_vp, ctypes.POINTER(_sz), ctypes.POINTER(_sz), _vp, ctypes.POINTER(_sz), ctypes.POINTER(_sz), _i, _vp,
                                            _vp],
     "b200_dicl_get_comm_name": [ctypes.c_char_p, _sz, _vp],
+    "b200_expandable_create": [ctypes.POINTER(_vp), _i, _vp, _sz, ctypes.POINTER(_i), _i], "b200_expandable_destroy": [_vp],
+    "b200_expandable_map": [_vp, _vp, _sz, ctypes.POINTER(_vp), ctypes.POINTER(_sz)],
+    "b200_expandable_unmap": [_vp, _vp, _sz, ctypes.POINTER(_vp), ctypes.POINTER(_sz)], "b200_expandable_add_peer": [_vp, _i],
 }
 for _n, _a in _SIGS.items():
     getattr(_v, _n).argtypes = _a
     getattr(_v, _n).restype = ctypes.c_int
 for _n in ("b200_stream_not_null", "b200_is_stream_empty", "b200_is_pinned_ptr", "b200_dicl_unique_id_bytes"):
     getattr(_v, _n).restype = ctypes.c_int
+_v.b200_expandable_ptr.argtypes = [_vp]
+_v.b200_expandable_ptr.restype = _vp
+_v.b200_expandable_size.argtypes = [_vp]
+_v.b200_expandable_size.restype = _sz
+_v.b200_expandable_mapped_bytes.argtypes = [_vp]
+_v.b200_expandable_mapped_bytes.restype = _sz
 _v.b200_stream_not_null.argtypes = [_vp]
 _v.b200_is_stream_empty.argtypes = [_vp]
 _v.b200_is_pinned_ptr.argtypes = [_vp]
 
 C_SYMBOLS = sorted(list(_SIGS) + ["b200_stream_not_null", "b200_is_stream_empty", "b200_is_pinned_ptr", "b200_dicl_unique_id_bytes",
-                                  "b200_last_error"])
+                                  "b200_last_error", "b200_expandable_ptr", "b200_expandable_size", "b200_expandable_mapped_bytes"])
 
 
 def last_error():
@@ -390,6 +399,45 @@ class CachingAllocator:
     @staticmethod
     def fakeCompleteEvents():
         _check(_v.b200_cache_fake_complete_events(), "fakeCompleteEvents")
+
+
+class ExpandableSegment:
+    """dipu::ExpandableSegment as the vendor implements it (runtime/core/allocator/ExpandableSegment.h:105-136): a
+    reservation of virtual addresses into which pages of `page_size` bytes are mapped and unmapped. map / unmap return
+    (ptr, size) of the affected whole pages; size 0 from map means the device is out of memory."""
+
+    def __init__(self, device, stream, page_size, peers=()):
+        h = _vp()
+        arr = (ctypes.c_int * max(len(peers), 1))(*peers)
+        _check(_v.b200_expandable_create(ctypes.byref(h), device, stream, page_size, arr, len(peers)), "vendorCreateExpandableSegment")
+        self.handle = h.value
+
+    def map(self, ptr, size):
+        p, n = _vp(), _sz()
+        _check(_v.b200_expandable_map(self.handle, ptr, size, ctypes.byref(p), ctypes.byref(n)), "ExpandableSegment.map")
+        return (p.value or 0), n.value
+
+    def unmap(self, ptr, size):
+        p, n = _vp(), _sz()
+        _check(_v.b200_expandable_unmap(self.handle, ptr, size, ctypes.byref(p), ctypes.byref(n)), "ExpandableSegment.unmap")
+        return (p.value or 0), n.value
+
+    def addPeer(self, device):
+        _check(_v.b200_expandable_add_peer(self.handle, device), "ExpandableSegment.addPeer")
+
+    def ptr(self):
+        return _v.b200_expandable_ptr(self.handle)
+
+    def size(self):
+        return _v.b200_expandable_size(self.handle)
+
+    def mappedBytes(self):
+        return _v.b200_expandable_mapped_bytes(self.handle)
+
+    def close(self):
+        if self.handle:
+            _check(_v.b200_expandable_destroy(self.handle), "ExpandableSegment destroy")
+            self.handle = None
 
 
 class CachingHostAllocator:

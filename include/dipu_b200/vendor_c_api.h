@@ -125,7 +125,8 @@ B200_API b200Status_t b200_cache_empty(void); /* empty_cache(): return every unu
 B200_API b200Status_t b200_cache_stats(int device, b200AllocStats* stats);
 B200_API b200Status_t b200_cache_reset_peak(int device);
 /* "key:value,key:value" as in DIPU_TORCH_ALLOCATOR_CONF (DIPUCachingDeviceAllocator.cpp:454-496):
- * max_split_size_mb, garbage_collection_threshold (accepted, unused), roundup_power2_divisions (accepted, unused) */
+ * max_split_size_mb, expandable_segments:True|False (one growing segment per pool and stream, see b200_expandable_*),
+ * garbage_collection_threshold (accepted, unused), roundup_power2_divisions (accepted, unused) */
 B200_API b200Status_t b200_cache_configure(const char* conf);
 /* Test backend: replaces cudaMalloc/cudaFree/events by host-side fakes with `capacity` bytes of pretend HBM, so the
  * allocator's policy (split, merge, retry ladder, deferred frees) is testable without a GPU. capacity 0 restores CUDA.
@@ -144,6 +145,22 @@ B200_API b200Status_t b200_host_cache_alloc(void** p, size_t nbytes);
 B200_API b200Status_t b200_host_cache_free(void* p);
 B200_API b200Status_t b200_host_cache_record_stream(void* p, b200Stream_t stream);
 B200_API b200Status_t b200_host_cache_empty(void);
+
+/* ---- expandable segments ------------------------------------------------------------------------------------
+ * The vendor side of DIPU's ExpandableSegment (runtime/core/allocator/ExpandableSegment.h:105-136: map, unmap, addPeer,
+ * ptr, size; factory vendorCreateExpandableSegment(device, stream, size, peers), CUDA implementation
+ * vendor/cuda/CUDAExpandableSegment.cpp:15-187). A segment reserves virtual addresses for 9/8 of the device's memory;
+ * map() backs the pages a range touches with physical memory and returns the mapped range, or an empty range when the
+ * device is out of memory; unmap() releases the whole pages inside a range after waiting for the segment's stream.
+ * page_size: a multiple of 2 MiB (DIPU uses 2 MiB for its small pool, 20 MiB for the large one). */
+B200_API b200Status_t b200_expandable_create(void** segment, int device, b200Stream_t stream, size_t page_size, const int* peers, int npeers);
+B200_API b200Status_t b200_expandable_destroy(void* segment);
+B200_API b200Status_t b200_expandable_map(void* segment, void* ptr, size_t size, void** mapped_ptr, size_t* mapped_size);
+B200_API b200Status_t b200_expandable_unmap(void* segment, void* ptr, size_t size, void** unmapped_ptr, size_t* unmapped_size);
+B200_API b200Status_t b200_expandable_add_peer(void* segment, int device);
+B200_API void* b200_expandable_ptr(void* segment);
+B200_API size_t b200_expandable_size(void* segment);
+B200_API size_t b200_expandable_mapped_bytes(void* segment);
 
 /* ---- stream / event pools --------------------------------------------------------------------------------
  * runtime/core/DIPUStream.cpp:38-131 (one lazily created default stream + 8 round-robin pool streams per

@@ -89,7 +89,8 @@ def test_torch_abi_library_has_dipu_devapis_signatures(pkg):
                  "dipu::devapis::memCopyD2DAsync(CUstream_st*, unsigned long, signed char, void*, signed char, void const*)",
                  "dipu::devapis::diclAllReduce(void const*, void*, unsigned long, c10::ScalarType, c10d::ReduceOp const&, b200Comm*, CUstream_st*)",
                  "dipu::devapis::diclCommInitRank(b200Comm**, int, b200UniqueId, int, int)",
-                 "dipu::devapis::diclAllToAllUnequalSplit(", "dipu::devapis::diclGetCommName(", "dipu::devapis::DICL_UNIQUE_ID_BYTES_SIZE"):
+                 "dipu::devapis::diclAllToAllUnequalSplit(", "dipu::devapis::diclGetCommName(", "dipu::devapis::DICL_UNIQUE_ID_BYTES_SIZE",
+                 "dipu::vendorCreateExpandableSegment(int, CUstream_st*, unsigned long, std::vector<int"):
         assert want in syms, want
     handle = ctypes.CDLL(lib)
     count = getattr(handle, "_ZN4dipu7devapis14getDeviceCountEv")

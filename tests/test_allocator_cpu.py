@@ -130,3 +130,83 @@ def test_configuration_strings(A, pkg):
         A.configure("no_such_option:1")
     with pytest.raises(pkg.devapis.VendorError):
         A.configure("max_split_size_mb:10")
+
+
+# ---- expandable segments (expandable_segments:True): one growing segment per pool and stream ----------------------------
+def test_expandable_segment_grows_in_place(A):
+    A.configure("expandable_segments:True")
+    a = A.allocate(10 * MiB, 0, 1)
+    st = A.stats(0)
+    assert st["segments"] == 1 and st["reserved_bytes"] == 20 * MiB   # one 20 MiB page of the large pool
+    b = A.allocate(30 * MiB, 0, 1)
+    # the free 10 MiB tail of the first page plus one more page: the segment grew at its end, contiguously
+    assert b == a + 10 * MiB
+    st = A.stats(0)
+    assert st["segments"] == 1 and st["reserved_bytes"] == 40 * MiB and st["allocated_bytes"] == 40 * MiB
+    A.free(a)
+    A.free(b)
+    n = A.stats(0)["num_device_mallocs"]
+    c = A.allocate(40 * MiB, 0, 1)   # the two freed blocks coalesced: a cache hit, nothing mapped
+    assert c == a and A.stats(0)["num_device_mallocs"] == n
+    A.free(c)
+    A.emptyCache()
+    st = A.stats(0)
+    assert st["reserved_bytes"] == 0 and st["segments"] == 0
+
+
+def test_expandable_small_pool_and_streams(A):
+    A.configure("expandable_segments:True")
+    small = [A.allocate(64 * 1024, 0, 1) for _ in range(100)]   # 6.25 MiB in 2 MiB pages
+    st = A.stats(0)
+    assert st["segments"] == 1 and st["reserved_bytes"] == 8 * MiB
+    assert sorted(small) == small and small[-1] - small[0] == 99 * 64 * 1024   # one contiguous run
+    other = A.allocate(64 * 1024, 0, 2)   # another stream: its own segment
+    assert A.stats(0)["segments"] == 2
+    big = A.allocate(5 * MiB, 0, 1)       # large pool of stream 1: a third one
+    assert A.stats(0)["segments"] == 3
+    for p in small + [other, big]:
+        A.free(p)
+    A.emptyCache()
+    assert A.stats(0)["reserved_bytes"] == 0 and A.stats(0)["segments"] == 0
+
+
+def test_expandable_unmaps_free_pages_when_memory_is_short(pkg):
+    A = pkg.devapis.CachingAllocator
+    A.useFakeBackend(100 * MiB)
+    try:
+        A.configure("expandable_segments:True")
+        a = A.allocate(60 * MiB, 0, 1)
+        A.free(a)                                  # 60 MiB stay mapped in stream 1's segment
+        assert A.stats(0)["reserved_bytes"] == 60 * MiB
+        b = A.allocate(60 * MiB, 0, 2)             # stream 2 needs 60 MiB, only 40 are left: stream 1's free pages go back
+        st = A.stats(0)
+        assert st["num_alloc_retries"] >= 1 and st["reserved_bytes"] == 60 * MiB and st["num_ooms"] == 0
+        with pytest.raises(MemoryError):
+            A.allocate(60 * MiB, 0, 1)
+        assert A.stats(0)["num_ooms"] == 1
+        A.free(b)
+    finally:
+        A.useFakeBackend(0)
+
+
+def test_expandable_refills_gaps_at_the_lowest_address(A):
+    A.configure("expandable_segments:True")
+    x, y, z = (A.allocate(20 * MiB, 0, 1) for _ in range(3))
+    assert y == x + 20 * MiB and z == y + 20 * MiB
+    A.free(y)
+    A.emptyCache()                                  # y's page is unmapped: a hole between x and z
+    assert A.stats(0)["reserved_bytes"] == 40 * MiB
+    w = A.allocate(15 * MiB, 0, 1)
+    assert w == y                                   # the hole is mapped again before the segment grows at its end
+    v = A.allocate(30 * MiB, 0, 1)                  # does not fit the 5 MiB left in the hole: goes behind z
+    assert v == z + 20 * MiB
+    for p in (x, z, w, v):
+        A.free(p)
+    A.emptyCache()
+    assert A.stats(0)["reserved_bytes"] == 0
+
+
+def test_expandable_config_is_validated(A):
+    with pytest.raises(Exception, match="True or False"):
+        A.configure("expandable_segments:yes")
+    A.configure("expandable_segments:False")

@@ -143,3 +143,88 @@ def test_allocator_every_small_size(devapis):
     devapis.CachingHostAllocator.free(hp)
     devapis.CachingHostAllocator.emptyCache()
     A.emptyCache()
+
+
+def _fill_and_check(devapis, stream, ptr, nbytes, value):
+    devapis.memSetAsync(stream, ptr, value, nbytes)
+    devapis.syncStream(stream)
+    for off in (0, nbytes // 2 - 8, nbytes - 16):
+        back = (ctypes.c_ubyte * 16)()
+        devapis.memCopyD2H(16, ctypes.addressof(back), ptr + off)
+        assert bytes(back) == bytes([value]) * 16
+
+
+def test_expandable_segment_maps_and_unmaps_pages(devapis):
+    """The vendor's ExpandableSegment on the real driver: address reservation, page-wise map / unmap, data survives growth."""
+    MiB = 1 << 20
+    devapis.setDevice(0)
+    s = devapis.getDefaultStream(0)
+    seg = devapis.ExpandableSegment(0, s, 2 * MiB)
+    try:
+        base = seg.ptr()
+        assert base and base % (2 * MiB) == 0 and seg.size() >= devapis.getDeviceProperties(0).totalGlobalMem
+        assert seg.mappedBytes() == 0
+        p, n = seg.map(base, 5 * MiB)                 # three 2 MiB pages
+        assert p == base and n == 6 * MiB and seg.mappedBytes() == 6 * MiB
+        _fill_and_check(devapis, s, base, 6 * MiB, 0x11)
+        p2, n2 = seg.map(base + 6 * MiB, 2 * MiB)     # grow at the end: the old pages keep their content
+        assert p2 == base + 6 * MiB and n2 == 2 * MiB
+        _fill_and_check(devapis, s, base + 6 * MiB, 2 * MiB, 0x22)
+        back = (ctypes.c_ubyte * 16)()
+        devapis.memCopyD2H(16, ctypes.addressof(back), base + 6 * MiB - 16)
+        assert bytes(back) == b"\x11" * 16
+        # a copy that crosses a page boundary
+        h = devapis.mallocHost(4 * MiB)
+        ctypes.memset(h, 0x33, 4 * MiB)
+        devapis.memCopyH2D(4 * MiB, base + 3 * MiB, h)
+        devapis.memCopyD2H(16, ctypes.addressof(back), base + 5 * MiB)
+        assert bytes(back) == b"\x33" * 16
+        devapis.freeHost(h)
+        # unmap: only whole pages inside the range go away
+        p3, n3 = seg.unmap(base + 1 * MiB, 4 * MiB)   # covers page 1 wholly, pages 0 and 2 partly
+        assert p3 == base + 2 * MiB and n3 == 2 * MiB and seg.mappedBytes() == 6 * MiB
+        p4, n4 = seg.unmap(base + 1 * MiB, 512 * 1024)
+        assert n4 == 0
+        p5, n5 = seg.map(base + 2 * MiB, 2 * MiB)     # the hole can be mapped again
+        assert p5 == base + 2 * MiB and n5 == 2 * MiB
+        _fill_and_check(devapis, s, base, 8 * MiB, 0x44)
+    finally:
+        seg.close()
+    devapis.checkLastError()
+
+
+def test_caching_allocator_with_expandable_segments(devapis):
+    """expandable_segments:True on the device: blocks of one growing segment hold their data, free pages go back."""
+    MiB = 1 << 20
+    A = devapis.CachingAllocator
+    devapis.setDevice(0)
+    s = devapis.createStream()
+    A.emptyCache()
+    before = A.stats(0)["reserved_bytes"]
+    A.configure("expandable_segments:True")
+    try:
+        a = A.allocate(30 * MiB, 0, s)
+        b = A.allocate(50 * MiB, 0, s)
+        assert b == a + 30 * MiB                       # same segment, contiguous
+        assert A.stats(0)["reserved_bytes"] - before == 80 * MiB
+        devapis.memSetAsync(s, a, 0x5c, 30 * MiB)
+        devapis.memSetAsync(s, b, 0xa7, 50 * MiB)
+        c = A.allocate(100 * MiB, 0, s)                # grows the segment by five more pages
+        assert c == b + 50 * MiB
+        devapis.memSetAsync(s, c, 0x01, 100 * MiB)
+        devapis.syncStream(s)
+        back = (ctypes.c_ubyte * 16)()
+        for ptr, n, val in ((a, 30 * MiB, 0x5c), (b, 50 * MiB, 0xa7), (c, 100 * MiB, 0x01)):
+            for off in (0, n - 16):
+                devapis.memCopyD2H(16, ctypes.addressof(back), ptr + off)
+                assert bytes(back) == bytes([val]) * 16
+        small = [A.allocate(4096, 0, s) for _ in range(8)]   # the small pool has its own segment with 2 MiB pages
+        assert A.stats(0)["reserved_bytes"] - before == 182 * MiB
+        for p in small + [a, b, c]:
+            A.free(p)
+        A.emptyCache()
+        assert A.stats(0)["reserved_bytes"] == before
+    finally:
+        A.configure("expandable_segments:False")
+        devapis.destroyStream(s)
+    devapis.checkLastError()
