@@ -7,6 +7,10 @@
 
 #include "vendorapi.h"
 
+#if __has_include(<csrc_dipu/runtime/core/allocator/ExpandableSegment.h>)
+#include <csrc_dipu/runtime/core/allocator/ExpandableSegment.h>
+namespace dipu {
+#else
 namespace dipu {
 
 struct SegmentRange {
@@ -24,6 +28,7 @@ class ExpandableSegment {
     virtual char* ptr() const = 0;
     virtual size_t size() const = 0;
 };
+#endif
 
 namespace {
 

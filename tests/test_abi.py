@@ -90,9 +90,14 @@ def test_torch_abi_library_has_dipu_devapis_signatures(pkg):
                  "dipu::devapis::diclAllReduce(void const*, void*, unsigned long, c10::ScalarType, c10d::ReduceOp const&, b200Comm*, CUstream_st*)",
                  "dipu::devapis::diclCommInitRank(b200Comm**, int, b200UniqueId, int, int)",
                  "dipu::devapis::diclAllToAllUnequalSplit(", "dipu::devapis::diclGetCommName(", "dipu::devapis::DICL_UNIQUE_ID_BYTES_SIZE",
-                 "dipu::vendorCreateExpandableSegment(int, CUstream_st*, unsigned long, std::vector<int"):
+                 "dipu::vendorCreateExpandableSegment(int, CUstream_st*, unsigned long, std::vector<int",
+                 "dipu::vendorMakeGenerator(signed char)"):
         assert want in syms, want
     handle = ctypes.CDLL(lib)
     count = getattr(handle, "_ZN4dipu7devapis14getDeviceCountEv")
     count.restype = ctypes.c_int
     assert count() >= 0
+    # the RNG state container behind vendorMakeGenerator: seed / offset round trip, clone, offset rule (all host-side)
+    selftest = handle.b200_torchabi_generator_selftest
+    selftest.restype = ctypes.c_int
+    assert selftest() == 0
