@@ -4,6 +4,7 @@
                                  stream and event pools, DICL communicator (NCCL bound at run time)
     lib/libdiopirt_minihost.so   a small DIOPI host (the diopirt callbacks over plain tensor structs)
     lib/libdiopi_impl.so         the DIOPI operator library: hand-written sm_100a kernels
+    lib/libtorch_dipu_b200.so             hot-path aten ops on the PrivateUse1 key ("dipu"), each wrapper calling ::diopiXxx
     lib/libdipu_vendor_b200_torchabi.so   the vendor contract with DIPU's exact C++ signatures (namespace dipu::devapis, torch
                                  types in the arguments): thin wrappers over the C-ABI runtime, built when torch's headers are present
 
@@ -81,6 +82,16 @@ def _link(name, objs, extra):
 
 def _build_torch_abi(vendor_lib, verbose):
     """csrc/torch_abi/*.cpp: the files a DIPU tree would compile as csrc_dipu/vendor/b200/. Needs torch's C++ headers."""
+    return _build_torch_lib("torch_abi", "libdipu_vendor_b200_torchabi.so", ["-l:libdipu_vendor_b200.so"], verbose)
+
+
+def _build_torch_adapter(verbose):
+    """csrc/torch_adapter/*.cpp: hot-path aten ops on the PrivateUse1 key ("dipu"), each wrapper calling ::diopiXxx."""
+    return _build_torch_lib("torch_adapter", "libtorch_dipu_b200.so",
+                            ["-l:libdipu_vendor_b200.so", "-l:libdiopirt_minihost.so", "-l:libdiopi_impl.so"], verbose)
+
+
+def _build_torch_lib(sub, out_name, link_libs, verbose):
     try:
         import torch
         from torch.utils.cpp_extension import include_paths
@@ -88,11 +99,11 @@ def _build_torch_abi(vendor_lib, verbose):
         torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
     except Exception:
         return None
-    srcs = sorted(os.path.join(CSRC, "torch_abi", f) for f in os.listdir(os.path.join(CSRC, "torch_abi")) if f.endswith(".cpp"))
+    srcs = sorted(os.path.join(CSRC, sub, f) for f in os.listdir(os.path.join(CSRC, sub)) if f.endswith(".cpp"))
     objs = []
     newest_hdr = max(os.path.getmtime(h) for h in _headers())
     for src in srcs:
-        obj = os.path.join(OBJ, "torch_abi_" + os.path.basename(src) + ".o")
+        obj = os.path.join(OBJ, sub + "_" + os.path.basename(src) + ".o")
         if not (os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(src), newest_hdr, os.path.getmtime(__file__))):
             cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-fvisibility=hidden", "-c", src, "-o", obj, "-I", os.path.join(ROOT, "include"),
                    "-I", "/usr/local/cuda/include"] + ["-I" + p for p in incs]
@@ -102,9 +113,9 @@ def _build_torch_abi(vendor_lib, verbose):
             if verbose:
                 print("compiled", os.path.relpath(src, ROOT), flush=True)
         objs.append(obj)
-    out = os.path.join(LIB, "libdipu_vendor_b200_torchabi.so")
+    out = os.path.join(LIB, out_name)
     if not (os.path.exists(out) and all(os.path.getmtime(out) >= os.path.getmtime(o) for o in objs)):
-        cmd = ["g++", "-shared", "-o", out] + objs + ["-L", LIB, "-l:libdipu_vendor_b200.so", "-L", torch_lib, "-lc10", "-ltorch_cpu",
+        cmd = ["g++", "-shared", "-o", out] + objs + ["-L", LIB] + link_libs + ["-L", torch_lib, "-lc10", "-ltorch_cpu",
                                                        "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + torch_lib]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
@@ -139,6 +150,9 @@ def build(verbose=False):
     abi = _build_torch_abi(vendor, verbose)
     if abi:
         built.append(abi)
+    adapter = _build_torch_adapter(verbose)
+    if adapter:
+        built.append(adapter)
     return built
 
 

@@ -14,28 +14,7 @@
 
 #include "diopi/diopirt.h"
 #include "dipu_b200/vendor_c_api.h"
-
-struct diopiTensor {
-    void* data = nullptr;
-    diopiDtype_t dtype = diopi_dtype_float32;
-    diopiDevice_t device = diopi_device;
-    int32_t device_index = 0;
-    int64_t ndim = 0;
-    int64_t shape[8] = {0};
-    int64_t stride[8] = {0};
-    int64_t numel = 0;
-    int64_t itemsize = 0;
-    int64_t storage_offset = 0;  // elements
-    size_t storage_nbytes = 0;
-    bool owns_memory = false;    // workspace allocated through the caching device allocator
-    bool owns_host_memory = false;  // workspace allocated through the pinned-host cache
-};
-
-struct diopiContext {
-    diopiStreamHandle_t stream = nullptr;
-    int32_t device_index = 0;
-    std::vector<diopiTensor*> arrays;  // workspace, released with the context
-};
+#include "minihost_structs.h"
 
 namespace {
 

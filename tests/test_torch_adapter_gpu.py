@@ -1,0 +1,168 @@
+"""The eager adapter: a plain nn.Module run on torch.device("dipu"), every op dispatched to a wrapper that calls the DIOPI
+C-ABI (the shape of the reference's generated wrappers, dipu/scripts/autogen_diopi_wrapper/diopi_wrapper_template.py:100-142),
+compared with the same module on CPU. Shapes and tolerances follow the reference's unit tests
+(dipu/tests/python/unittests/test_mm.py, test_softmax.py, test_layer_norm.py, test_cat.py, test_index.py, test_copy.py)."""
+import importlib
+import math
+
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def adapter(pkg):
+    return importlib.import_module(pkg.__name__ + ".torch_adapter")
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim, eps=1e-6):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(dim))
+
+    def forward(self, x):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)).type_as(x) * self.weight
+
+
+def rotate_half(x):
+    x1, x2 = x[..., : x.shape[-1] // 2], x[..., x.shape[-1] // 2:]
+    return torch.cat((-x2, x1), dim=-1)
+
+
+class Block(nn.Module):
+    """A Llama-style decoder block in plain torch: nothing in it knows about the device."""
+
+    def __init__(self, dim, heads, kv_heads, ffn):
+        super().__init__()
+        self.heads, self.kv_heads, self.head_dim = heads, kv_heads, dim // heads
+        self.wq = nn.Linear(dim, heads * self.head_dim, bias=False)
+        self.wk = nn.Linear(dim, kv_heads * self.head_dim, bias=False)
+        self.wv = nn.Linear(dim, kv_heads * self.head_dim, bias=False)
+        self.wo = nn.Linear(heads * self.head_dim, dim, bias=False)
+        self.w1 = nn.Linear(dim, ffn, bias=False)
+        self.w2 = nn.Linear(ffn, dim, bias=False)
+        self.w3 = nn.Linear(dim, ffn, bias=False)
+        self.attention_norm, self.ffn_norm = RMSNorm(dim), RMSNorm(dim)
+
+    def forward(self, x, cos, sin, mask):
+        b, s, _ = x.shape
+        h = self.attention_norm(x)
+        q = self.wq(h).view(b, s, self.heads, self.head_dim).transpose(1, 2)
+        k = self.wk(h).view(b, s, self.kv_heads, self.head_dim).transpose(1, 2)
+        v = self.wv(h).view(b, s, self.kv_heads, self.head_dim).transpose(1, 2)
+        q = q * cos + rotate_half(q) * sin
+        k = k * cos + rotate_half(k) * sin
+        if self.kv_heads != self.heads:
+            g = self.heads // self.kv_heads
+            k = k[:, :, None].expand(b, self.kv_heads, g, s, self.head_dim).reshape(b, self.heads, s, self.head_dim)
+            v = v[:, :, None].expand(b, self.kv_heads, g, s, self.head_dim).reshape(b, self.heads, s, self.head_dim)
+        scores = torch.matmul(q, k.transpose(2, 3)) / math.sqrt(self.head_dim)
+        scores = F.softmax((scores + mask).float(), dim=-1).type_as(q)
+        a = torch.matmul(scores, v).transpose(1, 2).contiguous().view(b, s, -1)
+        x = x + self.wo(a)
+        h = self.ffn_norm(x)
+        return x + self.w2(F.silu(self.w1(h)) * self.w3(h))
+
+
+def _tables(seq, head_dim):
+    inv = 1.0 / (10000.0 ** (torch.arange(0, head_dim, 2).float() / head_dim))
+    ang = torch.outer(torch.arange(seq).float(), inv)
+    emb = torch.cat((ang, ang), dim=-1)
+    return emb.cos()[None, None], emb.sin()[None, None]
+
+
+@pytest.mark.parametrize("dtype,kv_heads", [(torch.float32, 4), (torch.bfloat16, 4), (torch.bfloat16, 2)])
+def test_unmodified_module_runs_on_dipu(adapter, dtype, kv_heads):
+    torch.manual_seed(0)
+    dim, heads, ffn, b, s = 512, 4, 1376, 2, 96
+    block = Block(dim, heads, kv_heads, ffn)
+    for p in block.parameters():
+        if p.dim() == 2:
+            nn.init.normal_(p, std=0.02)
+    x = torch.randn(b, s, dim) * 0.5
+    cos, sin = _tables(s, dim // heads)
+    mask = torch.triu(torch.full((1, 1, s, s), float("-inf")), diagonal=1)
+    if dtype != torch.float32:   # the CPU side computes in fp32 from the rounded parameters and inputs
+        block = block.to(dtype).float()
+        x, cos, sin = x.to(dtype).float(), cos.to(dtype).float(), sin.to(dtype).float()
+    with torch.no_grad():
+        ref = block(x, cos, sin, mask)
+        before = adapter.stats()["diopi_calls"]
+        dev = torch.device("dipu:0")
+        dblock = Block(dim, heads, kv_heads, ffn)
+        dblock.load_state_dict(block.state_dict())
+        dblock = dblock.to(dtype).to(dev)
+        assert next(dblock.parameters()).device.type == "dipu"
+        y = dblock(x.to(dtype).to(dev), cos.to(dtype).to(dev), sin.to(dtype).to(dev), mask.to(dev))
+        assert y.device.type == "dipu" and y.dtype == dtype
+        got = y.float().cpu()
+    assert adapter.stats()["diopi_calls"] - before > 40   # every op of the block went through a DIOPI call
+    err = (got - ref).abs().max().item()
+    rel = ((got - ref).norm() / ref.norm()).item()
+    if dtype == torch.float32:
+        assert err <= 2e-4 and rel <= 1e-5, (err, rel)
+    else:
+        assert err <= 2e-2 and rel <= 1e-2, (err, rel)   # whole bf16 layer against fp32: the layer tests' bound
+
+
+def test_single_ops_against_cpu(adapter):
+    dev = torch.device("dipu:0")
+    g = torch.Generator().manual_seed(1)
+    with torch.no_grad():
+        # embedding lowers to index_select: bit-exact
+        table = torch.randn(1000, 64, generator=g)
+        ids = torch.randint(0, 1000, (3, 17), generator=g)
+        assert torch.equal(F.embedding(ids.to(dev), table.to(dev)).cpu(), F.embedding(ids, table))
+        # copies: cast, transpose materialisation, expand, slices, host round trip
+        a = torch.randn(5, 7, 9, generator=g)
+        ad = a.to(dev)
+        assert torch.equal(ad.cpu(), a)
+        assert torch.equal(ad.transpose(0, 2).contiguous().cpu(), a.transpose(0, 2).contiguous())
+        assert torch.equal(ad.to(torch.bfloat16).cpu(), a.to(torch.bfloat16))
+        assert torch.equal(ad[1:4, ::2].cpu(), a[1:4, ::2])
+        assert torch.equal(ad[:, :1].expand(5, 7, 9).contiguous().cpu(), a[:, :1].expand(5, 7, 9).contiguous())
+        assert abs(ad[2, 3, 4].item() - a[2, 3, 4].item()) == 0.0
+        # layer norm with statistics (reference unittests/test_layer_norm.py shapes)
+        x = torch.randn(4, 6, 32, generator=g)
+        w, b = torch.randn(32, generator=g), torch.randn(32, generator=g)
+        torch.testing.assert_close(F.layer_norm(x.to(dev), [32], w.to(dev), b.to(dev), 1e-5).cpu(), F.layer_norm(x, [32], w, b, 1e-5), rtol=1e-4,
+                                   atol=1e-5)
+        # mm / addmm / bmm / baddbmm
+        m1, m2, bias = torch.randn(33, 20, generator=g), torch.randn(20, 45, generator=g), torch.randn(45, generator=g)
+        torch.testing.assert_close(torch.mm(m1.to(dev), m2.to(dev)).cpu(), torch.mm(m1, m2), rtol=1e-4, atol=1e-4)
+        torch.testing.assert_close(torch.addmm(bias.to(dev), m1.to(dev), m2.to(dev), beta=0.5, alpha=2.0).cpu(),
+                                   torch.addmm(bias, m1, m2, beta=0.5, alpha=2.0), rtol=1e-4, atol=1e-4)
+        b1, b2 = torch.randn(3, 8, 5, generator=g), torch.randn(3, 5, 6, generator=g)
+        torch.testing.assert_close(torch.bmm(b1.to(dev), b2.to(dev)).cpu(), torch.bmm(b1, b2), rtol=1e-4, atol=1e-4)
+        # scalars on either side, in-place forms, mixed dtypes
+        torch.testing.assert_close((2.0 * x.to(dev) + 1.5).cpu(), 2.0 * x + 1.5)
+        torch.testing.assert_close((x.to(dev) / 3.0 - x.to(dev) * x.to(dev)).cpu(), x / 3.0 - x * x)
+        y = x.to(dev).clone()
+        y.mul_(0.5).add_(x.to(dev), alpha=2.0)
+        torch.testing.assert_close(y.cpu(), x * 0.5 + 2.0 * x)
+        torch.testing.assert_close((x.to(dev).to(torch.bfloat16) + x.to(dev)).cpu(), x.to(torch.bfloat16) + x)
+        # masks and selection
+        cond = x > 0
+        torch.testing.assert_close(torch.where(cond.to(dev), x.to(dev), -x.to(dev)).cpu(), torch.where(cond, x, -x))
+        z = x.to(dev).clone()
+        z.masked_fill_(cond.to(dev), -1.0)
+        torch.testing.assert_close(z.cpu(), x.masked_fill(cond, -1.0))
+        torch.testing.assert_close(torch.triu(torch.ones(6, 6, device=dev), diagonal=1).cpu(), torch.triu(torch.ones(6, 6), diagonal=1))
+        torch.testing.assert_close(torch.cat([x.to(dev), x.to(dev)[:, :2]], dim=1).cpu(), torch.cat([x, x[:, :2]], dim=1))
+        torch.testing.assert_close(torch.softmax(x.to(dev), dim=1).cpu(), torch.softmax(x, dim=1), rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(torch.zeros(3, 4, device=dev).cpu(), torch.zeros(3, 4))
+        # the fused norm entry of recent torch
+        out, rstd = torch.ops.aten._fused_rms_norm(x.to(dev), [32], w.to(dev), 1e-6)
+        want = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+        torch.testing.assert_close(out.cpu(), want, rtol=1e-5, atol=1e-5)
+
+
+def test_missing_wrapper_raises_instead_of_falling_back(adapter):
+    x = torch.ones(8, device="dipu:0")
+    with pytest.raises(NotImplementedError):
+        torch.cumsum(x, 0)
