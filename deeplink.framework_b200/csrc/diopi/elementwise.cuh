@@ -277,6 +277,96 @@ __global__ void __launch_bounds__(256, 4) ew_repeat_kernel(T* out, const T* dens
     }
 }
 
+// ---- row kernel --------------------------------------------------------------------------------------------------------
+// Operands of one 2- or 4-byte float dtype whose innermost run is dense (or, for an input, broadcast) while the outer
+// dimensions have arbitrary pitches: transposed views ([B, S, h, D] read as [B, h, S, D]), slices, tables broadcast over
+// batch and heads, outputs that keep the input's permutation. One thread moves 16-byte vectors; the outer index of a
+// vector is decomposed with 32-bit divisions. This is what keeps an op-by-op rotary embedding on views near the
+// bandwidth of the dense path instead of the element-at-a-time general kernel.
+template <typename T, int NIN, typename Op>
+__global__ void __launch_bounds__(256) ew_rows_kernel(const EwIter<NIN + 1> it, const uint32_t nvec, const uint32_t vec_per_row, const Op op) {
+    constexpr int V = Vec16<T>::N;
+    constexpr int UNROLL = 4;
+    const int last = it.ndim - 1;
+    const uint32_t base = blockIdx.x * (256u * UNROLL) + threadIdx.x;
+    int64_t off[UNROLL][NIN + 1];
+    bool live[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        const uint32_t iv = base + u * 256u;
+        live[u] = iv < nvec;
+        uint32_t r = iv / vec_per_row;
+        const uint32_t col = iv - r * vec_per_row;
+#pragma unroll
+        for (int a = 0; a <= NIN; ++a) off[u][a] = it.stride[a][last] != 0 ? static_cast<int64_t>(col) * V : 0;
+        for (int d = last - 1; d >= 0; --d) {
+            const uint32_t sh = static_cast<uint32_t>(it.shape[d]);
+            const uint32_t q = r / sh;
+            const uint32_t c = r - q * sh;
+            r = q;
+#pragma unroll
+            for (int a = 0; a <= NIN; ++a) off[u][a] += static_cast<int64_t>(c) * it.stride[a][d];
+        }
+    }
+    Vec16<T> x[NIN > 0 ? NIN : 1][UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        if (!live[u]) continue;
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) {
+            const T* p = static_cast<const T*>(it.ptr[a + 1]) + off[u][a + 1];
+            if (it.stride[a + 1][last] != 0) {
+                x[a][u] = ld16(p);
+            } else {
+                const T s = *p;  // one value for the whole row
+#pragma unroll
+                for (int e = 0; e < V; ++e) x[a][u].v[e] = s;
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        if (!live[u]) continue;
+        Vec16<T> y;
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            float f;
+            if constexpr (NIN == 0) f = op();
+            else if constexpr (NIN == 1) f = op(to_f32(x[0][u].v[e]));
+            else if constexpr (NIN == 2) f = op(to_f32(x[0][u].v[e]), to_f32(x[1][u].v[e]));
+            else f = op(to_f32(x[0][u].v[e]), to_f32(x[1][u].v[e]), to_f32(x[2][u].v[e]));
+            y.v[e] = from_f32<T>(f);
+        }
+        st16(static_cast<T*>(it.ptr[0]) + off[u][0], y);
+    }
+}
+
+// Eligibility of the row kernel for an iterator built by build_iter: one float dtype everywhere, the output's innermost
+// pitch 1, every input's innermost pitch 1 or 0, whole 16-byte vectors per row, 16-byte aligned vector addresses.
+template <int NARGS>
+inline bool rows_eligible(const EwIter<NARGS>& it, int64_t itemsize) {
+    if (it.ndim < 1) return false;
+    const int last = it.ndim - 1;
+    const int64_t V = 16 / itemsize;
+    if (it.stride[0][last] != 1 || it.shape[last] % V != 0) return false;
+    if (it.numel / V >= 0xffffffffLL) return false;
+    for (int a = 0; a < NARGS; ++a) {
+        if (it.dtype[a] != it.dtype[0]) return false;
+        const int64_t inner = it.stride[a][last];
+        if (inner != 1 && inner != 0) return false;
+        if (inner == 1) {
+            if (reinterpret_cast<uintptr_t>(it.ptr[a]) % 16 != 0) return false;
+            for (int d = 0; d < last; ++d) {
+                if (it.stride[a][d] % V != 0) return false;
+            }
+        }
+        for (int d = 0; d < last; ++d) {
+            if (it.shape[d] >= 0x7fffffffLL) return false;
+        }
+    }
+    return true;
+}
+
 template <typename T, int NIN, typename Op>
 void launch_vec(const TensorView& out, const void* const* p, const VecPeriods& per, const Op& op, cudaStream_t stream) {
     constexpr int V = Vec16<T>::N;
@@ -388,6 +478,18 @@ diopiError_t launch_elementwise(diopiContextHandle_t ctx, const char* name, cons
     // --- general path ---
     EwIter<NIN + 1> it;
     B200_CHECK(build_iter<NIN + 1>(out, ins, &it), "%s: operand shapes cannot be broadcast to the output shape", name);
+    if (allow_vec && vec_dtype && rows_eligible<NIN + 1>(it, out.itemsize)) {
+        const int64_t V = 16 / out.itemsize;
+        const uint32_t nvec = static_cast<uint32_t>(it.numel / V);
+        const uint32_t vpr = static_cast<uint32_t>(it.shape[it.ndim - 1] / V);
+        const unsigned grid = (nvec + 1023u) / 1024u;
+        OpT<float> op(sargs);
+        if (out.dtype == diopi_dtype_bfloat16) ew_rows_kernel<bf16, NIN, OpT<float>><<<grid, 256, 0, stream>>>(it, nvec, vpr, op);
+        else if (out.dtype == diopi_dtype_float16) ew_rows_kernel<fp16, NIN, OpT<float>><<<grid, 256, 0, stream>>>(it, nvec, vpr, op);
+        else ew_rows_kernel<float, NIN, OpT<float>><<<grid, 256, 0, stream>>>(it, nvec, vpr, op);
+        B200_LAUNCH_CHECK(name);
+        return diopiSuccess;
+    }
     const int threads = 256;
     const int grid = ew_grid(out.numel, threads);
     if (out.dtype == diopi_dtype_float64) {

@@ -224,6 +224,44 @@ def test_broadcast_fast_path_and_ragged_tail(diopi, ctx):
     assert torch.equal(o.cpu(), -y)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_elementwise_on_views_with_dense_rows(diopi, ctx, dtype):
+    """The op-by-op rotary embedding of a plain torch model: q as a transposed view, tables broadcast over batch and heads,
+    halves of the head dimension as slices, outputs that keep the view's permutation. bf16 add / mul of two bf16 values
+    round an exact fp32 result once: bit-exact against torch CPU."""
+    b, s, h, d = 2, 37, 3, 64
+    q = rnd((b, s, h, d), dtype, seed=1)
+    cos = rnd((1, 1, s, d), dtype, seed=2)
+    qd, cd = q.to(DEV), cos.to(DEV)
+    qt, qtd = q.transpose(1, 2), qd.transpose(1, 2)                  # [b, h, s, d] view, pitches (s*h*d, d, h*d, 1)
+    out = torch.empty_strided(qt.shape, qt.stride(), dtype=dtype, device=DEV)   # the permuted layout torch gives the result
+    diopi.diopiMul(ctx, out, qtd, cd)
+    assert torch.equal(out.cpu(), qt * cos)
+    dense = torch.empty(qt.shape, dtype=dtype, device=DEV)
+    diopi.diopiAdd(ctx, dense, qtd, cd, 1)
+    assert torch.equal(dense.cpu(), qt + cos)
+    # halves of the last dimension (32 elements = 64 or 128 bytes, 16-byte aligned starts)
+    neg = torch.empty((b, h, s, d // 2), dtype=dtype, device=DEV)
+    diopi.diopiNeg(ctx, neg, qtd[..., d // 2:])
+    assert torch.equal(neg.cpu(), -qt[..., d // 2:])
+    half = torch.empty((b, h, s, d // 2), dtype=dtype, device=DEV)
+    diopi.diopiMul(ctx, half, qtd[..., : d // 2], qtd[..., d // 2:])
+    assert torch.equal(half.cpu(), qt[..., : d // 2] * qt[..., d // 2:])
+    # an input that is constant along the row ([.., 1] against [.., d]) and one that repeats over the leading dimensions
+    col = rnd((b, h, s, 1), dtype, seed=3)
+    diopi.diopiMul(ctx, dense, qtd, col.to(DEV))
+    assert torch.equal(dense.cpu(), qt * col)
+    row = rnd((d,), dtype, seed=4)
+    diopi.diopiAddInp(ctx, out, row.to(DEV), 1)
+    assert torch.equal(out.cpu(), qt * cos + row)
+    # in place on a view
+    diopi.diopiSiluInp(ctx, qtd)
+    if dtype == torch.float32:
+        check_close(qtd, torch.nn.functional.silu(qt), 1e-5, 1e-6)
+    else:
+        check_bf16(qtd, torch.nn.functional.silu(qt.float()))
+
+
 def test_unary_reference_cases(diopi, ctx):
     # test_rsqrt.py:7-19, test_silu.py:8-34, test_neg.py
     x = torch.rand(10, generator=torch.Generator().manual_seed(1)) * 0.98 + 0.01
