@@ -308,6 +308,14 @@ def main():
         return y
 
     # ---- device-resident timing ----
+    if tp_group is not None:
+        # communicator set-up, not part of any step: NCCL picks its channels and registers buffers during its first calls
+        # on a message size, which would otherwise fall into the first timed steps
+        scratch = torch.empty((tokens, cfg.hidden), dtype=dtype, device=device)
+        for _ in range(10):
+            tp_group.all_reduce_(scratch, stream.cuda_stream)
+        torch.cuda.synchronize()
+        del scratch
     for _ in range(args.warmup):
         step_resident()
     barrier()
