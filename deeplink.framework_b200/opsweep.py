@@ -192,31 +192,35 @@ def gemm_case(case, diopi, ctx, dev):
     return fns, flops, per_set
 
 
-# (label, batch, seq, heads, kv_heads, causal): fused attention, head dim 128
+# (label, batch, seq_q, seq_kv, heads, kv_heads, causal): fused attention, head dim 128
 ATTENTION_CASES = [
-    ("prefill 7B causal", 8, 2048, 32, 32, True),
-    ("prefill 7B full", 8, 2048, 32, 32, False),
-    ("prefill 70B-shaped TP8 shard causal", 4, 4096, 8, 1, True),
-    ("prefill long causal", 1, 16384, 32, 32, True),
+    ("prefill 7B causal", 8, 2048, 2048, 32, 32, True),
+    ("prefill 7B full", 8, 2048, 2048, 32, 32, False),
+    ("prefill 70B-shaped TP8 shard causal", 4, 4096, 4096, 8, 1, True),
+    ("prefill long causal", 1, 16384, 16384, 32, 32, True),
+    ("decode 7B, KV 4096", 64, 1, 4096, 32, 32, False),
+    ("decode 70B-shaped TP8 shard, KV 4096", 64, 1, 4096, 8, 1, False),
+    ("decode 7B, 4 sequences, KV 16384", 4, 1, 16384, 32, 32, False),
 ]
 
 
 def attention_case(case, diopi, ctx, dev):
-    label, b, s, h, hk, causal = case
+    label, b, sq, skv, h, hk, causal = case
     bf = torch.bfloat16
     g = torch.Generator(device=dev)
-    g.manual_seed(b * s + h)
-    per_set = 2 * b * s * 128 * (2 * h + 2 * hk)
+    g.manual_seed(b * skv + h)
+    per_set = 2 * b * 128 * (2 * sq * h + 2 * skv * hk)   # q + out, k + v
     sets = int(max(1, min(8, math.ceil(2.0 * L2_BYTES / per_set))))
     fns = []
     for _ in range(sets):
-        q = torch.randn((b, s, h, 128), generator=g, device=dev, dtype=torch.float32).to(bf)
-        k = torch.randn((b, s, hk, 128), generator=g, device=dev, dtype=torch.float32).to(bf)
-        v = torch.randn((b, s, hk, 128), generator=g, device=dev, dtype=torch.float32).to(bf)
+        q = torch.randn((b, sq, h, 128), generator=g, device=dev, dtype=torch.float32).to(bf)
+        # keys / values in the cache layout [B, kv heads, L, D], handed over as the [B, L, kv heads, D] view
+        k = torch.randn((b, hk, skv, 128), generator=g, device=dev, dtype=torch.float32).to(bf).transpose(1, 2)
+        v = torch.randn((b, hk, skv, 128), generator=g, device=dev, dtype=torch.float32).to(bf).transpose(1, 2)
         out = torch.empty_like(q)
         fns.append(lambda q=q, k=k, v=v, out=out: diopi.diopiMultiHeadAttention(ctx, q, k, v, 0.0, causal, False, 128 ** -0.5, out, None, None, None))
     # products actually needed: 4*d flop per visible (query, key) pair
-    pairs = b * h * (s * (s + 1) // 2 if causal else s * s)
+    pairs = b * h * (sq * (sq + 1) // 2 + sq * (skv - sq) if causal else sq * skv)
     return fns, 4.0 * 128 * pairs, per_set
 
 
@@ -225,6 +229,7 @@ def main():
     ap.add_argument("--ops", default="all", help="comma list of: %s, gemm, attention" % ", ".join(MEM_OPS))
     ap.add_argument("--tokens", default="1,64,1024,16384,65536")
     ap.add_argument("--gemm", default="all", help="comma list of indices into the GEMM case table, or 'all'")
+    ap.add_argument("--attention", default="all", help="comma list of indices into the attention case table, or 'all'")
     ap.add_argument("--iters", type=int, default=50)
     args = ap.parse_args()
 
@@ -242,12 +247,14 @@ def main():
     tokens = [int(x) for x in args.tokens.split(",")]
     for op in ops:
         if op == "attention":
-            for case in ATTENTION_CASES:
+            which = range(len(ATTENTION_CASES)) if args.attention == "all" else [int(x) for x in args.attention.split(",")]
+            for case in [ATTENTION_CASES[i] for i in which]:
                 fns, flops, per_set = attention_case(case, diopi, ctx, dev)
-                ms = time_cases(fns, max(5, args.iters // 2), stream)
-                rec = {"op": "attention", "case": case[0], "batch": case[1], "seq": case[2], "heads": case[3], "kv_heads": case[4], "causal": case[5],
-                       "ms": round(ms, 4), "tflops_visible_pairs": round(flops / (ms * 1e-3) / 1e12, 2),
-                       "frac_of_%s_bf16_burst" % src: round(flops / (ms * 1e-3) / 1e12 / tflops, 4), "gbs": round(per_set / (ms * 1e-3) / 1e9, 1)}
+                ms = time_cases(fns, max(2, args.iters // 2), stream)
+                rec = {"op": "attention", "case": case[0], "batch": case[1], "seq_q": case[2], "seq_kv": case[3], "heads": case[4], "kv_heads": case[5],
+                       "causal": case[6], "ms": round(ms, 4), "tflops_visible_pairs": round(flops / (ms * 1e-3) / 1e12, 2),
+                       "frac_of_%s_bf16_burst" % src: round(flops / (ms * 1e-3) / 1e12 / tflops, 4), "algorithmic_bytes": per_set,
+                       "gbs": round(per_set / (ms * 1e-3) / 1e9, 1), "frac_of_%s_hbm" % src: round(per_set / (ms * 1e-3) / 1e9 / hbm, 4)}
                 print(json.dumps(rec), flush=True)
                 del fns
                 ctx.release_workspace()
