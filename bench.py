@@ -403,10 +403,19 @@ def main():
             ops[name]["gbs"] = round(by / (ms * 1e-3) / 1e9, 1)
     mm_calls = ops.get("diopiMm", {}).get("calls_per_step", 1)
     achieved = mm_flops / (mm_ms * 1e-3) / 1e12 if mm_ms > 0 else 0.0
-    roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel (diopiMm: the 7 projection GEMMs of the layer)", "achieved": round(achieved, 1),
+    # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the projection GEMMs at the single-GPU 7B
+    # shapes, from one ncu capture of `opsweep.py --ops gemm --gemm 0,1,2`: q/k/v/o 447.6 MB (x4), gate/up 1216.5 MB (x2),
+    # down 2087 MB (x1); algorithmic 302 / 585 / 585 MB. Other shapes (tensor-parallel shards, the 70B stack): not captured.
+    traffic = None
+    if world == 1 and args.workload == "7b" and (batch, seq) == (8, 2048):
+        traffic = (4 * 447.6e6 + 2 * 1216.5e6 + 2087.0e6) / 7
+    roofline = {"bound": "tensor", "kernel": "gemm_tc_pair_kernel / gemm_tc_kernel (diopiMm: the 7 projection GEMMs of the layer)",
+                "achieved": round(achieved, 1),
                 "peak": peaks["tflops_sustained"], "unit": "TFLOP/s", "frac": round(achieved / peaks["tflops_sustained"], 4),
                 "peak_source": "%s bf16 cuBLAS, sustained (kernel timed inside a long step)" % peaks["source"],
-                "flops_per_launch": mm_flops / max(mm_calls, 1), "ms_per_launch": mm_ms / max(mm_calls, 1), "traffic": None}
+                "flops_per_launch": mm_flops / max(mm_calls, 1), "ms_per_launch": mm_ms / max(mm_calls, 1), "traffic": traffic,
+                "traffic_unit": "bytes per launch (mean over the 7 launches), ncu dram__bytes_read.sum + dram__bytes_write.sum",
+                "algorithmic_bytes_per_launch": (4 * 302.0e6 + 3 * 585.1e6) / 7 if traffic else None}
 
     # ---- variant: attention scores through one baddbmm (scale and mask-add in the GEMM epilogue) ----
     # `value` above is the reference block's literal op order (bmm, div, add, softmax, bmm). A model written with

@@ -44,6 +44,7 @@ static_assert(kSmemBytes <= 232448, "shared memory budget");
 struct PairParams {
     int M, N, K, batch;
     int m_pairs, n_blocks, k_blocks;
+    int group_m;  // row-pair blocks per tile group (tile order: all tiles of a group before the next group)
     int64_t ldc, stride_cb;
     void* C;
     const void* bias;
@@ -59,10 +60,10 @@ __device__ __forceinline__ void pair_tile_coords(int tile, const PairParams& p, 
     const int per_batch = p.m_pairs * p.n_blocks;
     *b = tile / per_batch;
     const int t = tile - *b * per_batch;
-    const int group_sz = kGroupM * p.n_blocks;
+    const int group_sz = p.group_m * p.n_blocks;
     const int g = t / group_sz;
-    const int first = g * kGroupM;
-    const int rows = min(p.m_pairs - first, kGroupM);
+    const int first = g * p.group_m;
+    const int rows = min(p.m_pairs - first, p.group_m);
     const int r = t - g * group_sz;
     *mp = first + r % rows;
     *nb = r / rows;
@@ -349,6 +350,11 @@ diopiError_t gemm_tc2_launch(const GemmProblem& g, cudaStream_t stream) {
     p.M = static_cast<int>(g.M); p.N = static_cast<int>(g.N); p.K = static_cast<int>(g.K); p.batch = static_cast<int>(g.batch);
     p.m_pairs = static_cast<int>((g.M + 2 * BM - 1) / (2 * BM));
     p.n_blocks = static_cast<int>((g.N + BN - 1) / BN);
+    p.group_m = kGroupM;
+    if (const char* e = std::getenv("B200_GEMM_GROUP_M")) {
+        const int v = std::atoi(e);
+        if (v >= 1 && v <= 64) p.group_m = v;
+    }
     p.k_blocks = static_cast<int>((g.K + BK - 1) / BK);
     p.ldc = g.c_sm; p.stride_cb = g.c_sb; p.C = g.C;
     p.bias = g.bias; p.bias_sb = g.bias_sb; p.bias_sr = g.bias_sm; p.bias_sc = g.bias_sn;
