@@ -100,6 +100,9 @@ _SIGS = {
     "b200_dicl_all_to_all_unequal_split": [_vp, ctypes.POINTER(_sz), ctypes.POINTER(_sz), _vp, ctypes.POINTER(_sz), ctypes.POINTER(_sz), _i, _vp,
                                            _vp],
     "b200_dicl_get_comm_name": [ctypes.c_char_p, _sz, _vp],
+    "b200_dicl_comm_rank": [_vp, ctypes.POINTER(_i), ctypes.POINTER(_i)],
+    "b200_dicl_peer_reduce_create": [ctypes.POINTER(_vp), _vp, _sz, _vp], "b200_dicl_peer_all_reduce": [_vp, _vp, _vp, _sz, _i, _vp],
+    "b200_dicl_peer_reduce_destroy": [_vp],
     "b200_expandable_create": [ctypes.POINTER(_vp), _i, _vp, _sz, ctypes.POINTER(_i), _i], "b200_expandable_destroy": [_vp],
     "b200_expandable_map": [_vp, _vp, _sz, ctypes.POINTER(_vp), ctypes.POINTER(_sz)],
     "b200_expandable_unmap": [_vp, _vp, _sz, ctypes.POINTER(_vp), ctypes.POINTER(_sz)], "b200_expandable_add_peer": [_vp, _i],
@@ -109,6 +112,8 @@ for _n, _a in _SIGS.items():
     getattr(_v, _n).restype = ctypes.c_int
 for _n in ("b200_stream_not_null", "b200_is_stream_empty", "b200_is_pinned_ptr", "b200_dicl_unique_id_bytes"):
     getattr(_v, _n).restype = ctypes.c_int
+_v.b200_dicl_peer_reduce_status.argtypes = [_vp]
+_v.b200_dicl_peer_reduce_status.restype = ctypes.c_int
 _v.b200_expandable_ptr.argtypes = [_vp]
 _v.b200_expandable_ptr.restype = _vp
 _v.b200_expandable_size.argtypes = [_vp]
@@ -120,7 +125,7 @@ _v.b200_is_stream_empty.argtypes = [_vp]
 _v.b200_is_pinned_ptr.argtypes = [_vp]
 
 C_SYMBOLS = sorted(list(_SIGS) + ["b200_stream_not_null", "b200_is_stream_empty", "b200_is_pinned_ptr", "b200_dicl_unique_id_bytes",
-                                  "b200_last_error", "b200_expandable_ptr", "b200_expandable_size", "b200_expandable_mapped_bytes"])
+                                  "b200_last_error", "b200_dicl_peer_reduce_status", "b200_expandable_ptr", "b200_expandable_size", "b200_expandable_mapped_bytes"])
 
 
 def last_error():
@@ -495,6 +500,33 @@ def diclGetCommAsyncError(comm):
 
 def diclAllReduce(sendBuf, recvBuf, count, datatype, reduceOp, comm, stream):
     return _dicl(_v.b200_dicl_all_reduce(sendBuf, recvBuf, count, datatype, int(reduceOp), comm, stream), "diclAllReduce")
+
+
+def diclCommRank(comm):
+    r, n = ctypes.c_int(), ctypes.c_int()
+    _check(_v.b200_dicl_comm_rank(comm, ctypes.byref(r), ctypes.byref(n)), "diclCommRank")
+    return r.value, n.value
+
+
+class PeerAllReduce:
+    """SUM all-reduce of small messages in one kernel over peer memory (no reference counterpart; see
+    b200_dicl_peer_reduce_* in include/dipu_b200/vendor_c_api.h). Creation is collective over the communicator."""
+
+    def __init__(self, comm, max_bytes, stream):
+        h = _vp()
+        _check(_v.b200_dicl_peer_reduce_create(ctypes.byref(h), comm, max_bytes, stream), "peer reduce create")
+        self.handle, self.max_bytes = h.value, max_bytes
+
+    def all_reduce(self, sendBuf, recvBuf, count, datatype, stream):
+        _check(_v.b200_dicl_peer_all_reduce(self.handle, sendBuf, recvBuf, count, datatype, stream), "peer all-reduce")
+
+    def status(self):
+        return _v.b200_dicl_peer_reduce_status(self.handle)
+
+    def close(self):
+        if self.handle:
+            _check(_v.b200_dicl_peer_reduce_destroy(self.handle), "peer reduce destroy")
+            self.handle = None
 
 
 def diclBroadcast(sendBuf, recvBuf, count, datatype, root, comm, stream):

@@ -46,9 +46,21 @@ class TpGroup:
         self.rank, self.size, self.device = rank, size, device
         self.comm = devapis.diclCommInitRank(size, unique_id, rank, device)
         self.stream = devapis.getStreamFromPool(device)
+        self.peer = None  # one-kernel all-reduce over peer memory for small messages (enable_peer_reduce)
+
+    def enable_peer_reduce(self, max_bytes=1 << 20):
+        """Collective: from now on dense bf16 / fp16 / fp32 messages of up to max_bytes are summed by one kernel over peer
+        memory on the compute stream itself (no stream hop, no library call); larger ones keep going through diclAllReduce."""
+        self.peer = devapis.PeerAllReduce(self.comm, max_bytes, self.stream)
+        devapis.syncStream(self.stream)
 
     def all_reduce_(self, tensor, compute_stream):
         """In-place SUM all-reduce of a dense tensor; the compute stream waits for the result without a host block."""
+        nbytes = tensor.numel() * tensor.element_size()
+        if (self.peer is not None and nbytes <= self.peer.max_bytes and nbytes % 16 == 0 and tensor.data_ptr() % 16 == 0
+                and tensor.dtype in (torch.bfloat16, torch.float16, torch.float32)):
+            self.peer.all_reduce(tensor.data_ptr(), tensor.data_ptr(), tensor.numel(), diopi.DTYPE[tensor.dtype], compute_stream)
+            return
         self.wait(self.all_reduce_async_(tensor, compute_stream), compute_stream)
 
     def all_reduce_async_(self, tensor, compute_stream):
@@ -70,6 +82,9 @@ class TpGroup:
 
     def close(self):
         devapis.syncStream(self.stream)
+        if self.peer is not None:
+            self.peer.close()
+            self.peer = None
         devapis.diclCommDestroy(self.comm)
         self.comm = None
 

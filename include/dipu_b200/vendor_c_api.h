@@ -207,6 +207,20 @@ B200_API b200Status_t b200_dicl_all_to_all_unequal_split(const void* send, const
                                                          const size_t* recv_counts, const size_t* recv_displs, int dtype, b200Comm_t comm,
                                                          b200Stream_t stream);
 B200_API b200Status_t b200_dicl_get_comm_name(char* name, size_t capacity, b200Comm_t comm);
+B200_API b200Status_t b200_dicl_comm_rank(b200Comm_t comm, int* rank, int* nranks);
+
+/* All-reduce (SUM) of small messages in ONE kernel over peer memory (CUDA IPC mappings of every rank's staging buffer,
+ * NVLink loads / stores, bounded flag waits) instead of a library collective: for the latency-bound partial sums of
+ * tensor-parallel decode, which the reference sends through diclAllReduce = ncclAllReduce
+ * (runtime/distributed/ProcessGroupDICL.cpp:539-567, vendor/cuda/communiatorimpl.cpp:84-92). No reference counterpart.
+ * create is collective over `comm` (handles are exchanged with the communicator's all-gather); every rank must call
+ * all_reduce with the same count, in the same order; float16 / bfloat16 / float32, buffers 16-byte aligned, byte count a
+ * multiple of 16 and at most max_bytes; in place (send == recv) is allowed. The sum is formed in fp32 in rank order, so
+ * every rank gets bit-identical results. status: 0, or 1 once a wait for a peer ran into its 1 s limit. */
+B200_API b200Status_t b200_dicl_peer_reduce_create(void** handle, b200Comm_t comm, size_t max_bytes, b200Stream_t stream);
+B200_API b200Status_t b200_dicl_peer_all_reduce(void* handle, const void* send, void* recv, size_t count, int dtype, b200Stream_t stream);
+B200_API int b200_dicl_peer_reduce_status(void* handle);
+B200_API b200Status_t b200_dicl_peer_reduce_destroy(void* handle);
 
 #ifdef __cplusplus
 }

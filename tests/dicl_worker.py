@@ -113,6 +113,37 @@ def main():
     sync()
     assert torch.equal(u_out.cpu(), torch.arange(world).float().repeat_interleave(rank + 1))
 
+    # all-reduce in one kernel over peer memory: closed-form sums, bit-identical on every rank, in place and out of place,
+    # sizes from one vector to the handle's limit, 40 calls back to back (the call counter lives on the device)
+    assert dv.diclCommRank(comm) == (rank, world)
+    peer = dv.PeerAllReduce(comm, 1 << 20, stream)
+    sync()
+    for dtype, n in ((torch.bfloat16, 8), (torch.bfloat16, 64 * 4096), (torch.float16, 4096 + 8), (torch.float32, 1 << 18), (torch.bfloat16, 1 << 19)):
+        src = (torch.arange(n, device=dev, dtype=torch.float32) % 13 + rank).to(dtype)
+        out = torch.empty_like(src)
+        peer.all_reduce(src.data_ptr(), out.data_ptr(), n, DT[dtype], stream)
+        sync()
+        want = sum((torch.arange(n, dtype=torch.float32) % 13 + r).to(dtype).float() for r in range(world)).to(dtype)
+        assert torch.equal(out.cpu(), want), (dtype, n)
+        peer.all_reduce(src.data_ptr(), src.data_ptr(), n, DT[dtype], stream)   # in place
+        sync()
+        assert torch.equal(src.cpu(), want), (dtype, n, "in place")
+    acc = torch.full((4096,), 1.0, device=dev, dtype=torch.float32)
+    for _ in range(40):
+        peer.all_reduce(acc.data_ptr(), acc.data_ptr(), 4096, DT[acc.dtype], stream)
+        dv.diclAllReduce(acc.data_ptr(), acc.data_ptr(), 1, DT[acc.dtype], dv.ReduceOp.MAX, comm, stream)  # a library collective in between
+    sync()
+    assert peer.status() == 0
+    assert torch.equal(acc.cpu(), torch.full((4096,), float(world) ** 40)) or world > 2
+    # a message above the limit is refused on the host
+    try:
+        big = torch.zeros((1 << 20) // 2 + 8, device=dev, dtype=torch.bfloat16)
+        peer.all_reduce(big.data_ptr(), big.data_ptr(), big.numel(), DT[big.dtype], stream)
+        raise SystemExit("oversized peer all-reduce was not refused")
+    except dv.VendorError:
+        pass
+    peer.close()
+
     # tensor-parallel layer: every rank's output equals the unsharded CPU oracle
     from oracle import llama_cpu
     from dipu_b200 import layer as L
@@ -124,7 +155,7 @@ def main():
 
     class Group:
         def __init__(self):
-            self.rank, self.size, self.device, self.comm, self.stream = rank, world, rank, comm, stream
+            self.rank, self.size, self.device, self.comm, self.stream, self.peer = rank, world, rank, comm, stream, None
     grp = L.TpGroup.__new__(L.TpGroup)
     grp.__dict__.update(Group().__dict__)
     lay = L.DecoderLayer(cfg, w, dtype=torch.float32, device=dev, tp_rank=rank, tp_size=world, tp_group=grp)
@@ -134,6 +165,18 @@ def main():
         torch.cuda.synchronize()
         err = (y.cpu() - ref).abs().max().item()
         assert err <= 2e-4, (overlap, err)
+
+    # the same layer with its partial sums (256 KiB each) reduced by the peer-memory kernel on the compute stream
+    grp.enable_peer_reduce(1 << 20)
+    lay.overlap_comm = False
+    for _ in range(3):
+        y = lay.prefill(L.embed(emb.to(dev), ids.to(dev)), 2, 64)
+    torch.cuda.synchronize()
+    assert grp.peer.status() == 0
+    err = (y.cpu() - ref).abs().max().item()
+    assert err <= 2e-4, ("peer reduce", err)
+    grp.peer.close()
+    grp.peer = None
 
     dv.diclCommDestroy(comm)
     print("rank %d ok" % rank, flush=True)
