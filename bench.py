@@ -549,6 +549,28 @@ def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ra
     barrier()
     ms_fused = max_over_ranks(e0.elapsed_time(e1)) / steps
     devapis.graphDestroy(replay.graph)
+    # tensor parallel: the two 512 KiB partial sums per step reduced by ONE kernel over peer memory on the compute stream
+    # (b200_dicl_peer_all_reduce) instead of ncclAllReduce on the communication stream; fused attention stays on
+    ms_peer = None
+    if world > 1 and lay.tp_group is not None:
+        lay.tp_group.enable_peer_reduce(1 << 20)
+        barrier()
+        for _ in range(3):
+            lay.decode(xd, kc, vc, length - 1, ctx)
+        replay, _ = lay.capture_decode(xd, kc, vc, length - 1, ctx)
+        for _ in range(5):
+            replay()
+        barrier()
+        e0.record(stream)
+        for _ in range(steps):
+            replay()
+        e1.record(stream)
+        barrier()
+        ms_peer = max_over_ranks(e0.elapsed_time(e1)) / steps
+        devapis.graphDestroy(replay.graph)
+        assert lay.tp_group.peer.status() == 0, "a peer all-reduce wait timed out"
+        lay.tp_group.peer.close()
+        lay.tp_group.peer = None
     lay.fused_attention = False
     d = cfg.head_dim
     weight_bytes = 2 * (cfg.hidden * lay.heads * d * 2 + cfg.hidden * lay.kv_heads * d * 2 + 3 * cfg.hidden * lay.ffn)
@@ -560,7 +582,10 @@ def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ra
             "hbm_frac": round(gbs / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
             "fused_attention": {"tokens_per_s": b / (ms_fused * 1e-3), "ms_per_step": ms_fused,
                                 "hbm_frac": round((weight_bytes + kv_bytes) / (ms_fused * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
-                                "note": "diopiMultiHeadAttention on views of the cache replaces diopiBmm, diopiDivInpScalar, diopiSoftmax, diopiBmm"}}
+                                "note": "diopiMultiHeadAttention on views of the cache replaces diopiBmm, diopiDivInpScalar, diopiSoftmax, diopiBmm"},
+            "fused_attention_peer_all_reduce": None if ms_peer is None else {
+                "tokens_per_s": b / (ms_peer * 1e-3), "ms_per_step": ms_peer,
+                "note": "as fused_attention, with both all-reduces done by one kernel each over peer memory (NVLink loads, bounded flag waits)"}}
 
 
 if __name__ == "__main__":
