@@ -85,6 +85,26 @@ DIOPI_RT_API void minihostFreeContext(diopiContextHandle_t ctx) {
     delete ctx;
 }
 
+DIOPI_RT_API diopiGeneratorHandle_t minihostMakeGenerator(uint64_t seed) {
+    diopiGenerator* g = new diopiGenerator();
+    g->seed = seed;
+    return g;
+}
+DIOPI_RT_API void minihostFreeGenerator(diopiGeneratorHandle_t g) { delete g; }
+
+DIOPI_RT_API diopiError_t diopiGeneratorGetSeedAndOffset(diopiGeneratorHandle_t th, uint64_t* seed, uint64_t* offset) {
+    if (th == nullptr) return diopiErrorOccurred;
+    *seed = th->seed;
+    *offset = th->offset;
+    return diopiSuccess;
+}
+DIOPI_RT_API diopiError_t diopiGeneratorSetSeedAndOffset(diopiGeneratorHandle_t th, uint64_t seed, uint64_t offset) {
+    if (th == nullptr) return diopiErrorOccurred;
+    th->seed = seed;
+    th->offset = offset;
+    return diopiSuccess;
+}
+
 DIOPI_RT_API int64_t minihostWorkspaceCount(diopiContextHandle_t ctx) { return ctx ? static_cast<int64_t>(ctx->arrays.size()) : 0; }
 
 // ---- diopirt callbacks -------------------------------------------------------------------------------------------

@@ -30,3 +30,8 @@ struct diopiContext {
     int32_t device_index = 0;
     std::vector<diopiTensor*> arrays;  // workspace, released with the context
 };
+
+struct diopiGenerator {
+    uint64_t seed = 67280421310721ull;
+    uint64_t offset = 0;
+};

@@ -138,6 +138,7 @@ class Context:
 # ---- signatures ---------------------------------------------------------------------------------------------
 # T: tensor handle   t: tensor handle or None   s: const diopiScalar_t*   i: int64   d: double   b: bool
 # z: diopiSize_t by value   L: (const handle*, int64 count)   r: diopiRoundMode_t
+# I: const int64_t* or None   P: const bool* or None   G: generator handle (Generator or None)
 SIGNATURES = {
     "diopiCopyInp": "tT", "diopiCastDtype": "Tt", "diopiFill": "Ts", "diopiZeroInp": "T", "diopiOnes": "Tz", "diopiZeros": "Tz",
     "diopiArange": "Tsss",
@@ -156,10 +157,13 @@ SIGNATURES = {
     "diopiLinear": "Tttt",
     "diopiRMSNorm": "TTtzttd", "diopiRotaryEmbedding": "Ttttbb",
     "diopiMultiHeadAttention": "TTTdbbdTttt",
+    "diopiArgmax": "TtIb", "diopiSort": "TTtibP", "diopiTopk": "TTtiibb", "diopiCumsum": "Tti", "diopiGather": "Ttit",
+    "diopiMultinomial": "TtibG", "diopiIndexPutInp": "TtLb",
 }
 
 _CTYPES = {"T": ctypes.c_void_p, "t": ctypes.c_void_p, "s": ctypes.POINTER(_Scalar), "i": ctypes.c_int64, "d": ctypes.c_double,
-           "b": ctypes.c_bool, "z": _Size, "r": ctypes.c_int}
+           "b": ctypes.c_bool, "z": _Size, "r": ctypes.c_int, "I": ctypes.POINTER(ctypes.c_int64), "P": ctypes.POINTER(ctypes.c_bool),
+           "G": ctypes.c_void_p}
 
 
 def _bind(name):
@@ -205,6 +209,22 @@ def _bind(name):
                 arr = (ctypes.c_void_p * max(len(hs), 1))(*[h.ptr for h in hs])
                 keep.append(arr)
                 cargs += [arr, len(hs)]
+            elif c == "I":
+                if a is None:
+                    cargs.append(None)
+                else:
+                    v = ctypes.c_int64(int(a))
+                    keep.append(v)
+                    cargs.append(ctypes.byref(v))
+            elif c == "P":
+                if a is None:
+                    cargs.append(None)
+                else:
+                    v = ctypes.c_bool(bool(a))
+                    keep.append(v)
+                    cargs.append(ctypes.byref(v))
+            elif c == "G":
+                cargs.append(None if a is None else a.ptr)
             elif c == "b":
                 cargs.append(bool(a))
             elif c == "d":
@@ -218,6 +238,54 @@ def _bind(name):
 
     call.__name__ = name
     return call
+
+
+class Generator:
+    """The host's RNG state the library reads and advances (diopiGeneratorGetSeedAndOffset / SetSeedAndOffset)."""
+
+    def __init__(self, seed=67280421310721):
+        _host.minihostMakeGenerator.restype = ctypes.c_void_p
+        _host.minihostMakeGenerator.argtypes = [ctypes.c_uint64]
+        self.ptr = _host.minihostMakeGenerator(seed)
+
+    def state(self):
+        seed, off = ctypes.c_uint64(), ctypes.c_uint64()
+        _host.diopiGeneratorGetSeedAndOffset(ctypes.c_void_p(self.ptr), ctypes.byref(seed), ctypes.byref(off))
+        return seed.value, off.value
+
+    def set_state(self, seed, offset):
+        _host.diopiGeneratorSetSeedAndOffset(ctypes.c_void_p(self.ptr), ctypes.c_uint64(seed), ctypes.c_uint64(offset))
+
+    def __del__(self):
+        if getattr(self, "ptr", None):
+            _host.minihostFreeGenerator(ctypes.c_void_p(self.ptr))
+            self.ptr = None
+
+
+def diopiIndex(ctx, self_tensor, indices):
+    """diopiIndex allocates its result through diopiRequireTensor (the reference's wrapper passes `&out_ptr`); here the
+    result is copied out of the context's workspace into a torch tensor before the workspace is released."""
+    fn = _lib.diopiIndex
+    fn.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int64]
+    fn.restype = ctypes.c_int
+    hs = [handle(x) for x in indices]
+    arr = (ctypes.c_void_p * max(len(hs), 1))(*[h.ptr for h in hs])
+    out = ctypes.c_void_p()
+    hself = handle(self_tensor)
+    rc = fn(ctx.ptr, ctypes.byref(out), hself.ptr, arr, len(hs))
+    if rc != 0:
+        raise DiopiError("diopiIndex failed with code %d: %s" % (rc, last_error()))
+    size = _Size()
+    _host.diopiGetTensorShape(out, ctypes.byref(size))
+    shape = [size.data[i] for i in range(size.len)]
+    data = ctypes.c_void_p()
+    _host.diopiGetTensorData(out, ctypes.byref(data))
+    result = torch.empty(shape, dtype=self_tensor.dtype, device=self_tensor.device)
+    nbytes = result.numel() * result.element_size()
+    if nbytes:
+        from . import devapis
+        devapis.memCopyD2DAsync(ctx.stream, nbytes, ctx.device, result.data_ptr(), ctx.device, data.value)
+    return result
 
 
 def last_error():

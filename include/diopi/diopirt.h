@@ -137,6 +137,10 @@ extern DIOPI_RT_API diopiError_t diopiRequireTensor(diopiContextHandle_t ctx, di
                                                     const diopiDevice_t device);
 extern DIOPI_RT_API diopiError_t diopiRequireBuffer(diopiContextHandle_t ctx, diopiTensorHandle_t* tensor, int64_t num_bytes,
                                                     diopiDevice_t device);
+/* RNG state of the host's generator (diopirt_impl.cpp:175-222): seed and Philox offset; an op that consumes random numbers
+ * reads them and stores the advanced offset back. */
+extern DIOPI_RT_API diopiError_t diopiGeneratorGetSeedAndOffset(diopiGeneratorHandle_t th, uint64_t* seed, uint64_t* offset);
+extern DIOPI_RT_API diopiError_t diopiGeneratorSetSeedAndOffset(diopiGeneratorHandle_t th, uint64_t seed, uint64_t offset);
 
 /* ---- exported by the operator library --------------------------------------------------- */
 extern DIOPI_API const char* diopiGetVendorName(void);

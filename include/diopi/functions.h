@@ -172,6 +172,31 @@ DIOPI_API diopiError_t diopiMatmul(diopiContextHandle_t ctx, diopiTensorHandle_t
 DIOPI_API diopiError_t diopiLinear(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
                                    diopiConstTensorHandle_t weight, diopiConstTensorHandle_t bias);
 
+/* ---- operators of a sampling loop -------------------------------------------------------------- */
+/* yaml:1516-1519; dim NULL = over the flattened tensor; ties -> lowest index; out int64 */
+DIOPI_API diopiError_t diopiArgmax(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input, const int64_t* dim, bool keepdim);
+/* yaml:1143-1175; stable may be NULL; equal keys keep their order, NaN sorts above every number */
+DIOPI_API diopiError_t diopiSort(diopiContextHandle_t ctx, diopiTensorHandle_t values, diopiTensorHandle_t indices, diopiConstTensorHandle_t input,
+                                 int64_t dim, bool descending, const bool* stable);
+/* yaml:816-828 */
+DIOPI_API diopiError_t diopiTopk(diopiContextHandle_t ctx, diopiTensorHandle_t values, diopiTensorHandle_t indices, diopiConstTensorHandle_t input,
+                                 int64_t k, int64_t dim, bool largest, bool sorted);
+/* yaml:1908-1912 (the wrapper has already cast the input to the result dtype) */
+DIOPI_API diopiError_t diopiCumsum(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input, int64_t dim);
+/* yaml:1923-1924 */
+DIOPI_API diopiError_t diopiGather(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input, int64_t dim,
+                                   diopiConstTensorHandle_t index);
+/* yaml:1199-1211; input: weights [categories] or [rows, categories]; out int64 [rows, num_samples]; generator may be NULL */
+DIOPI_API diopiError_t diopiMultinomial(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input, int64_t num_samples,
+                                        bool replacement, diopiGeneratorHandle_t generator);
+/* yaml:2349-2360; the library allocates *out through diopiRequireTensor. Supported: int64 index tensors for the leading
+ * `nums` dimensions, broadcast together (no skipped dimensions, no boolean masks) */
+DIOPI_API diopiError_t diopiIndex(diopiContextHandle_t ctx, diopiTensorHandle_t* out, diopiConstTensorHandle_t input,
+                                  diopiConstTensorHandle_t* indices, int64_t nums);
+/* yaml:2362-2382; same index forms as diopiIndex; values broadcast to the indexed shape */
+DIOPI_API diopiError_t diopiIndexPutInp(diopiContextHandle_t ctx, diopiTensorHandle_t input, diopiConstTensorHandle_t values,
+                                        diopiConstTensorHandle_t* indices, int64_t nums, bool accumulate);
+
 #ifdef __cplusplus
 }
 #endif

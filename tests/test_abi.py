@@ -28,7 +28,7 @@ def test_operator_library_exports_declared_functions(pkg):
     # and the Python binding knows every DIOPI function of the two DIOPI headers
     for h in ("functions.h", "functions_ext.h"):
         for n in _declared(os.path.join(INC, "diopi", h), "DIOPI_API", "diopi"):
-            assert n in pkg.diopi.SIGNATURES, n
+            assert n in pkg.diopi.SIGNATURES or callable(getattr(pkg.diopi, n, None)), n   # diopiIndex has a hand-written binding
 
 
 def test_host_library_exports_the_diopirt_callbacks(pkg):
