@@ -314,7 +314,71 @@ at::Tensor where_self(const at::Tensor& condition, const at::Tensor& self, const
     return out;
 }
 
+// ---- sampling loop (yaml:816-828 topk, 1143-1175 sort, 1516-1519 argmax, 1908-1912 cumsum, 1923-1924 gather, 1199-1211 multinomial)
+at::Tensor& argmax_out(const at::Tensor& self, std::optional<int64_t> dim, bool keepdim, at::Tensor& out) {
+    const c10::DeviceGuard guard(self.device());
+    CallContext ctx(self);
+    Wrapped o(out), s(self);
+    const int64_t d = dim.has_value() ? *dim : 0;
+    DIPU_B200_CALL(diopiArgmax(&ctx, &o, &s, dim.has_value() ? &d : nullptr, keepdim));
+    return out;
+}
+
+std::tuple<at::Tensor&, at::Tensor&> topk_values(const at::Tensor& self, int64_t k, int64_t dim, bool largest, bool sorted, at::Tensor& values,
+                                                 at::Tensor& indices) {
+    const c10::DeviceGuard guard(self.device());
+    CallContext ctx(self);
+    Wrapped v(values), i(indices), s(self);
+    DIPU_B200_CALL(diopiTopk(&ctx, &v, &i, &s, k, dim, largest, sorted));
+    return {values, indices};
+}
+
+std::tuple<at::Tensor&, at::Tensor&> sort_values_stable(const at::Tensor& self, std::optional<bool> stable, int64_t dim, bool descending,
+                                                        at::Tensor& values, at::Tensor& indices) {
+    const c10::DeviceGuard guard(self.device());
+    CallContext ctx(self);
+    Wrapped v(values), i(indices), s(self);
+    const bool st = stable.value_or(false);
+    DIPU_B200_CALL(diopiSort(&ctx, &v, &i, &s, at::maybe_wrap_dim(dim, self.dim()), descending, &st));
+    return {values, indices};
+}
+
+at::Tensor& cumsum_out(const at::Tensor& self, int64_t dim, std::optional<at::ScalarType> dtype, at::Tensor& out) {
+    (void)dtype;  // `out` has the result dtype; the library converts while it loads
+    const c10::DeviceGuard guard(self.device());
+    CallContext ctx(self);
+    Wrapped o(out), s(self);
+    DIPU_B200_CALL(diopiCumsum(&ctx, &o, &s, dim));
+    return out;
+}
+
+at::Tensor& gather_out(const at::Tensor& self, int64_t dim, const at::Tensor& index, bool sparse_grad, at::Tensor& out) {
+    (void)sparse_grad;
+    const c10::DeviceGuard guard(self.device());
+    CallContext ctx(self);
+    Wrapped o(out), s(self), i(index);
+    DIPU_B200_CALL(diopiGather(&ctx, &o, &s, dim, &i));
+    return out;
+}
+
+at::Tensor multinomial(const at::Tensor& self, int64_t num_samples, bool replacement, std::optional<at::Generator> generator) {
+    TORCH_CHECK(!generator.has_value() || !generator->defined(), "multinomial on dipu: pass no generator (the library's default stream is used)");
+    const c10::DeviceGuard guard(self.device());
+    at::Tensor out = self.dim() == 2 ? at::empty({self.size(0), num_samples}, self.options().dtype(at::kLong))
+                                     : at::empty({num_samples}, self.options().dtype(at::kLong));
+    CallContext ctx(self);
+    Wrapped o(out), s(self);
+    DIPU_B200_CALL(diopiMultinomial(&ctx, &o, &s, num_samples, replacement, nullptr));
+    return out;
+}
+
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+    m.impl("argmax.out", &argmax_out);
+    m.impl("topk.values", &topk_values);
+    m.impl("sort.values_stable", &sort_values_stable);
+    m.impl("cumsum.out", &cumsum_out);
+    m.impl("gather.out", &gather_out);
+    m.impl("multinomial", &multinomial);
     m.impl("add.out", &add_out);
     m.impl("sub.out", &sub_out);
     m.impl("mul.out", &mul_out);

@@ -162,7 +162,27 @@ def test_single_ops_against_cpu(adapter):
         torch.testing.assert_close(out.cpu(), want, rtol=1e-5, atol=1e-5)
 
 
+def test_sampling_ops_through_the_adapter(adapter):
+    dev = torch.device("dipu:0")
+    g = torch.Generator().manual_seed(5)
+    logits = torch.randn(4, 5000, generator=g)
+    ld = logits.to(dev)
+    with torch.no_grad():
+        assert torch.equal(torch.argmax(ld, dim=-1).cpu(), torch.argmax(logits, dim=-1))
+        v, i = torch.topk(ld, 20, dim=-1)
+        rv, ri = torch.topk(logits, 20, dim=-1)
+        assert torch.equal(v.cpu(), rv) and torch.equal(i.cpu(), ri)
+        sv, si = torch.sort(torch.softmax(ld, -1), dim=-1, descending=True, stable=True)
+        rsv, rsi = torch.sort(torch.softmax(logits, -1), dim=-1, descending=True, stable=True)
+        torch.testing.assert_close(sv.cpu(), rsv, rtol=1e-5, atol=1e-8)
+        torch.testing.assert_close(torch.cumsum(sv, -1).cpu(), torch.cumsum(rsv, -1), rtol=1e-4, atol=1e-5)
+        pos = torch.multinomial(sv, 1)
+        assert pos.shape == (4, 1) and pos.dtype == torch.int64
+        tok = torch.gather(si, 1, pos)
+        assert torch.equal(tok.cpu(), si.cpu().gather(1, pos.cpu()))
+
+
 def test_missing_wrapper_raises_instead_of_falling_back(adapter):
     x = torch.ones(8, device="dipu:0")
     with pytest.raises(NotImplementedError):
-        torch.cumsum(x, 0)
+        torch.flip(x, [0])
