@@ -177,8 +177,8 @@ __global__ void __launch_bounds__(256) gather_kernel(const void* self, int items
 // ---- sort / top-k -------------------------------------------------------------------------------------------------------------
 // One CTA per slice sorts 64-bit composites (order-preserving key << 32 | position) with a bitonic network: equal keys
 // keep their original order (the position breaks the tie), which is torch's stable order, and "descending" only flips the
-// key bits. Slices of up to 16384 elements (after padding to a power of two) live in shared memory, longer ones in a
-// workspace that stays in L2. The first n_out sorted elements are written out (n_out = n for sort, k for top-k).
+// key bits. The network runs on chunks of up to 16384 elements in shared memory; only the few stages that pair elements
+// of different chunks touch the workspace in L2 (one such stage for a 32 k vocabulary). The first n_out sorted elements are written out (n_out = n for sort, k for top-k).
 constexpr int kSortThreads = 1024;
 constexpr int64_t kSortSmemElems = 16384;
 
@@ -194,38 +194,64 @@ struct SortArgs {
     uint32_t flip;       // 0xffffffff for descending
 };
 
+// One compare-exchange stage of the network over `count` elements of `buf` whose first element has global position `origin`
+// (the direction of a pair depends on its global position and the size of the bitonic sequences being merged).
+__device__ __forceinline__ void bitonic_stage(unsigned long long* buf, int64_t count, int64_t origin, int64_t size, int64_t stride) {
+    const int64_t mask = stride - 1;
+    for (int64_t t = threadIdx.x; t < (count >> 1); t += kSortThreads) {
+        const int64_t i = ((t & ~mask) << 1) | (t & mask);
+        const int64_t p = i + stride;
+        const bool up = ((origin + i) & size) == 0;
+        const unsigned long long x = buf[i], y = buf[p];
+        if ((x > y) == up) {
+            buf[i] = y;
+            buf[p] = x;
+        }
+    }
+    __syncthreads();
+}
+
 __global__ void __launch_bounds__(kSortThreads) sort_kernel(const SortArgs a) {
     extern __shared__ unsigned long long sort_smem[];
     const int64_t slice = blockIdx.x;
     const int64_t o = slice / a.s.inner, k = slice - o * a.s.inner;
     const int64_t base = o * a.s.n * a.s.inner + k;
-    unsigned long long* buf = a.work != nullptr ? a.work + slice * a.n_pad : sort_smem;
-    for (int64_t j = threadIdx.x; j < a.n_pad; j += kSortThreads) {
-        unsigned long long c = ~0ull;  // padding sorts to the end
-        if (j < a.s.n) c = (static_cast<unsigned long long>(load_key(a.in, a.dt, base + j * a.s.inner) ^ a.flip) << 32) | static_cast<uint32_t>(j);
-        buf[j] = c;
-    }
-    __syncthreads();
-    const int64_t half = a.n_pad >> 1;
-    for (int64_t size = 2; size <= a.n_pad; size <<= 1) {
-        for (int64_t stride = size >> 1; stride > 0; stride >>= 1) {
-            for (int64_t t = threadIdx.x; t < half; t += kSortThreads) {
-                const int64_t i = (t / stride) * 2 * stride + (t % stride);
-                const int64_t p = i + stride;
-                const bool up = (i & size) == 0;
-                const unsigned long long x = buf[i], y = buf[p];
-                if ((x > y) == up) {
-                    buf[i] = y;
-                    buf[p] = x;
-                }
-            }
+    const int64_t chunk = a.n_pad < kSortSmemElems ? a.n_pad : kSortSmemElems;   // elements sorted in shared memory at a time
+    unsigned long long* work = a.work != nullptr ? a.work + slice * a.n_pad : nullptr;
+    // phase 1: every chunk becomes a sorted run (alternating directions, as the network wants them), in shared memory
+    for (int64_t c0 = 0; c0 < a.n_pad; c0 += chunk) {
+        for (int64_t j = threadIdx.x; j < chunk; j += kSortThreads) {
+            const int64_t g = c0 + j;
+            unsigned long long c = ~0ull;  // padding sorts to the end
+            if (g < a.s.n) c = (static_cast<unsigned long long>(load_key(a.in, a.dt, base + g * a.s.inner) ^ a.flip) << 32) | static_cast<uint32_t>(g);
+            sort_smem[j] = c;
+        }
+        __syncthreads();
+        for (int64_t size = 2; size <= chunk; size <<= 1) {
+            for (int64_t stride = size >> 1; stride > 0; stride >>= 1) bitonic_stage(sort_smem, chunk, c0, size, stride);
+        }
+        if (work != nullptr) {
+            for (int64_t j = threadIdx.x; j < chunk; j += kSortThreads) work[c0 + j] = sort_smem[j];
             __syncthreads();
         }
     }
+    // phase 2 (slices longer than a chunk): the merges across chunks run on the workspace (it stays in L2), everything
+    // below a chunk's length again in shared memory
+    for (int64_t size = chunk << 1; size <= a.n_pad; size <<= 1) {
+        for (int64_t stride = size >> 1; stride >= chunk; stride >>= 1) bitonic_stage(work, a.n_pad, 0, size, stride);
+        for (int64_t c0 = 0; c0 < a.n_pad; c0 += chunk) {
+            for (int64_t j = threadIdx.x; j < chunk; j += kSortThreads) sort_smem[j] = work[c0 + j];
+            __syncthreads();
+            for (int64_t stride = chunk >> 1; stride > 0; stride >>= 1) bitonic_stage(sort_smem, chunk, c0, size, stride);
+            for (int64_t j = threadIdx.x; j < chunk; j += kSortThreads) work[c0 + j] = sort_smem[j];
+            __syncthreads();
+        }
+    }
+    const unsigned long long* sorted = work != nullptr ? work : sort_smem;
     // output slice geometry: the operated dimension has n_out elements
     const int64_t obase = o * a.n_out * a.s.inner + k;
     for (int64_t r = threadIdx.x; r < a.n_out; r += kSortThreads) {
-        const int64_t j = static_cast<int64_t>(buf[r] & 0xffffffffull);
+        const int64_t j = static_cast<int64_t>(sorted[r] & 0xffffffffull);
         if (a.values != nullptr) copy_element(a.values, obase + r * a.s.inner, a.in, base + j * a.s.inner, a.itemsize);
         if (a.indices != nullptr) a.indices[obase + r * a.s.inner] = j;
     }
@@ -252,9 +278,9 @@ diopiError_t launch_sort(diopiContextHandle_t ctx, const char* name, const Tenso
     a.n_pad = n_pad;
     a.n_out = n_out;
     a.flip = descending ? 0xffffffffu : 0u;
-    size_t smem = 0;
-    if (n_pad <= kSortSmemElems) {
-        smem = static_cast<size_t>(n_pad) * sizeof(unsigned long long);
+    const int64_t chunk = n_pad < kSortSmemElems ? n_pad : kSortSmemElems;
+    const size_t smem = static_cast<size_t>(chunk) * sizeof(unsigned long long);
+    {
         static bool attr_set[64] = {false};
         int dev = 0;
         cudaGetDevice(&dev);
@@ -262,7 +288,8 @@ diopiError_t launch_sort(diopiContextHandle_t ctx, const char* name, const Tenso
             B200_CUDA(cudaFuncSetAttribute(sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSortSmemElems * sizeof(unsigned long long))));
             attr_set[dev] = true;
         }
-    } else {
+    }
+    if (n_pad > chunk) {
         diopiTensorHandle_t ws = nullptr;
         const int64_t bytes = s.outer * s.inner * n_pad * static_cast<int64_t>(sizeof(unsigned long long));
         B200_CHECK(diopiRequireBuffer(ctx, &ws, bytes, diopi_device) == diopiSuccess && ws != nullptr, "%s: workspace allocation failed", name);

@@ -226,7 +226,7 @@ def attention_case(case, diopi, ctx, dev):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ops", default="all", help="comma list of: %s, gemm, attention" % ", ".join(MEM_OPS))
+    ap.add_argument("--ops", default="all", help="comma list of: %s, gemm, attention, sampling" % ", ".join(MEM_OPS))
     ap.add_argument("--tokens", default="1,64,1024,16384,65536")
     ap.add_argument("--gemm", default="all", help="comma list of indices into the GEMM case table, or 'all'")
     ap.add_argument("--attention", default="all", help="comma list of indices into the attention case table, or 'all'")
@@ -243,9 +243,32 @@ def main():
     stream = torch.cuda.current_stream()
     ctx = diopi.Context(stream=stream.cuda_stream, device=0)
     hbm, tflops, src = peaks()
-    ops = MEM_OPS + ["gemm", "attention"] if args.ops == "all" else args.ops.split(",")
+    ops = MEM_OPS + ["gemm", "attention", "sampling"] if args.ops == "all" else args.ops.split(",")
     tokens = [int(x) for x in args.tokens.split(",")]
     for op in ops:
+        if op == "sampling":
+            # one sampling step over a [64, 32000] fp32 logits matrix, each operator timed on its own
+            b, v = 64, 32000
+            g = torch.Generator(device=dev)
+            g.manual_seed(7)
+            logits = torch.randn((b, v), generator=g, device=dev, dtype=torch.float32)
+            probs = torch.softmax(logits, -1)
+            vals, idx = torch.empty_like(logits), torch.empty((b, v), dtype=torch.int64, device=dev)
+            tv, ti = torch.empty((b, 50), device=dev), torch.empty((b, 50), dtype=torch.int64, device=dev)
+            am, pick = torch.empty((b,), dtype=torch.int64, device=dev), torch.empty((b, 1), dtype=torch.int64, device=dev)
+            cum = torch.empty_like(logits)
+            cases = [("argmax", lambda: diopi.diopiArgmax(ctx, am, logits, 1, False), 4 * b * v),
+                     ("topk k=50", lambda: diopi.diopiTopk(ctx, tv, ti, logits, 50, 1, True, True), 4 * b * v),
+                     ("sort descending", lambda: diopi.diopiSort(ctx, vals, idx, probs, 1, True, True), 16 * b * v),
+                     ("cumsum", lambda: diopi.diopiCumsum(ctx, cum, probs, 1), 8 * b * v),
+                     ("multinomial 1 sample", lambda: diopi.diopiMultinomial(ctx, pick, probs, 1, True, None), 4 * b * v),
+                     ("gather", lambda: diopi.diopiGather(ctx, pick, idx, 1, pick), 16 * b)]
+            for label, fn, alg in cases:
+                ms = time_cases([fn], args.iters, stream)
+                print(json.dumps({"op": "sampling", "case": label, "rows": b, "vocabulary": v, "us": round(ms * 1e3, 2), "algorithmic_bytes": alg,
+                                  "gbs": round(alg / (ms * 1e-3) / 1e9, 1)}), flush=True)
+                ctx.release_workspace()
+            continue
         if op == "attention":
             which = range(len(ATTENTION_CASES)) if args.attention == "all" else [int(x) for x in args.attention.split(",")]
             for case in [ATTENTION_CASES[i] for i in which]:
