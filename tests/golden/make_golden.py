@@ -1,8 +1,8 @@
 """Generates the golden fixtures in this directory by running the REFERENCE's own Python code on CPU.
 
-Run once in a container that has the reference checkout (default /root/reference, override with REFERENCE_ROOT):
+Run once where a checkout of the reference project is available; REFERENCE_ROOT names its top directory:
 
-    python tests/golden/make_golden.py
+    REFERENCE_ROOT=<reference checkout> python tests/golden/make_golden.py
 
 It imports dicp/test/model/llama/model.py unmodified (only the relative import of a device helper is satisfied with a
 stub that answers "cpu") and records, for seeded inputs:
@@ -33,7 +33,9 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("REFERENCE_ROOT")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set REFERENCE_ROOT to the top directory of the reference checkout")
 sys.path.insert(0, ROOT)
 from oracle import llama_cpu  # noqa: E402
 
