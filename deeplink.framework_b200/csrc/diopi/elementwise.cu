@@ -45,6 +45,23 @@ B200_UNARY_FLOAT_OP(OpCos, m_cos(x))
 B200_UNARY_FLOAT_OP(OpTanh, m_tanh(x))
 B200_UNARY_FLOAT_OP(OpSigmoid, F(1) / (F(1) + m_exp(-x)))
 B200_UNARY_FLOAT_OP(OpSilu, x / (F(1) + m_exp(-x)))
+// 16-bit storage: ex2.approx and an approximate division (about 2 ulp of fp32 each) instead of the exact forms, which cost
+// more instructions per element than the memory system leaves room for
+template <typename C>
+struct OpSiluFast {
+    explicit OpSiluFast(const ScalarArgs&) {}
+    __device__ __forceinline__ C operator()(C a) const {
+        const float x = static_cast<float>(a);
+        return static_cast<C>(__fdividef(x, 1.0f + __expf(-x)));
+    }
+};
+}  // namespace
+template <>
+struct HalfOp<OpSilu> {
+    template <typename C>
+    using type = OpSiluFast<C>;
+};
+namespace {
 
 template <typename C>
 struct OpNeg {
