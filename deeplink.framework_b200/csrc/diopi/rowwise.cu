@@ -206,6 +206,57 @@ __global__ void __launch_bounds__(1024) softmax_row_kernel(const T* __restrict__
     }
 }
 
+// Rows of at most 256 vectors (2048 two-byte or 1024 four-byte elements - the rows of an attention score tensor): one
+// WARP per row and eight rows per CTA. A CTA per row would be 32 - 64 threads; at half a million rows the launch rate of
+// such tiny CTAs, not memory, bounds the kernel. Lane l owns vectors l, l + 32, ...; reductions are shuffles only.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(256) softmax_warp_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t rows, int64_t cols) {
+    constexpr int V = Vec16<T>::N;
+    const int lane = threadIdx.x & 31;
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const int nvec = static_cast<int>(cols / V);
+    const T* row = in + r * cols;
+    Vec16<T> x[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        if (i * 32 + lane < nvec) x[i] = ld16_stream(row + static_cast<int64_t>(i * 32 + lane) * V);
+    }
+    float f[VPT][V];
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const bool live = i * 32 + lane < nvec;
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            f[i][e] = live ? to_f32(x[i].v[e]) : -INFINITY;
+            m = fmaxf(m, f[i][e]);
+        }
+    }
+    m = warp_max(m);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            f[i][e] = (sizeof(T) == 2) ? __expf(f[i][e] - m) : expf(f[i][e] - m);  // exp(-inf) = 0 for the padding lanes
+            s += f[i][e];
+        }
+    }
+    s = warp_sum(s);
+    const float inv = 1.f / s;
+    T* orow = out + r * cols;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        if (i * 32 + lane < nvec) {
+            Vec16<T> y;
+#pragma unroll
+            for (int e = 0; e < V; ++e) y.v[e] = from_f32<T>(f[i][e] * inv);
+            st16_stream(orow + static_cast<int64_t>(i * 32 + lane) * V, y);
+        }
+    }
+}
+
 // ---- row sum / mean --------------------------------------------------------------------------------------------------
 template <typename T, int VPT>
 __global__ void __launch_bounds__(1024) rowsum_kernel(const T* __restrict__ in, void* out, diopiDtype_t out_dt, int64_t cols, float scale) {
@@ -433,6 +484,20 @@ diopiError_t diopiSoftmax(diopiContextHandle_t ctx, diopiTensorHandle_t out, dio
     RowCfg cfg;
     if (inner == 1 && vo.dtype == vx.dtype && row_fast_ok(vx, n, &cfg) && vo.aligned(16) && outer <= 0x7fffffffLL) {
         const unsigned grid = static_cast<unsigned>(outer);
+        const int64_t nvec = n * vx.itemsize / 16;
+        if (nvec <= 256 && outer >= 1024) {
+            // many short rows: a warp per row
+            const unsigned wgrid = static_cast<unsigned>((outer + 7) / 8);
+            const int wvpt = nvec <= 32 ? 1 : (nvec <= 64 ? 2 : (nvec <= 128 ? 4 : 8));
+#define LAUNCH_SMW(T) \
+    B200_DISPATCH_VPT(wvpt, (softmax_warp_kernel<T, VPT><<<wgrid, 256, 0, stream>>>(static_cast<const T*>(vx.data), static_cast<T*>(vo.data), outer, n)))
+            if (vx.dtype == diopi_dtype_bfloat16) { LAUNCH_SMW(bf16); }
+            else if (vx.dtype == diopi_dtype_float16) { LAUNCH_SMW(fp16); }
+            else { LAUNCH_SMW(float); }
+#undef LAUNCH_SMW
+            B200_LAUNCH_CHECK("diopiSoftmax");
+            return diopiSuccess;
+        }
 #define LAUNCH_SM(T) \
     B200_DISPATCH_VPT(cfg.vpt, (softmax_row_kernel<T, VPT><<<grid, cfg.threads, 0, stream>>>(static_cast<const T*>(vx.data), static_cast<T*>(vo.data), n)))
         if (vx.dtype == diopi_dtype_bfloat16) { LAUNCH_SM(bf16); }

@@ -443,6 +443,23 @@ def test_sweep_softmax_bf16(diopi, ctx, t):
     check_bf16(out, torch.softmax(x.float(), -1))
 
 
+@pytest.mark.parametrize("rows,cols,dtype", [(4096, 2048, torch.bfloat16), (2000, 264, torch.bfloat16), (1500, 1000, torch.float32),
+                                            (1025, 8, torch.float16), (3000, 1024, torch.float32)])
+def test_softmax_many_short_rows(diopi, ctx, rows, cols, dtype):
+    """Score-tensor-like inputs (many rows of at most 256 vectors) take the warp-per-row kernel; causal -inf entries, in place."""
+    x = rnd((rows, cols), dtype, seed=rows, scale=3.0)
+    k = min(rows, cols)
+    x[:k, :k] = (x[:k, :k].float() + torch.triu(torch.full((k, k), float("-inf")), diagonal=1)).to(dtype)
+    xd = x.to(DEV)
+    diopi.diopiSoftmax(ctx, xd, xd, -1)
+    ref = torch.softmax(x.float(), -1)
+    if dtype == torch.float32:
+        check_close(xd, ref, 1e-4, 1e-6)
+    else:
+        check_bf16(xd, ref)
+    assert torch.isfinite(xd.float()).all()
+
+
 def test_softmax_reference_cases(diopi, ctx):
     # dipu/tests/python/unittests/test_softmax.py:24-70: fp32, U(0,10), dim = 0 and last
     g = torch.Generator().manual_seed(1)
