@@ -40,12 +40,12 @@ constexpr int kThreads = 192;
 constexpr int kGroupM = 8;
 constexpr int kSmemLimit = 232448;  // 227 KiB per CTA
 
-template <int BN>
+template <int BN, int EPI = 4>
 struct TileCfg {
     static constexpr int kABytes = BM * BK * 2;
     static constexpr int kBBytes = BN * BK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStoreBytes = 4 /*warps*/ * 2 /*buffers*/ * 32 /*rows*/ * 128 /*bytes*/;  // epilogue staging
+    static constexpr int kStoreBytes = EPI /*warps*/ * 2 /*buffers*/ * 32 /*rows*/ * 128 /*bytes*/;  // epilogue staging
     static constexpr int kStagesRaw = (kSmemLimit - 1024 - 512 - kStoreBytes) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
     static constexpr int kTmemCols = (2 * BN) < 32 ? 32 : (2 * BN);
@@ -113,11 +113,15 @@ __device__ __forceinline__ void store_chunk(const TcParams& p, const uint32_t (&
     }
 }
 
-template <int BN, typename TOut>
-__global__ void __launch_bounds__(kThreads, 1)
+// EPI: epilogue warps, 4 or 8. With 8, two warps share each 32-lane quarter of the accumulator and take half of the tile's
+// columns each: for products with a short K loop (Q K^T: two K blocks per 64 KiB output tile) the epilogue, not the
+// tensor pipe, is the critical path, and its per-piece latency chain (TMEM load, convert, stage, bulk store) needs more
+// warps in flight to keep the store stream busy.
+template <int BN, typename TOut, int EPI>
+__global__ void __launch_bounds__(64 + 32 * EPI, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
                const TcParams p) {
-    using Cfg = TileCfg<BN>;
+    using Cfg = TileCfg<BN, EPI>;
     constexpr int STAGES = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
     // 128-byte swizzle patterns repeat every 1024 bytes: stage buffers must start on that boundary
@@ -144,7 +148,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&acc_full[a], 1);
-            mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
+            mbar_init(&acc_empty[a], EPI);  // one arrival per epilogue warp
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -228,8 +232,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
     } else {
-        // ---------------- epilogue (warps 2..5) ----------------
+        // ---------------- epilogue (warps 2 .. 2+EPI-1) ----------------
         const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are the ones this warp may read
+        const int half = (warp - 2) >> 2;  // with eight warps: which half of the tile's columns this warp converts
         int local = 0;
         uint32_t store_seq = 0;
         bool ok = true;
@@ -249,8 +254,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 constexpr int PIECE_COLS = 128 / static_cast<int>(sizeof(TOut));
                 constexpr int LOADS = PIECE_COLS / 32;
                 uint8_t* stage_base = smem_c + (warp - 2) * (2 * 32 * 128);
+                constexpr int PIECES = BN / PIECE_COLS;
+                const int c_begin = EPI == 8 ? half * (PIECES / 2) : 0;
+                const int c_end = EPI == 8 ? c_begin + PIECES / 2 : PIECES;
 #pragma unroll 1
-                for (int c = 0; c < BN / PIECE_COLS; ++c) {
+                for (int c = c_begin; c < c_end; ++c) {
                     const int col0 = nb * BN + c * PIECE_COLS;
                     if (col0 >= p.N) break;  // warp-uniform
                     uint8_t* buf = stage_base + (store_seq & 1) * (32 * 128);
@@ -308,8 +316,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     ++store_seq;
                 }
             } else {
+                const int s_begin = EPI == 8 ? half * (BN / 64) : 0;
+                const int s_end = EPI == 8 ? s_begin + BN / 64 : BN / 32;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = s_begin; c < s_end; ++c) {
                     const int col0 = nb * BN + c * 32;
                     if (col0 >= p.N) break;  // warp-uniform
                     uint32_t r[32];
@@ -597,29 +607,31 @@ uint32_t* status_word() {
     return words[dev];
 }
 
-template <int BN, typename TOut>
+template <int BN, typename TOut, int EPI>
 cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const TcParams& p, int grid, cudaStream_t stream) {
-    using Cfg = TileCfg<BN>;
+    using Cfg = TileCfg<BN, EPI>;
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, TOut, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    gemm_tc_kernel<BN, TOut><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(ma, mb, mc, p);
+    gemm_tc_kernel<BN, TOut, EPI><<<grid, 64 + 32 * EPI, Cfg::kSmemBytes, stream>>>(ma, mb, mc, p);
     return cudaPeekAtLastError();
 }
 
 template <typename TOut>
 cudaError_t launch_tc_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const TcParams& p, int grid,
                          cudaStream_t stream) {
+    // eight epilogue warps where the K loop is too short to hide the epilogue (and the tile is wide enough to split)
+    const bool wide_epilogue = p.k_blocks <= 8 && bn >= 128;
     switch (bn) {
-        case 256: return launch_tc<256, TOut>(ma, mb, mc, p, grid, stream);
-        case 128: return launch_tc<128, TOut>(ma, mb, mc, p, grid, stream);
-        case 64: return launch_tc<64, TOut>(ma, mb, mc, p, grid, stream);
-        default: return launch_tc<32, TOut>(ma, mb, mc, p, grid, stream);
+        case 256: return wide_epilogue ? launch_tc<256, TOut, 8>(ma, mb, mc, p, grid, stream) : launch_tc<256, TOut, 4>(ma, mb, mc, p, grid, stream);
+        case 128: return wide_epilogue ? launch_tc<128, TOut, 8>(ma, mb, mc, p, grid, stream) : launch_tc<128, TOut, 4>(ma, mb, mc, p, grid, stream);
+        case 64: return launch_tc<64, TOut, 4>(ma, mb, mc, p, grid, stream);
+        default: return launch_tc<32, TOut, 4>(ma, mb, mc, p, grid, stream);
     }
 }
 

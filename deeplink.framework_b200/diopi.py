@@ -130,7 +130,7 @@ class Context:
         return _host.minihostWorkspaceCount(self.ptr)
 
     def __del__(self):
-        if getattr(self, "ptr", None):
+        if getattr(self, "ptr", None) and _host is not None:  # at interpreter exit the module globals may already be gone
             _host.minihostFreeContext(self.ptr)
             self.ptr = None
 
