@@ -250,7 +250,12 @@ def main():
     gi.manual_seed(SEED + 2)
     ids_host = torch.randint(0, VOCAB, (batch, seq), generator=gi, dtype=torch.int64).pin_memory()
     ids_dev = torch.empty((batch, seq), dtype=torch.int64, device=device)
-    out_host = [torch.empty((tokens, cfg.hidden), dtype=dtype).pin_memory() for _ in range(2)]  # double-buffered results
+    # the layer output is replicated after the last all-reduce: every rank returns its own 1/N of the token rows to its host
+    # process, so the N PCIe links share the transfer (N = 1: the whole tensor)
+    rows_per_rank = (tokens + world - 1) // world
+    row_lo = min(rank * rows_per_rank, tokens)
+    row_hi = min(row_lo + rows_per_rank, tokens)
+    out_host = [torch.empty((max(row_hi - row_lo, 1), cfg.hidden), dtype=dtype).pin_memory() for _ in range(2)]  # double-buffered results
     copy_stream = devapis.getStreamFromPool(local_rank)   # D2H of step i overlaps the compute of step i+1
     copy_events = [devapis.getEventFromPool(), devapis.getEventFromPool()]
     done_events = [devapis.getEventFromPool(), devapis.getEventFromPool()]
@@ -293,13 +298,14 @@ def main():
         devapis.memCopyH2DAsync(stream.cuda_stream, ids_host.numel() * 8, ids_dev.data_ptr(), ids_host.data_ptr())  # this step's input
         h = L.embed(table, ids_dev, ctx)
         y = run_layers(h)
-        if rank != 0:
-            return y  # the layer output is replicated after the all-reduce: one rank returns it to the host
+        if row_hi <= row_lo:
+            return y
         devapis.recordEvent(copy_events[i], stream.cuda_stream)
         devapis.streamWaitEvent(copy_stream, copy_events[i])
         if e2e_state["i"] > 2:
             devapis.waitEvent(done_events[i])  # the host buffer's previous copy (two steps back) has landed
-        devapis.memCopyD2HAsync(copy_stream, y.numel() * y.element_size(), out_host[i].data_ptr(), y.data_ptr())  # this step's result
+        row_bytes = cfg.hidden * y.element_size()
+        devapis.memCopyD2HAsync(copy_stream, (row_hi - row_lo) * row_bytes, out_host[i].data_ptr(), y.data_ptr() + row_lo * row_bytes)  # this step's result
         devapis.recordEvent(done_events[i], copy_stream)
         if not args.no_caching_allocator:
             devapis.CachingAllocator.recordStream(y.data_ptr(), copy_stream)
@@ -478,8 +484,9 @@ def main():
                                       + 3 * cfg.hidden * cfg.ffn) // world) >> 20, (tokens * cfg.hidden * 2) >> 20),
                        "allocator": "torch default" if args.no_caching_allocator else "b200 caching allocator (pluggable)"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": ids_host.numel() * 8,
-                    "d2h_bytes_per_step": out_host[0].numel() * out_host[0].element_size(),
-                    "note": "result copied back on a pool stream, overlapping the next step's compute"},
+                    "d2h_bytes_per_step": tokens * cfg.hidden * 2,
+                    "note": "result copied back on a pool stream, overlapping the next step's compute"
+                            + ("" if world == 1 else "; each rank returns its 1/%d of the (replicated) output rows" % world)},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": roofline,

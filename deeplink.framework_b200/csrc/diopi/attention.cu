@@ -271,29 +271,24 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const int k0 = j * kBlockKv;
             // warp-uniform: does any element of this tile x block need the mask?
             const bool need_mask = (k0 + kBlockKv > p.Skv) || (p.causal && k0 + kBlockKv - 1 > q_lo + p.causal_off);
-            float mx = neg_inf;
+            // Row maximum of the RAW scores (the scale is positive, so it commutes with the maximum); four independent
+            // running maxima: with two softmax warps per scheduler there is little else to hide a 128-long dependent chain
             if (need_mask) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        float v = __uint_as_float(s[c][i]) * p.scale_log2;
-                        if (k0 + c * 32 + i > k_visible) v = neg_inf;
-                        s[c][i] = __float_as_uint(v);
-                        mx = fmaxf(mx, v);
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float v = __uint_as_float(s[c][i]) * p.scale_log2;
-                        s[c][i] = __float_as_uint(v);
-                        mx = fmaxf(mx, v);
+                        if (k0 + c * 32 + i > k_visible) s[c][i] = __float_as_uint(neg_inf);
                     }
                 }
             }
+            float mxs[4] = {neg_inf, neg_inf, neg_inf, neg_inf};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mxs[i & 3] = fmaxf(mxs[i & 3], __uint_as_float(s[c][i]));
+            }
+            const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])) * p.scale_log2;  // -inf stays -inf
             // The running maximum only moves when some row of the warp outgrew it by more than the threshold: P stays
             // below 2^8 and most blocks need no pass over O.
             float factor = 1.f;
@@ -327,7 +322,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 }
             }
             const float base = (m_used == neg_inf) ? 0.f : m_used;
-            float part = 0.f;
+            float parts[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
 #pragma unroll
@@ -335,8 +330,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     float e[8];
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
-                        e[u] = fast_exp2(__uint_as_float(s[c][i + u]) - base);
-                        part += e[u];
+                        // scale and shift in one FMA: exp2(s * scale * log2(e) - m)
+                        e[u] = fast_exp2(fmaf(__uint_as_float(s[c][i + u]), p.scale_log2, -base));
+                        parts[u & 3] += e[u];
                     }
                     uint4 w;
                     w.x = pack2<T>(e[0], e[1]);
@@ -349,7 +345,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     *reinterpret_cast<uint4*>(pbuf + (c >> 1) * kHalfBytes + r_in_tile * 128 + ((chunk ^ (r_in_tile & 7)) * 16)) = w;
                 }
             }
-            l_sum += part;
+            l_sum += (parts[0] + parts[1]) + (parts[2] + parts[3]);
             fence_proxy_async();  // generic-proxy writes of P -> visible to the tensor core's reads
             tc_fence_before();
             __syncwarp();
