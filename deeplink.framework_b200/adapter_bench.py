@@ -40,9 +40,9 @@ def rotate_half(x):
 
 
 class Block(nn.Module):
-    def __init__(self, dim, heads, ffn):
+    def __init__(self, dim, heads, ffn, sdpa=False):
         super().__init__()
-        self.heads, self.head_dim = heads, dim // heads
+        self.heads, self.head_dim, self.sdpa = heads, dim // heads, sdpa
         self.wq, self.wk, self.wv, self.wo = (nn.Linear(dim, dim, bias=False) for _ in range(4))
         self.w1, self.w3 = nn.Linear(dim, ffn, bias=False), nn.Linear(dim, ffn, bias=False)
         self.w2 = nn.Linear(ffn, dim, bias=False)
@@ -56,9 +56,13 @@ class Block(nn.Module):
         v = self.wv(h).view(b, s, self.heads, self.head_dim).transpose(1, 2)
         q = q * cos + rotate_half(q) * sin
         k = k * cos + rotate_half(k) * sin
-        scores = torch.matmul(q, k.transpose(2, 3)) / math.sqrt(self.head_dim)
-        scores = F.softmax(scores + mask, dim=-1)
-        a = torch.matmul(scores, v).transpose(1, 2).contiguous().view(b, s, -1)
+        if self.sdpa:
+            # torch's own fused-attention entry: on the dipu device it reaches diopiMultiHeadAttention
+            a = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(b, s, -1)
+        else:
+            scores = torch.matmul(q, k.transpose(2, 3)) / math.sqrt(self.head_dim)
+            scores = F.softmax(scores + mask, dim=-1)
+            a = torch.matmul(scores, v).transpose(1, 2).contiguous().view(b, s, -1)
         x = x + self.wo(a)
         h = self.ffn_norm(x)
         return x + self.w2(F.silu(self.w1(h)) * self.w3(h))
@@ -69,6 +73,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--sdpa", action="store_true", help="attention through F.scaled_dot_product_attention instead of matmul / softmax / matmul")
     args = ap.parse_args()
     import __graft_entry__ as entry
     pkg = entry.load_package()
@@ -78,7 +83,7 @@ def main():
     dim, heads, ffn, bf = 4096, 32, 11008, torch.bfloat16
     torch.manual_seed(1234)
     with torch.no_grad():
-        block = Block(dim, heads, ffn)
+        block = Block(dim, heads, ffn, sdpa=args.sdpa)
         for p in block.parameters():
             if p.dim() == 2:
                 nn.init.normal_(p, std=0.02)
@@ -125,7 +130,8 @@ def main():
     ctypes_us = (time.perf_counter() - t0) * 1e6 / n
     devapis.syncStream(stream)
     tokens = args.batch * args.seq
-    print(json.dumps({"workload": "plain-torch Llama-style block on torch.device('dipu'), bf16, batch %d x seq %d" % (args.batch, args.seq),
+    print(json.dumps({"workload": "plain-torch Llama-style block on torch.device('dipu'), bf16, batch %d x seq %d, attention by %s"
+                                  % (args.batch, args.seq, "F.scaled_dot_product_attention" if args.sdpa else "matmul / softmax / matmul"),
                       "ms_per_step": round(ms, 3), "tokens_per_s": round(tokens / (ms * 1e-3)), "host_ms_per_step": round(host_ms, 3),
                       "diopi_calls_per_step": int(calls), "add_1_element_host_us": {"torch dispatch + wrapper": round(adapter_us, 2),
                                                                                      "ctypes binding": round(ctypes_us, 2)}}))

@@ -2,9 +2,13 @@
 // the reference's generated wrapper calls for it (dipu/scripts/autogen_diopi_wrapper/diopi_functions.yaml, lines cited per
 // op). Structured ops are registered through their `.out` overload only: torch's structured wrappers derive the functional
 // and in-place forms from it, with output shape, dtype promotion and allocation done by the op's meta function.
+#include <cmath>
+
 #include <ATen/ExpandUtils.h>
 #include <ATen/WrapDimUtils.h>
 #include <ATen/WrapDimUtilsMulti.h>
+#include <ATen/native/DispatchStub.h>
+#include <ATen/native/transformers/attention.h>
 #include <torch/library.h>
 
 #include "adapter_common.h"
@@ -372,7 +376,39 @@ at::Tensor multinomial(const at::Tensor& self, int64_t num_samples, bool replace
     return out;
 }
 
+// ---- fused attention: torch.nn.functional.scaled_dot_product_attention ------------------------------------------------------
+// torch routes SDPA on a PrivateUse1 device to _scaled_dot_product_fused_attention_overrideable when _fused_sdp_choice
+// answers "overrideable" (SDPBackend value 4). q / k / v arrive as [batch, heads, seq, dim] (usually transposed views of the
+// projection output); the library takes the [batch, seq, heads, dim] views by their pitches, so nothing is copied.
+int64_t fused_sdp_choice(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value, const std::optional<at::Tensor>& attn_mask,
+                         double dropout_p, bool is_causal, std::optional<double> scale, bool enable_gqa) {
+    (void)key; (void)value; (void)is_causal; (void)scale; (void)enable_gqa;
+    const bool fused = !attn_mask.has_value() && dropout_p == 0.0 && query.dim() == 4 && query.size(3) == 128 &&
+                       (query.scalar_type() == at::kBFloat16 || query.scalar_type() == at::kHalf);
+    return fused ? 4 /* overrideable */ : 0 /* math: the op-by-op composite */;
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, c10::SymInt, c10::SymInt, at::Tensor, at::Tensor, at::Tensor> sdpa_overrideable(
+    const at::Tensor& query, const at::Tensor& key, const at::Tensor& value, const std::optional<at::Tensor>& attn_bias, double dropout_p, bool is_causal,
+    bool return_debug_mask, std::optional<double> scale) {
+    TORCH_CHECK(!attn_bias.has_value() || !attn_bias->defined(), "fused attention on dipu takes no attn_bias (use is_causal)");
+    TORCH_CHECK(query.dim() == 4 && key.dim() == 4 && value.dim() == 4, "fused attention expects [batch, heads, seq, dim] tensors");
+    const c10::DeviceGuard guard(query.device());
+    const int64_t b = query.size(0), h = query.size(1), sq = query.size(2), d = query.size(3);
+    at::Tensor out = at::empty({b, sq, h, d}, query.options());                    // merged layout; returned as its [b, h, sq, d] view
+    at::Tensor lse = at::empty({b, h, sq}, query.options().dtype(at::kFloat));
+    const at::Tensor q = query.transpose(1, 2), k = key.transpose(1, 2), v = value.transpose(1, 2);
+    CallContext ctx(out);
+    Wrapped wq(q), wk(k), wv(v), wo(out), wl(lse);
+    const double sc = scale.has_value() ? *scale : 1.0 / std::sqrt(static_cast<double>(d));
+    DIPU_B200_CALL(diopiMultiHeadAttention(&ctx, &wq, &wk, &wv, dropout_p, is_causal, return_debug_mask, sc, &wo, &wl, nullptr, nullptr));
+    const at::Tensor none = at::empty({0}, query.options().dtype(at::kLong));
+    return {out.transpose(1, 2), lse, none, none, c10::SymInt(sq), c10::SymInt(key.size(2)), none, none, at::empty({0}, query.options())};
+}
+
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+    m.impl("_fused_sdp_choice", &fused_sdp_choice);  // the dispatcher op (Python-visible); SDPA itself asks the stub below
+    m.impl("_scaled_dot_product_fused_attention_overrideable", &sdpa_overrideable);
     m.impl("argmax.out", &argmax_out);
     m.impl("topk.values", &topk_values);
     m.impl("sort.values_stable", &sort_values_stable);
@@ -414,3 +450,18 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
 
 }  // namespace
 }  // namespace dipu_b200
+
+// scaled_dot_product_attention picks its backend through a dispatch stub, not the dispatcher: the PrivateUse1 slot of that
+// stub is this backend's to fill.
+namespace at::native {
+namespace {
+int64_t dipu_b200_sdp_choice(const Tensor& query, const Tensor& key, const Tensor& value, const std::optional<Tensor>& attn_mask, double dropout_p,
+                             bool is_causal, std::optional<double> scale, bool enable_gqa) {
+    (void)key; (void)value; (void)is_causal; (void)scale; (void)enable_gqa;
+    const bool fused = !attn_mask.has_value() && dropout_p == 0.0 && query.dim() == 4 && query.size(3) == 128 &&
+                       (query.scalar_type() == at::kBFloat16 || query.scalar_type() == at::kHalf);
+    return fused ? 4 /* SDPBackend::overrideable */ : 0 /* SDPBackend::math */;
+}
+}  // namespace
+REGISTER_PRIVATEUSE1_DISPATCH(_fused_sdp_choice_stub, &dipu_b200_sdp_choice)
+}  // namespace at::native

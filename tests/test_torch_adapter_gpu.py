@@ -162,6 +162,31 @@ def test_single_ops_against_cpu(adapter):
         torch.testing.assert_close(out.cpu(), want, rtol=1e-5, atol=1e-5)
 
 
+@pytest.mark.parametrize("kv_heads,causal", [(4, True), (4, False), (1, True)])
+def test_scaled_dot_product_attention_reaches_the_fused_kernel(adapter, kv_heads, causal):
+    """F.scaled_dot_product_attention on the dipu device dispatches to the library's fused attention (one DIOPI call, views
+    taken as they are); anything it cannot run (here: an explicit mask) takes torch's op-by-op composite instead."""
+    dev = torch.device("dipu:0")
+    g = torch.Generator().manual_seed(9)
+    b, s, h, d = 2, 300, 4, 128
+    q = torch.randn(b, s, h, d, generator=g).to(torch.bfloat16)
+    k = torch.randn(b, s, kv_heads, d, generator=g).to(torch.bfloat16)
+    v = torch.randn(b, s, kv_heads, d, generator=g).to(torch.bfloat16)
+    rep = h // kv_heads
+    ref = F.scaled_dot_product_attention(q.float().transpose(1, 2), k.float().transpose(1, 2).repeat_interleave(rep, 1),
+                                         v.float().transpose(1, 2).repeat_interleave(rep, 1), is_causal=causal)
+    with torch.no_grad():
+        before = adapter.stats()["diopi_calls"]
+        out = F.scaled_dot_product_attention(q.to(dev).transpose(1, 2), k.to(dev).transpose(1, 2), v.to(dev).transpose(1, 2), is_causal=causal,
+                                             enable_gqa=kv_heads != h)
+        calls = adapter.stats()["diopi_calls"] - before
+        got = out.float().cpu()
+    assert calls == 1, calls
+    assert out.shape == (b, h, s, d)
+    err, rel = (got - ref).abs().max().item(), ((got - ref).norm() / ref.norm()).item()
+    assert err <= 2e-2 and rel <= 5e-3, (err, rel)
+
+
 def test_sampling_ops_through_the_adapter(adapter):
     dev = torch.device("dipu:0")
     g = torch.Generator().manual_seed(5)
