@@ -5,6 +5,7 @@
     lib/libdiopirt_minihost.so   a small DIOPI host (the diopirt callbacks over plain tensor structs)
     lib/libdiopi_impl.so         the DIOPI operator library: hand-written sm_100a kernels
     lib/libtorch_dipu_b200.so             hot-path aten ops on the PrivateUse1 key ("dipu"), each wrapper calling ::diopiXxx
+    lib/dipu_b200_c10d.<abi>.so           the c10d backend "dicl" (torch.distributed on dipu tensors) as a Python extension module
     lib/libdipu_vendor_b200_torchabi.so   the vendor contract with DIPU's exact C++ signatures (namespace dipu::devapis, torch
                                  types in the arguments): thin wrappers over the C-ABI runtime, built when torch's headers are present
 
@@ -91,7 +92,18 @@ def _build_torch_adapter(verbose):
                             ["-l:libdipu_vendor_b200.so", "-l:libdiopirt_minihost.so", "-l:libdiopi_impl.so"], verbose)
 
 
-def _build_torch_lib(sub, out_name, link_libs, verbose):
+def _build_torch_c10d(verbose):
+    """csrc/torch_c10d/*.cpp: the c10d backend "dicl" as a Python extension module (pybind11 from torch's headers)."""
+    import sysconfig
+    suffix = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
+    py_inc = sysconfig.get_paths()["include"]
+    if not os.path.exists(os.path.join(py_inc, "Python.h")):
+        return None
+    return _build_torch_lib("torch_c10d", "dipu_b200_c10d" + suffix, ["-l:libtorch_dipu_b200.so", "-l:libdipu_vendor_b200.so"], verbose,
+                            extra_cflags=["-DTORCH_EXTENSION_NAME=dipu_b200_c10d", "-I", py_inc], extra_link=["-ltorch_python", "-ltorch"])
+
+
+def _build_torch_lib(sub, out_name, link_libs, verbose, extra_cflags=(), extra_link=()):
     try:
         import torch
         from torch.utils.cpp_extension import include_paths
@@ -106,7 +118,7 @@ def _build_torch_lib(sub, out_name, link_libs, verbose):
         obj = os.path.join(OBJ, sub + "_" + os.path.basename(src) + ".o")
         if not (os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(src), newest_hdr, os.path.getmtime(__file__))):
             cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-fvisibility=hidden", "-c", src, "-o", obj, "-I", os.path.join(ROOT, "include"),
-                   "-I", "/usr/local/cuda/include"] + ["-I" + p for p in incs]
+                   "-I", "/usr/local/cuda/include"] + ["-I" + p for p in incs] + list(extra_cflags)
             r = subprocess.run(cmd, capture_output=True, text=True)
             if r.returncode != 0:
                 raise RuntimeError("g++ failed for %s:\n%s\n%s" % (src, r.stdout, r.stderr))
@@ -115,7 +127,7 @@ def _build_torch_lib(sub, out_name, link_libs, verbose):
         objs.append(obj)
     out = os.path.join(LIB, out_name)
     if not (os.path.exists(out) and all(os.path.getmtime(out) >= os.path.getmtime(o) for o in objs)):
-        cmd = ["g++", "-shared", "-o", out] + objs + ["-L", LIB] + link_libs + ["-L", torch_lib, "-lc10", "-ltorch_cpu",
+        cmd = ["g++", "-shared", "-o", out] + objs + ["-L", LIB] + link_libs + ["-L", torch_lib] + list(extra_link) + ["-lc10", "-ltorch_cpu",
                                                        "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + torch_lib]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
@@ -153,6 +165,9 @@ def build(verbose=False):
     adapter = _build_torch_adapter(verbose)
     if adapter:
         built.append(adapter)
+        c10d = _build_torch_c10d(verbose)
+        if c10d:
+            built.append(c10d)
     return built
 
 

@@ -31,12 +31,14 @@ struct AdapterStats {
     int64_t allocations = 0;
     int64_t host_copies = 0;
 };
-AdapterStats& stats();
+// exported: the c10d backend library links against them
+#define DIPU_B200_EXPORT __attribute__((visibility("default")))
+DIPU_B200_EXPORT AdapterStats& stats();
 
-b200Stream_t current_stream(int device);
-c10::Allocator* device_allocator();
+DIPU_B200_EXPORT b200Stream_t current_stream(int device);
+DIPU_B200_EXPORT c10::Allocator* device_allocator();
 
-diopiDtype_t to_diopi_dtype(at::ScalarType t);
+DIPU_B200_EXPORT diopiDtype_t to_diopi_dtype(at::ScalarType t);
 
 // An at::Tensor described for the operator library (no ownership; valid while the tensor lives).
 struct Wrapped : diopiTensor {

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include <ATen/EmptyTensor.h>
+#include <ATen/detail/PrivateUse1HooksInterface.h>
 #include <ATen/native/Resize.h>
 #include <ATen/native/TensorShape.h>
 #include <c10/core/impl/DeviceGuardImplInterface.h>
@@ -135,10 +136,36 @@ struct GuardImpl final : c10::impl::DeviceGuardImplInterface {
 
 C10_REGISTER_GUARD_IMPL(PrivateUse1, GuardImpl);
 
+// What torch asks an accelerator backend outside of operator dispatch (torch.accelerator, torch.distributed.barrier, ...).
+struct Hooks final : at::PrivateUse1HooksInterface {
+    bool isBuilt() const override { return true; }
+    bool isAvailable() const override { return deviceCount() > 0; }
+    bool hasPrimaryContext(c10::DeviceIndex) const override { return true; }
+    c10::DeviceIndex deviceCount() const override {
+        int n = 0;
+        if (b200_get_device_count(&n) != B200_SUCCESS) return 0;
+        return static_cast<c10::DeviceIndex>(n);
+    }
+    void setCurrentDevice(c10::DeviceIndex device) const override { VENDOR_CHECK(b200_set_device(device)); }
+    c10::DeviceIndex getCurrentDevice() const override {
+        int dev = 0;
+        VENDOR_CHECK(b200_current_device(&dev));
+        return static_cast<c10::DeviceIndex>(dev);
+    }
+    c10::DeviceIndex exchangeDevice(c10::DeviceIndex device) const override {
+        const c10::DeviceIndex old = getCurrentDevice();
+        if (old != device) setCurrentDevice(device);
+        return old;
+    }
+    c10::DeviceIndex maybeExchangeDevice(c10::DeviceIndex device) const override { return exchangeDevice(device); }
+    bool isPinnedPtr(const void* data) const override { return b200_is_pinned_ptr(const_cast<void*>(data)) != 0; }
+};
+
 struct Registrar {
     Registrar() {
         c10::register_privateuse1_backend("dipu");
         c10::SetAllocator(kDevice, &g_allocator);
+        at::RegisterPrivateUse1HooksInterface(new Hooks());  // owned by torch for the life of the process
     }
 };
 Registrar g_registrar;

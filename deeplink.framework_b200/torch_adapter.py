@@ -71,6 +71,30 @@ torch._register_device_module("dipu", _DeviceModule)
 torch.utils.generate_methods_for_privateuse1_backend(for_tensor=True, for_module=True, for_storage=False)
 
 
+def _load_c10d():
+    import glob
+    import importlib.util
+    paths = glob.glob(os.path.join(os.path.dirname(_LIB), "dipu_b200_c10d*.so"))
+    if not paths:
+        return None
+    spec = importlib.util.spec_from_file_location("dipu_b200_c10d", paths[0])
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+_c10d = _load_c10d()
+if _c10d is not None:
+    import torch.distributed as _dist
+
+    def _create_dicl(store, rank, size, timeout):
+        """What the reference's torch_dipu/dipu/distributed.py:22-27 registers: the creator of the "dicl" backend."""
+        return _c10d.create_process_group_dicl(store, rank, size, timeout)
+
+    if not hasattr(_dist.Backend, "DICL"):
+        _dist.Backend.register_backend("dicl", _create_dicl, devices=["dipu"])
+
+
 def stats():
     """(DIOPI calls issued, device allocations served, host<->device copies) since the library was loaded."""
     a, b, c = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()

@@ -30,3 +30,23 @@ def test_collectives_and_tp_layer_on_two_gpus():
             outs.append(out)
         for r, (p, out) in enumerate(zip(procs, outs)):
             assert p.returncode == 0 and "rank %d ok" % r in out, "rank %d failed:\n%s" % (r, out[-3000:])
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs at least two GPUs")
+def test_c10d_backend_on_two_gpus():
+    """torch.distributed with backend "dicl" on dipu tensors (the reference's ProcessGroupDICL, here over the adapter)."""
+    world, port = 2, 29741
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "c10d_worker.py"), str(r), str(world), str(port)], env=env,
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    outs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=240)
+        except subprocess.TimeoutExpired:
+            p.kill()  # the exact child started above
+            out, _ = p.communicate()
+            out += "\n[timed out]"
+        outs.append(out)
+    for r, (p, out) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and "rank %d ok" % r in out, "rank %d failed:\n%s" % (r, out[-3000:])
