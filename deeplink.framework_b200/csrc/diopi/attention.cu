@@ -18,6 +18,7 @@
 #include <cuda_fp16.h>
 
 #include <cmath>
+#include <cstdlib>
 
 #include "common.h"
 #include "gemm.h"
@@ -36,8 +37,8 @@ constexpr int kBlockKv = 128;          // keys per block
 constexpr int kRing = 3;               // K / V slots
 constexpr int kTileBytes = 128 * 128 * 2;  // one 128 x 128 two-byte tile = two 128-byte-swizzled halves of 16 KiB
 constexpr int kHalfBytes = kTileBytes / 2;
-constexpr int kAttnThreads = 384;
-constexpr int kAttnSmem = (kTilesPerCta * 2 + kRing) * kTileBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+constexpr int kAttnSmem = (kTilesPerCta * 2 + kRing) * kTileBytes + 1024 /*alignment*/ + 256 /*barriers*/ + 1024 /*row exchange*/ + 256 /*votes*/;
+static_assert(kAttnSmem <= 232448, "shared memory budget");
 constexpr float kRescaleThreshold = 8.f;   // log2 units: P stays below 2^8
 
 struct AttnParams {
@@ -85,8 +86,15 @@ __device__ __forceinline__ int blocks_of_tile(const AttnParams& p, int q_lo) {
     return kv_end <= 0 ? 0 : (kv_end + kBlockKv - 1) / kBlockKv;
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+// Named barrier over `count` threads (two partner warps of a row group); barrier 0 is the CTA-wide one.
+__device__ __forceinline__ void pair_barrier(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+
+// SPLIT = threads per query row (1 or 2). With 2, the two threads of a row own 64 score columns each (warps w and w + 4 of
+// the tile's eight softmax warps share a 32-lane quarter of tensor memory), which halves the length of the serial
+// load -> max -> exponentiate -> pack chain that separates a tile's score product from its P V product. Row maxima and
+// row sums cross the pair through one shared-memory slot per row and a 64-thread named barrier.
+template <typename T, int SPLIT>
+__global__ void __launch_bounds__(128 + 256 * SPLIT, 1)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                     const __grid_constant__ CUtensorMap map_o, const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -103,6 +111,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     uint64_t* pv_done = p_full + 2;            // [2] MMA -> softmax: O holds the block, P may be overwritten
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);      // [tile][128 rows]: pair exchange (SPLIT = 2)
+    volatile uint8_t* xfail = reinterpret_cast<uint8_t*>(bars) + 256 + 1024;            // [tile][128 rows]: a wait of the pair failed
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -126,7 +136,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(&s_full[t], 1);
-            mbar_init(&p_full[t], 4);  // one arrival per softmax warp of the tile
+            mbar_init(&p_full[t], 4 * SPLIT);  // one arrival per softmax warp of the tile
             mbar_init(&pv_done[t], 1);
         }
         *abort_flag = 0;
@@ -141,6 +151,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
+    if (threadIdx.x < 256) xfail[threadIdx.x] = 0;
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -243,9 +254,13 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
         }
     } else if (warp >= 4) {
-        // ---------------- softmax + output (one thread per query row) ----------------
-        const int t = (warp - 4) >> 2;
+        // ---------------- softmax + output (SPLIT threads per query row) ----------------
+        constexpr int COLS = 128 / SPLIT;   // score columns per thread
+        constexpr int NCH = COLS / 32;      // 32-column TMEM chunks per thread
+        const int t = (warp - 4) / (4 * SPLIT);
+        const int half = ((warp - 4) % (4 * SPLIT)) >> 2;   // which column half of the row (always 0 with one thread per row)
         const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are the ones this warp may touch
+        const int coff = half * COLS;
         const int r_in_tile = quarter * 32 + lane;
         const int q_lo = q0 + t * kTileQ;
         const int q_row = q_lo + r_in_tile;
@@ -253,64 +268,90 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const int k_visible = p.causal ? min(p.Skv - 1, q_row + p.causal_off) : p.Skv - 1;  // last key this row may see
         uint8_t* pbuf = smem_p + t * kTileBytes;
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-        const uint32_t s_tmem = lane_base + t * 128;
-        const uint32_t o_tmem = lane_base + 256 + t * 128;
+        const uint32_t s_tmem = lane_base + t * 128 + coff;
+        const uint32_t o_tmem = lane_base + 256 + t * 128 + coff;
+        float* slot = xch + t * 128 + r_in_tile;
+        volatile uint8_t* fail = xfail + t * 128 + r_in_tile;
+        const int bar_id = 1 + t * 4 + quarter;
         const float neg_inf = -INFINITY;
         float m_used = neg_inf;
-        float l_sum = 0.f;
+        float l_sum = 0.f;   // this thread's columns only
         bool ok = true;
+        // Combines a per-row value of the two threads of a row (SPLIT = 2): the upper half deposits, the lower half combines
+        // and publishes, two named barriers order the three steps. A failed wait on either side is voted through `fail`,
+        // so that both warps of the pair leave their loops together and nobody is left behind at a barrier.
+        auto pair_combine = [&](float v, bool is_max, bool my_ok) -> float {
+            if (SPLIT == 1) return v;
+            if (!my_ok) *fail = 1;
+            if (half == 1) *slot = v;
+            pair_barrier(bar_id, 64);
+            float r = v;
+            if (half == 0) {
+                const float o = *slot;
+                r = is_max ? fmaxf(v, o) : v + o;
+                *slot = r;
+            }
+            pair_barrier(bar_id, 64);
+            if (half == 1) r = *slot;
+            return r;
+        };
         for (int j = 0; j < n_t; ++j) {
-            ok = mbar_wait(&s_full[t], static_cast<uint32_t>(j) & 1u, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            bool my_ok = mbar_wait(&s_full[t], static_cast<uint32_t>(j) & 1u, abort_flag);
+            // P of the previous block has been consumed and O is at rest: the tensor core runs this tile's products in
+            // issue order, so once the scores of block j have landed the P V product of block j-1 is complete as well
+            if (my_ok && j > 0) my_ok = mbar_wait(&pv_done[t], static_cast<uint32_t>(j - 1) & 1u, abort_flag);
+            my_ok = __all_sync(0xffffffffu, my_ok);
+            if (SPLIT == 1 && !my_ok) {
+                ok = false;
+                break;
+            }
             tc_fence_after();
-            uint32_t s[4][32];
+            uint32_t s[NCH][32];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_tmem + c * 32, s[c]);
+            for (int c = 0; c < NCH; ++c) tmem_ld_32x32(s_tmem + c * 32, s[c]);
             tmem_ld_wait();
             const int k0 = j * kBlockKv;
             // warp-uniform: does any element of this tile x block need the mask?
             const bool need_mask = (k0 + kBlockKv > p.Skv) || (p.causal && k0 + kBlockKv - 1 > q_lo + p.causal_off);
             // Row maximum of the RAW scores (the scale is positive, so it commutes with the maximum); four independent
-            // running maxima: with two softmax warps per scheduler there is little else to hide a 128-long dependent chain
+            // running maxima: with few softmax warps per scheduler there is little else to hide a long dependent chain
             if (need_mask) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < NCH; ++c) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        if (k0 + c * 32 + i > k_visible) s[c][i] = __float_as_uint(neg_inf);
+                        if (k0 + coff + c * 32 + i > k_visible) s[c][i] = __float_as_uint(neg_inf);
                     }
                 }
             }
             float mxs[4] = {neg_inf, neg_inf, neg_inf, neg_inf};
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < NCH; ++c) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) mxs[i & 3] = fmaxf(mxs[i & 3], __uint_as_float(s[c][i]));
             }
-            const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])) * p.scale_log2;  // -inf stays -inf
+            const float mx_own = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
+            const float mx = pair_combine(mx_own, true, my_ok) * p.scale_log2;  // -inf stays -inf
+            if (SPLIT == 2) {
+                const bool pair_ok = __all_sync(0xffffffffu, *fail == 0);   // the same rows in both warps: the same answer
+                if (!pair_ok) {
+                    ok = false;
+                    break;
+                }
+            }
             // The running maximum only moves when some row of the warp outgrew it by more than the threshold: P stays
-            // below 2^8 and most blocks need no pass over O.
-            float factor = 1.f;
-            bool rescale = false;
+            // below 2^8 and most blocks need no pass over O. Both threads of a row see the same maxima, hence decide alike.
             if (j == 0) {
                 m_used = mx;
             } else {
-                rescale = __any_sync(0xffffffffu, mx > m_used + kRescaleThreshold);
+                const bool rescale = __any_sync(0xffffffffu, mx > m_used + kRescaleThreshold);
                 if (rescale) {
                     const float m_new = fmaxf(m_used, mx);
-                    factor = (m_used == neg_inf) ? 0.f : fast_exp2(m_used - m_new);
+                    const float factor = (m_used == neg_inf) ? 0.f : fast_exp2(m_used - m_new);
                     m_used = m_new;
-                }
-                // P of the previous block has been consumed and O is at rest
-                ok = mbar_wait(&pv_done[t], static_cast<uint32_t>(j - 1) & 1u, abort_flag);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tc_fence_after();
-                if (rescale) {
                     l_sum *= factor;
 #pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < NCH; ++c) {
                         uint32_t o[32];
                         tmem_ld_32x32(o_tmem + c * 32, o);
                         tmem_ld_wait();
@@ -324,7 +365,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const float base = (m_used == neg_inf) ? 0.f : m_used;
             float parts[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < NCH; ++c) {
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
                     float e[8];
@@ -340,9 +381,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     w.z = pack2<T>(e[4], e[5]);
                     w.w = pack2<T>(e[6], e[7]);
                     // 16-byte chunk `chunk` of the row sits at position chunk ^ (row & 7): the 128-byte swizzle of a
-                    // K-major tensor-core operand
-                    const int chunk = (c & 1) * 4 + (i >> 3);
-                    *reinterpret_cast<uint4*>(pbuf + (c >> 1) * kHalfBytes + r_in_tile * 128 + ((chunk ^ (r_in_tile & 7)) * 16)) = w;
+                    // K-major tensor-core operand; columns 0..63 and 64..127 are separate 16 KiB halves
+                    const int col = coff + c * 32 + i;
+                    const int chunk = (col & 63) >> 3;
+                    *reinterpret_cast<uint4*>(pbuf + (col >> 6) * kHalfBytes + r_in_tile * 128 + ((chunk ^ (r_in_tile & 7)) * 16)) = w;
                 }
             }
             l_sum += (parts[0] + parts[1]) + (parts[2] + parts[3]);
@@ -352,17 +394,20 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (lane == 0) mbar_arrive(&p_full[t]);
         }
 
-        // ---- normalise and store this warp's 32 rows ----
+        // ---- normalise and store this warp's 32 rows (its column half with two threads per row) ----
         if (ok && q_lo + quarter * 32 < p.Sq) {
+            bool my_ok = true;
             if (n_t > 0) {
-                ok = mbar_wait(&pv_done[t], static_cast<uint32_t>(n_t - 1) & 1u, abort_flag);
-                ok = __all_sync(0xffffffffu, ok);
+                my_ok = mbar_wait(&pv_done[t], static_cast<uint32_t>(n_t - 1) & 1u, abort_flag);
+                my_ok = __all_sync(0xffffffffu, my_ok);
             }
-            if (ok) {
+            const float l_row = pair_combine(l_sum, false, my_ok);
+            if (SPLIT == 2) my_ok = __all_sync(0xffffffffu, *fail == 0);
+            if (my_ok) {
                 tc_fence_after();
-                const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+                const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < NCH; ++c) {
                     uint32_t o[32];
                     if (n_t > 0) {
                         tmem_ld_32x32(o_tmem + c * 32, o);
@@ -378,22 +423,24 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                         w.y = pack2<T>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
                         w.z = pack2<T>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
                         w.w = pack2<T>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-                        const int chunk = (c & 1) * 4 + (i >> 3);
-                        *reinterpret_cast<uint4*>(pbuf + (c >> 1) * kHalfBytes + r_in_tile * 128 + ((chunk ^ (r_in_tile & 7)) * 16)) = w;
+                        const int col = coff + c * 32 + i;
+                        const int chunk = (col & 63) >> 3;
+                        *reinterpret_cast<uint4*>(pbuf + (col >> 6) * kHalfBytes + r_in_tile * 128 + ((chunk ^ (r_in_tile & 7)) * 16)) = w;
                     }
                 }
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) {
-                    for (int g = 0; g < 2; ++g) {
+                    const int g_begin = SPLIT == 2 ? half : 0, g_end = SPLIT == 2 ? half + 1 : 2;
+                    for (int g = g_begin; g < g_end; ++g) {
                         // rows beyond Sq are clipped by the copy engine
                         const int row = q_lo + quarter * 32;
                         tma_store_4d(&map_o, pbuf + g * kHalfBytes + quarter * (32 * 128), g * 64, p.o_hfirst ? h : row, p.o_hfirst ? row : h, b);
                     }
                     tma_store_commit();
                 }
-                if (p.lse != nullptr && q_row < p.Sq) {
-                    const float lse = l_sum > 0.f ? m_used * 0.6931471805599453f + logf(l_sum) : neg_inf;
+                if (p.lse != nullptr && q_row < p.Sq && half == 0) {
+                    const float lse = l_row > 0.f ? m_used * 0.6931471805599453f + logf(l_row) : neg_inf;
                     p.lse[static_cast<int64_t>(b) * p.lse_sb + static_cast<int64_t>(h) * p.lse_sh + static_cast<int64_t>(q_row) * p.lse_sq] = lse;
                 }
                 if (lane == 0) tma_store_wait_all<0>();
@@ -417,19 +464,32 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 }
 
 
-template <typename T>
-cudaError_t launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, const AttnParams& p, int grid,
-                           cudaStream_t stream) {
+template <typename T, int SPLIT>
+cudaError_t launch_prefill_split(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, const AttnParams& p,
+                                 int grid, cudaStream_t stream) {
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<T, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    attn_prefill_kernel<T><<<grid, kAttnThreads, kAttnSmem, stream>>>(mq, mk, mv, mo, p);
+    attn_prefill_kernel<T, SPLIT><<<grid, 128 + 256 * SPLIT, kAttnSmem, stream>>>(mq, mk, mv, mo, p);
     return cudaPeekAtLastError();
+}
+
+template <typename T>
+cudaError_t launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, const AttnParams& p, int grid,
+                           cudaStream_t stream) {
+    // One thread per row is the default. Two threads per row (B200_ATTN_ROW_SPLIT=2) halve the per-thread work, but measured
+    // slower (7B causal prefill 0.62 against 0.38 ms): twenty warps at 96 registers spill, and the two named barriers per block
+    // cost more than the shorter chain saves.
+    static const bool two_threads = [] {
+        const char* e = std::getenv("B200_ATTN_ROW_SPLIT");
+        return e != nullptr && e[0] == '2';
+    }();
+    return two_threads ? launch_prefill_split<T, 2>(mq, mk, mv, mo, p, grid, stream) : launch_prefill_split<T, 1>(mq, mk, mv, mo, p, grid, stream);
 }
 
 // [B, S, H, D] view -> 4-D tensor map with a 64-column x box_rows-row box. The driver wants every pitch to be a

@@ -257,6 +257,101 @@ __global__ void __launch_bounds__(kSortThreads) sort_kernel(const SortArgs a) {
     }
 }
 
+// ---- top-k by radix selection -----------------------------------------------------------------------------------------------
+// For k up to 2048 a full sort is wasted work: four passes over the slice with a 256-bin histogram each pin down the
+// k-th key (most significant byte first), one more pass collects the k winners (everything beyond the threshold key plus, in
+// position order, as many elements equal to it as are still needed), and only those are sorted. One CTA per slice; the
+// slice is read five times (from L2 after the first pass) instead of going through ~120 network stages.
+constexpr int kSelectMaxK = 2048;
+
+__global__ void __launch_bounds__(kSortThreads) topk_select_kernel(const SortArgs a) {
+    __shared__ unsigned int hist[256];
+    __shared__ unsigned int sel_prefix, sel_remaining, n_taken, warp_cnt[32], tie_base;
+    __shared__ unsigned long long cand[kSelectMaxK];
+    const int64_t slice = blockIdx.x;
+    const int64_t o = slice / a.s.inner, k = slice - o * a.s.inner;
+    const int64_t base = o * a.s.n * a.s.inner + k;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        sel_prefix = 0;
+        sel_remaining = static_cast<unsigned int>(a.n_out);
+        n_taken = 0;
+        tie_base = 0;
+    }
+    // with the flip applied the wanted elements are the n_out SMALLEST keys
+    uint32_t mask = 0;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        if (threadIdx.x < 256) hist[threadIdx.x] = 0;
+        __syncthreads();
+        const uint32_t prefix = sel_prefix;
+        for (int64_t j = threadIdx.x; j < a.s.n; j += kSortThreads) {
+            const uint32_t key = load_key(a.in, a.dt, base + j * a.s.inner) ^ a.flip;
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned int rem = sel_remaining, cum = 0;
+            int bkt = 0;
+            for (; bkt < 256; ++bkt) {
+                if (cum + hist[bkt] >= rem) break;
+                cum += hist[bkt];
+            }
+            sel_prefix = prefix | (static_cast<uint32_t>(bkt) << shift);
+            sel_remaining = rem - cum;   // still needed among the elements of the chosen bucket
+        }
+        mask |= 255u << shift;
+        __syncthreads();
+    }
+    const uint32_t threshold = sel_prefix;     // the n_out-th smallest key
+    const unsigned int need_ties = sel_remaining;  // how many elements EQUAL to it belong to the result (>= 1)
+    // collect: keys below the threshold in any order, ties in position order
+    for (int64_t start = 0; start < a.s.n; start += kSortThreads) {
+        const int64_t j = start + threadIdx.x;
+        uint32_t key = 0xffffffffu;
+        bool below = false, tie = false;
+        if (j < a.s.n) {
+            key = load_key(a.in, a.dt, base + j * a.s.inner) ^ a.flip;
+            below = key < threshold;
+            tie = key == threshold;
+        }
+        if (below) {
+            const unsigned int pos = atomicAdd(&n_taken, 1u);
+            cand[pos] = (static_cast<unsigned long long>(key) << 32) | static_cast<uint32_t>(j);
+        }
+        const unsigned int ballot = __ballot_sync(0xffffffffu, tie);
+        if (lane == 0) warp_cnt[warp] = __popc(ballot);
+        __syncthreads();
+        unsigned int before = tie_base;
+        for (int w = 0; w < warp; ++w) before += warp_cnt[w];
+        const unsigned int rank = before + __popc(ballot & ((1u << lane) - 1u));
+        if (tie && rank < need_ties) {
+            const unsigned int pos = atomicAdd(&n_taken, 1u);
+            cand[pos] = (static_cast<unsigned long long>(key) << 32) | static_cast<uint32_t>(j);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned int tot = 0;
+            for (int w = 0; w < kSortThreads / 32; ++w) tot += warp_cnt[w];
+            tie_base += tot;
+        }
+        __syncthreads();
+    }
+    // exactly n_out candidates; pad to a power of two and sort them
+    int64_t n_pad = 2;
+    while (n_pad < a.n_out) n_pad <<= 1;
+    for (int64_t j = a.n_out + threadIdx.x; j < n_pad; j += kSortThreads) cand[j] = ~0ull;
+    __syncthreads();
+    for (int64_t size = 2; size <= n_pad; size <<= 1) {
+        for (int64_t stride = size >> 1; stride > 0; stride >>= 1) bitonic_stage(cand, n_pad, 0, size, stride);
+    }
+    const int64_t obase = o * a.n_out * a.s.inner + k;
+    for (int64_t r = threadIdx.x; r < a.n_out; r += kSortThreads) {
+        const int64_t j = static_cast<int64_t>(cand[r] & 0xffffffffull);
+        if (a.values != nullptr) copy_element(a.values, obase + r * a.s.inner, a.in, base + j * a.s.inner, a.itemsize);
+        if (a.indices != nullptr) a.indices[obase + r * a.s.inner] = j;
+    }
+}
+
 diopiError_t launch_sort(diopiContextHandle_t ctx, const char* name, const TensorView& x, int64_t dim, bool descending, int64_t n_out,
                          const TensorView* values, const TensorView* indices, cudaStream_t stream) {
     B200_CHECK(key32_dtype(x.dtype), "%s: dtype %s is not supported (floats up to 32 bits, integers up to 32 bits, bool)", name, dtype_name(x.dtype));
@@ -278,6 +373,12 @@ diopiError_t launch_sort(diopiContextHandle_t ctx, const char* name, const Tenso
     a.n_pad = n_pad;
     a.n_out = n_out;
     a.flip = descending ? 0xffffffffu : 0u;
+    if (n_out < s.n && n_out <= kSelectMaxK && s.n > 4096) {
+        // a small part of a long slice is wanted (top-k, draws without replacement): select, then sort only the winners
+        topk_select_kernel<<<static_cast<unsigned>(s.outer * s.inner), kSortThreads, 0, stream>>>(a);
+        B200_LAUNCH_CHECK(name);
+        return diopiSuccess;
+    }
     const int64_t chunk = n_pad < kSortSmemElems ? n_pad : kSortSmemElems;
     const size_t smem = static_cast<size_t>(chunk) * sizeof(unsigned long long);
     {

@@ -141,3 +141,32 @@ def test_attention_against_reference_golden(pkg, ctx):
         assert (got - ref).abs().max().item() <= 2e-2 and ((got - ref).norm() / ref.norm()).item() <= 5e-3
     torch.cuda.synchronize()
     assert pkg.diopi.gemm_status() == 0
+
+
+def test_prefill_attention_two_threads_per_row_variant(pkg):
+    """The non-default kernel variant (two threads per query row, selected by B200_ATTN_ROW_SPLIT=2 when the library first
+    launches the kernel) in a child process: same parity bar."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import sys, math, numpy as np, torch\n"
+        "sys.path.insert(0, %r)\n"
+        "import __graft_entry__ as e\n"
+        "from oracle import llama_cpu\n"
+        "pkg = e.load_package(); ctx = pkg.diopi.Context()\n"
+        "rng = np.random.default_rng(1)\n"
+        "for (b, sq, skv, h, hk, causal) in [(2, 640, 640, 4, 2, True), (1, 200, 457, 2, 2, False), (1, 300, 300, 2, 1, True)]:\n"
+        "    q, k, v = (torch.from_numpy(rng.standard_normal(s, dtype=np.float32)).to(torch.bfloat16) for s in ((b, sq, h, 128), (b, skv, hk, 128), (b, skv, hk, 128)))\n"
+        "    ref, lse_ref = llama_cpu.fused_attention(q, k, v, causal)\n"
+        "    out = torch.empty(q.shape, dtype=q.dtype, device='cuda:0'); lse = torch.empty(b, h, sq, device='cuda:0')\n"
+        "    pkg.diopi.diopiMultiHeadAttention(ctx, q.cuda(), k.cuda(), v.cuda(), 0.0, causal, False, 128 ** -0.5, out, lse, None, None)\n"
+        "    torch.cuda.synchronize()\n"
+        "    got = out.float().cpu()\n"
+        "    assert (got - ref).abs().max().item() <= 2e-2 and ((got - ref).norm() / ref.norm()).item() <= 5e-3\n"
+        "    torch.testing.assert_close(lse.cpu(), lse_ref, rtol=1e-4, atol=2e-3)\n"
+        "assert pkg.diopi.gemm_status() == 0\n"
+        "print('variant ok')\n" % root)
+    r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, B200_ATTN_ROW_SPLIT="2"), capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "variant ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]

@@ -60,6 +60,27 @@ def test_topk(diopi, ctx, shape, k, dim, largest):
     ctx.release_workspace()
 
 
+@pytest.mark.parametrize("largest", [True, False])
+@pytest.mark.parametrize("dtype,k", [(torch.float32, 2048), (torch.bfloat16, 37), (torch.int32, 500)])
+def test_topk_by_selection_with_heavy_ties(diopi, ctx, dtype, k, largest):
+    """Long rows with few distinct values: the threshold key has many equals, of which the lowest positions must be taken -
+    the result equals the first k entries of a stable sort."""
+    g = torch.Generator().manual_seed(k)
+    x = torch.randint(-10, 10, (5, 20000), generator=g).to(dtype)
+    vals = torch.empty((5, k), dtype=dtype, device=DEV)
+    idx = torch.empty((5, k), dtype=torch.int64, device=DEV)
+    diopi.diopiTopk(ctx, vals, idx, x.to(DEV), k, 1, largest, True)
+    rv, ri = torch.sort(x.float(), dim=1, descending=largest, stable=True)
+    assert torch.equal(vals.cpu().float(), rv[:, :k]) and torch.equal(idx.cpu(), ri[:, :k])
+    # a middle dimension
+    y = torch.randn(3, 9000, 4, generator=g)
+    v2 = torch.empty((3, 5, 4), device=DEV)
+    i2 = torch.empty((3, 5, 4), dtype=torch.int64, device=DEV)
+    diopi.diopiTopk(ctx, v2, i2, y.to(DEV), 5, 1, largest, True)
+    tv, ti = torch.topk(y, 5, dim=1, largest=largest)
+    assert torch.equal(v2.cpu(), tv) and torch.equal(i2.cpu(), ti)
+
+
 @pytest.mark.parametrize("shape,dim,keepdim", [((16, 32000), 1, False), ((4, 5, 6), 0, True), ((4, 5, 6), -1, False), ((1000,), None, False),
                                                ((3, 7), None, False)])
 def test_argmax(diopi, ctx, shape, dim, keepdim):
