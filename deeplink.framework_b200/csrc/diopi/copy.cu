@@ -22,21 +22,30 @@ struct OpCopy {
 // ---- 2. dense cast --------------------------------------------------------------------------------------
 template <typename S, typename D>
 __global__ void __launch_bounds__(256) cast_vec_kernel(const S* __restrict__ src, D* __restrict__ dst, int64_t numel) {
-    // One "group" = as many elements as the narrower type packs into 16 bytes.
-    constexpr int G = (sizeof(S) < sizeof(D)) ? (16 / sizeof(S)) : (16 / sizeof(D));
-    constexpr int UNROLL = 4;
+    // One "group" = the elements of ONE 16-byte store, so that a warp's store instruction covers 512 contiguous bytes
+    // (full sectors); the matching load is 8, 16 or 32 bytes per thread, contiguous across the warp as well. Widening
+    // casts move fewer bytes per group and keep more groups in flight.
+    constexpr int G = 16 / sizeof(D);
+    constexpr int IN_BYTES = G * sizeof(S);
+    constexpr int UNROLL = IN_BYTES < 16 ? 8 : 4;
     const int64_t ngroup = numel / G;
     const int64_t tile = static_cast<int64_t>(blockDim.x) * UNROLL;
     for (int64_t base = static_cast<int64_t>(blockIdx.x) * tile; base < ngroup; base += static_cast<int64_t>(gridDim.x) * tile) {
-        S in[UNROLL][G];
+        alignas(16) S in[UNROLL][G];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int64_t g = base + u * blockDim.x + threadIdx.x;
             if (g < ngroup) {
-                const uint4* p = reinterpret_cast<const uint4*>(src + g * G);
-                uint4* q = reinterpret_cast<uint4*>(&in[u][0]);
+                if constexpr (IN_BYTES == 8) {
+                    *reinterpret_cast<uint2*>(&in[u][0]) = __ldcs(reinterpret_cast<const uint2*>(src + g * G));
+                } else if constexpr (IN_BYTES == 4) {
+                    *reinterpret_cast<uint32_t*>(&in[u][0]) = __ldcs(reinterpret_cast<const uint32_t*>(src + g * G));
+                } else {
+                    const uint4* p = reinterpret_cast<const uint4*>(src + g * G);
+                    uint4* q = reinterpret_cast<uint4*>(&in[u][0]);
 #pragma unroll
-                for (int w = 0; w < static_cast<int>(G * sizeof(S) / 16); ++w) q[w] = __ldcs(p + w);
+                    for (int w = 0; w < IN_BYTES / 16; ++w) q[w] = __ldcs(p + w);
+                }
             }
         }
 #pragma unroll
@@ -46,10 +55,7 @@ __global__ void __launch_bounds__(256) cast_vec_kernel(const S* __restrict__ src
                 alignas(16) D o[G];
 #pragma unroll
                 for (int e = 0; e < G; ++e) o[e] = from_f32<D>(to_f32(in[u][e]));
-                uint4* q = reinterpret_cast<uint4*>(dst + g * G);
-                const uint4* p = reinterpret_cast<const uint4*>(&o[0]);
-#pragma unroll
-                for (int w = 0; w < static_cast<int>(G * sizeof(D) / 16); ++w) __stcs(q + w, p[w]);
+                __stcs(reinterpret_cast<uint4*>(dst + g * G), *reinterpret_cast<const uint4*>(&o[0]));
             }
         }
     }
@@ -60,9 +66,10 @@ __global__ void __launch_bounds__(256) cast_vec_kernel(const S* __restrict__ src
 
 template <typename S, typename D>
 void launch_cast(const void* src, void* dst, int64_t numel, cudaStream_t stream) {
-    constexpr int G = (sizeof(S) < sizeof(D)) ? (16 / sizeof(S)) : (16 / sizeof(D));
+    constexpr int G = 16 / sizeof(D);
+    constexpr int UNROLL = G * sizeof(S) < 16 ? 8 : 4;
     const int64_t ngroup = numel / G;
-    const int grid = ew_grid((ngroup + 3) / 4 + 1, 256);
+    const int grid = ew_grid((ngroup + UNROLL - 1) / UNROLL + 1, 256);
     cast_vec_kernel<S, D><<<grid, 256, 0, stream>>>(static_cast<const S*>(src), static_cast<D*>(dst), numel);
 }
 
