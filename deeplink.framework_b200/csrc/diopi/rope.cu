@@ -36,13 +36,23 @@ __global__ void __launch_bounds__(256) rope_half_kernel(const T* x, T* out, cons
                                                         int table_cols, float sin_sign) {
     const int half = dim / 2;
     const int chunks = half / 8;
-    const int64_t total = tokens * heads * chunks;
-    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
-        const int c = static_cast<int>(i % chunks);
-        const int64_t th = i / chunks;  // token * heads + head
-        const int64_t t = th / heads;
-        const int64_t row = t % table_rows;
+    // A block covers 256 / chunks (token, head) rows; the thread's chunk and row come from threadIdx with 32-bit arithmetic
+    // and one division per loop trip remains (64-bit index arithmetic per thread costs as much as the rotation itself).
+    const int rows_per_block = 256 / chunks;
+    const int local_row = static_cast<int>(threadIdx.x) / chunks;
+    const int c = static_cast<int>(threadIdx.x) - local_row * chunks;
+    const int64_t total_rows = tokens * heads;
+    const bool narrow = total_rows < 0x7fffffffLL;
+    for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * rows_per_block; row0 < total_rows; row0 += static_cast<int64_t>(gridDim.x) * rows_per_block) {
+        const int64_t th = row0 + local_row;  // token * heads + head
+        if (local_row >= rows_per_block || th >= total_rows) continue;
+        int64_t row;
+        if (narrow && table_rows < 0x7fffffffLL) {
+            const uint32_t t = static_cast<uint32_t>(th) / static_cast<uint32_t>(heads);
+            row = t % static_cast<uint32_t>(table_rows);
+        } else {
+            row = (th / heads) % table_rows;
+        }
         const T* px = x + th * dim + c * 8;
         const Vec16<T> x0 = ld16_stream(px);
         const Vec16<T> x1 = ld16_stream(px + half);
@@ -133,9 +143,9 @@ extern "C" diopiError_t diopiRotaryEmbedding(diopiContextHandle_t ctx, diopiTens
     const float sign = conj ? -1.f : 1.f;
     const bool two_byte = vx.dtype == diopi_dtype_bfloat16 || vx.dtype == diopi_dtype_float16;
     const bool tables_ok = (vc.dtype == vx.dtype || vc.dtype == diopi_dtype_float32) && vc.aligned(16) && vs.aligned(16) && (table_cols % 8 == 0);
-    if (!interleaved && two_byte && (dim / 2) % 8 == 0 && vx.aligned(16) && vo.aligned(16) && tables_ok) {
-        const int64_t total = tokens * heads * (dim / 16);
-        int64_t blocks = (total + 255) / 256;
+    if (!interleaved && two_byte && (dim / 2) % 8 == 0 && dim / 16 <= 256 && vx.aligned(16) && vo.aligned(16) && tables_ok) {
+        const int64_t rows_per_block = 256 / (dim / 16);
+        int64_t blocks = (tokens * heads + rows_per_block - 1) / rows_per_block;
         const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
         if (blocks > cap) blocks = cap;
         const unsigned grid = static_cast<unsigned>(blocks);
