@@ -102,12 +102,16 @@ __global__ void __launch_bounds__(1024) layernorm_kernel(const T* __restrict__ i
     const int64_t r = blockIdx.x;
     Vec16<T> x[VPT];
     load_row<T, VPT>(in + r * cols, nvec, x);
+    // the row is converted to fp32 once and stays in registers for the three passes (sum, squared deviations, output)
+    float f[VPT][V];
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-        if (static_cast<int64_t>(i) * blockDim.x + threadIdx.x < nvec) {
+        const bool live = static_cast<int64_t>(i) * blockDim.x + threadIdx.x < nvec;
 #pragma unroll
-            for (int e = 0; e < V; ++e) s += to_f32(x[i].v[e]);
+        for (int e = 0; e < V; ++e) {
+            f[i][e] = live ? to_f32(x[i].v[e]) : 0.f;
+            s += f[i][e];
         }
     }
     const float mean = block_sum(s, red) / static_cast<float>(cols);
@@ -117,8 +121,8 @@ __global__ void __launch_bounds__(1024) layernorm_kernel(const T* __restrict__ i
         if (static_cast<int64_t>(i) * blockDim.x + threadIdx.x < nvec) {
 #pragma unroll
             for (int e = 0; e < V; ++e) {
-                const float d = to_f32(x[i].v[e]) - mean;
-                q += d * d;
+                f[i][e] -= mean;
+                q += f[i][e] * f[i][e];
             }
         }
     }
@@ -134,25 +138,23 @@ __global__ void __launch_bounds__(1024) layernorm_kernel(const T* __restrict__ i
         const int64_t iv = static_cast<int64_t>(i) * blockDim.x + threadIdx.x;
         if (iv < nvec) {
             Vec16<T> y;
-#pragma unroll
-            for (int e = 0; e < V; ++e) {
-                float f = (to_f32(x[i].v[e]) - mean) * rstd;
-                y.v[e] = from_f32<T>(f);
-            }
             if (weight != nullptr) {
                 const Vec16<T> w = ld16(weight + iv * V);
                 if (bias != nullptr) {
                     const Vec16<T> b = ld16(bias + iv * V);
 #pragma unroll
-                    for (int e = 0; e < V; ++e) y.v[e] = from_f32<T>((to_f32(x[i].v[e]) - mean) * rstd * to_f32(w.v[e]) + to_f32(b.v[e]));
+                    for (int e = 0; e < V; ++e) y.v[e] = from_f32<T>(f[i][e] * rstd * to_f32(w.v[e]) + to_f32(b.v[e]));
                 } else {
 #pragma unroll
-                    for (int e = 0; e < V; ++e) y.v[e] = from_f32<T>((to_f32(x[i].v[e]) - mean) * rstd * to_f32(w.v[e]));
+                    for (int e = 0; e < V; ++e) y.v[e] = from_f32<T>(f[i][e] * rstd * to_f32(w.v[e]));
                 }
             } else if (bias != nullptr) {
                 const Vec16<T> b = ld16(bias + iv * V);
 #pragma unroll
-                for (int e = 0; e < V; ++e) y.v[e] = from_f32<T>((to_f32(x[i].v[e]) - mean) * rstd + to_f32(b.v[e]));
+                for (int e = 0; e < V; ++e) y.v[e] = from_f32<T>(f[i][e] * rstd + to_f32(b.v[e]));
+            } else {
+#pragma unroll
+                for (int e = 0; e < V; ++e) y.v[e] = from_f32<T>(f[i][e] * rstd);
             }
             st16_stream(orow + iv * V, y);
         }
