@@ -10,6 +10,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
 #include <cmath>
 #include <vector>
 
@@ -175,12 +176,12 @@ __global__ void __launch_bounds__(256) gather_kernel(const void* self, int items
 
 
 // ---- sort / top-k -------------------------------------------------------------------------------------------------------------
-// One CTA per slice sorts 64-bit composites (order-preserving key << 32 | position) with a bitonic network: equal keys
-// keep their original order (the position breaks the tie), which is torch's stable order, and "descending" only flips the
-// key bits. The network runs on chunks of up to 16384 elements in shared memory; only the few stages that pair elements
-// of different chunks touch the workspace in L2 (one such stage for a 32 k vocabulary). The first n_out sorted elements are written out (n_out = n for sort, k for top-k).
+// One CTA per slice sorts 64-bit composites (order-preserving key << 32 | position): equal keys keep their original order
+// (the position breaks the tie), which is torch's stable order, and "descending" only flips the key bits. Slices of up to
+// 4096 elements run a bitonic network in shared memory; longer ones the radix sort below; a small k of a long slice the
+// radix selection. The first n_out sorted elements are written out (n_out = n for sort, k for top-k).
 constexpr int kSortThreads = 1024;
-constexpr int64_t kSortSmemElems = 16384;
+constexpr int64_t kSortSmemElems = 4096;   // longer slices take the radix sort
 
 struct SortArgs {
     const void* in;
@@ -188,7 +189,6 @@ struct SortArgs {
     int itemsize;
     void* values;        // may be nullptr
     int64_t* indices;    // may be nullptr
-    unsigned long long* work;  // nullptr: shared memory
     Slices s;
     int64_t n_pad, n_out;
     uint32_t flip;       // 0xffffffff for descending
@@ -212,46 +212,23 @@ __device__ __forceinline__ void bitonic_stage(unsigned long long* buf, int64_t c
 }
 
 __global__ void __launch_bounds__(kSortThreads) sort_kernel(const SortArgs a) {
-    extern __shared__ unsigned long long sort_smem[];
+    __shared__ unsigned long long buf[kSortSmemElems];
     const int64_t slice = blockIdx.x;
     const int64_t o = slice / a.s.inner, k = slice - o * a.s.inner;
     const int64_t base = o * a.s.n * a.s.inner + k;
-    const int64_t chunk = a.n_pad < kSortSmemElems ? a.n_pad : kSortSmemElems;   // elements sorted in shared memory at a time
-    unsigned long long* work = a.work != nullptr ? a.work + slice * a.n_pad : nullptr;
-    // phase 1: every chunk becomes a sorted run (alternating directions, as the network wants them), in shared memory
-    for (int64_t c0 = 0; c0 < a.n_pad; c0 += chunk) {
-        for (int64_t j = threadIdx.x; j < chunk; j += kSortThreads) {
-            const int64_t g = c0 + j;
-            unsigned long long c = ~0ull;  // padding sorts to the end
-            if (g < a.s.n) c = (static_cast<unsigned long long>(load_key(a.in, a.dt, base + g * a.s.inner) ^ a.flip) << 32) | static_cast<uint32_t>(g);
-            sort_smem[j] = c;
-        }
-        __syncthreads();
-        for (int64_t size = 2; size <= chunk; size <<= 1) {
-            for (int64_t stride = size >> 1; stride > 0; stride >>= 1) bitonic_stage(sort_smem, chunk, c0, size, stride);
-        }
-        if (work != nullptr) {
-            for (int64_t j = threadIdx.x; j < chunk; j += kSortThreads) work[c0 + j] = sort_smem[j];
-            __syncthreads();
-        }
+    for (int64_t j = threadIdx.x; j < a.n_pad; j += kSortThreads) {
+        unsigned long long c = ~0ull;  // padding sorts to the end
+        if (j < a.s.n) c = (static_cast<unsigned long long>(load_key(a.in, a.dt, base + j * a.s.inner) ^ a.flip) << 32) | static_cast<uint32_t>(j);
+        buf[j] = c;
     }
-    // phase 2 (slices longer than a chunk): the merges across chunks run on the workspace (it stays in L2), everything
-    // below a chunk's length again in shared memory
-    for (int64_t size = chunk << 1; size <= a.n_pad; size <<= 1) {
-        for (int64_t stride = size >> 1; stride >= chunk; stride >>= 1) bitonic_stage(work, a.n_pad, 0, size, stride);
-        for (int64_t c0 = 0; c0 < a.n_pad; c0 += chunk) {
-            for (int64_t j = threadIdx.x; j < chunk; j += kSortThreads) sort_smem[j] = work[c0 + j];
-            __syncthreads();
-            for (int64_t stride = chunk >> 1; stride > 0; stride >>= 1) bitonic_stage(sort_smem, chunk, c0, size, stride);
-            for (int64_t j = threadIdx.x; j < chunk; j += kSortThreads) work[c0 + j] = sort_smem[j];
-            __syncthreads();
-        }
+    __syncthreads();
+    for (int64_t size = 2; size <= a.n_pad; size <<= 1) {
+        for (int64_t stride = size >> 1; stride > 0; stride >>= 1) bitonic_stage(buf, a.n_pad, 0, size, stride);
     }
-    const unsigned long long* sorted = work != nullptr ? work : sort_smem;
     // output slice geometry: the operated dimension has n_out elements
     const int64_t obase = o * a.n_out * a.s.inner + k;
     for (int64_t r = threadIdx.x; r < a.n_out; r += kSortThreads) {
-        const int64_t j = static_cast<int64_t>(sorted[r] & 0xffffffffull);
+        const int64_t j = static_cast<int64_t>(buf[r] & 0xffffffffull);
         if (a.values != nullptr) copy_element(a.values, obase + r * a.s.inner, a.in, base + j * a.s.inner, a.itemsize);
         if (a.indices != nullptr) a.indices[obase + r * a.s.inner] = j;
     }
@@ -458,7 +435,6 @@ diopiError_t launch_sort(diopiContextHandle_t ctx, const char* name, const Tenso
     a.itemsize = static_cast<int>(x.itemsize);
     a.values = values != nullptr ? values->data : nullptr;
     a.indices = indices != nullptr ? static_cast<int64_t*>(indices->data) : nullptr;
-    a.work = nullptr;
     a.s = s;
     a.n_pad = n_pad;
     a.n_out = n_out;
@@ -481,26 +457,7 @@ diopiError_t launch_sort(diopiContextHandle_t ctx, const char* name, const Tenso
         B200_LAUNCH_CHECK(name);
         return diopiSuccess;
     }
-    const int64_t chunk = n_pad < kSortSmemElems ? n_pad : kSortSmemElems;
-    const size_t smem = static_cast<size_t>(chunk) * sizeof(unsigned long long);
-    {
-        static bool attr_set[64] = {false};
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-            B200_CUDA(cudaFuncSetAttribute(sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSortSmemElems * sizeof(unsigned long long))));
-            attr_set[dev] = true;
-        }
-    }
-    if (n_pad > chunk) {
-        diopiTensorHandle_t ws = nullptr;
-        const int64_t bytes = s.outer * s.inner * n_pad * static_cast<int64_t>(sizeof(unsigned long long));
-        B200_CHECK(diopiRequireBuffer(ctx, &ws, bytes, diopi_device) == diopiSuccess && ws != nullptr, "%s: workspace allocation failed", name);
-        void* ptr = nullptr;
-        B200_CHECK(diopiGetTensorData(ws, &ptr) == diopiSuccess && ptr != nullptr, "%s: workspace has no data pointer", name);
-        a.work = static_cast<unsigned long long*>(ptr);
-    }
-    sort_kernel<<<static_cast<unsigned>(s.outer * s.inner), kSortThreads, smem, stream>>>(a);
+    sort_kernel<<<static_cast<unsigned>(s.outer * s.inner), kSortThreads, 0, stream>>>(a);
     B200_LAUNCH_CHECK(name);
     return diopiSuccess;
 }
@@ -874,19 +831,19 @@ diopiError_t diopiMultinomial(diopiContextHandle_t ctx, diopiTensorHandle_t out,
     if (make_contiguous(ctx, vx_raw, &vx) != diopiSuccess) return diopiErrorOccurred;
     // Generator state: the host's generator when given (its offset advances by the draws consumed, in multiples of 4),
     // else a library-wide default stream.
-    static uint64_t default_offset = 0;
+    static std::atomic<uint64_t> default_offset{0};
     uint64_t seed = 67280421310721ull, offset = 0;
     if (generator != nullptr) {
         B200_CHECK(diopiGeneratorGetSeedAndOffset(generator, &seed, &offset) == diopiSuccess, "diopiMultinomial: cannot read the generator");
     } else {
-        offset = default_offset;
+        offset = default_offset.load();
     }
     const uint64_t draws = static_cast<uint64_t>(replacement || num_samples == 1 ? rows * num_samples : rows * n);
     const uint64_t advance = (draws + 3) / 4 * 4;
     if (generator != nullptr) {
         B200_CHECK(diopiGeneratorSetSeedAndOffset(generator, seed, offset + advance) == diopiSuccess, "diopiMultinomial: cannot advance the generator");
     } else {
-        default_offset += advance;
+        default_offset.fetch_add(advance);
     }
     cudaStream_t stream = stream_of(ctx);
     if (replacement || num_samples == 1) {
