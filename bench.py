@@ -192,6 +192,8 @@ def main():
     ap.add_argument("--workload", default="7b", choices=["7b", "70b"],
                     help="7b: one Llama-2-7B-shaped layer, batch 8 x seq 2048 (default). 70b: a stack of four Llama-2-70B-shaped "
                          "layers (GQA 64/8), batch 4 x seq 4096, meant for --gpus 2/4/8")
+    ap.add_argument("--fused-collective-parts", default="both", choices=["1", "2", "both"],
+                    help="N > 1: time the fused-collective variants with the batch in one piece, in two interleaved halves, or both")
     ap.add_argument("--overlap", default="auto", choices=["auto", "on", "off"],
                     help="tensor-parallel prefill: interleave two half-batches so the all-reduces overlap compute")
     args = ap.parse_args()
@@ -460,6 +462,44 @@ def main():
     variants["fused_attention"] = {"value": tokens * args.steps / (ms_fused * 1e-3), "unit": "tokens/s", "ms_per_step": ms_fused / args.steps,
                                    "note": "diopiMultiHeadAttention (causal) replaces the transposes, diopiBmm, diopiDivInpScalar, diopiAddInp, "
                                            "diopiSoftmax, diopiBmm of the attention core"}
+
+    # ---- variants (N > 1): row-parallel linears with the all-reduce and the residual add fused into the kernels ----
+    # diopiB200MmPush pushes each output tile to the rank that owns its rows while the product is still running; one
+    # reduce-gather kernel per linear sums the pieces, adds the residual and writes the finished rows to every rank. No
+    # library collective and no separate diopiAdd on this path.
+    def time_steps():
+        for _ in range(3):
+            step_resident()
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            step_resident()
+        e1.record(stream)
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1))
+
+    if world > 1 and tokens % (256 * world) == 0 and cfg.hidden % 256 == 0:
+        choices = [1, 2] if args.fused_collective_parts == "both" else [int(args.fused_collective_parts)]
+        for parts in choices:
+            if batch % parts != 0 or (tokens // parts) % (256 * world) != 0:
+                continue
+            tp_group.enable_fused_linear(tokens // parts, cfg.hidden, parts, on_comm_stream=(parts > 1))
+            for l_ in layers:
+                l_.fused_collective = True
+            for fused_attn in (False, True):
+                for l_ in layers:
+                    l_.fused_attention = fused_attn
+                ms_v = time_steps()
+                ok = tp_group.space.status() == 0 and diopi.gemm_status() == 0
+                name = ("fused_attention_" if fused_attn else "") + "fused_collective" + ("_interleaved_halves" if parts > 1 else "")
+                variants[name] = {"value": tokens * args.steps / (ms_v * 1e-3), "unit": "tokens/s", "ms_per_step": ms_v / args.steps, "status_ok": ok,
+                                  "note": "diopiB200MmPush + peer reduce-gather replace diopiMm + diclAllReduce + diopiAdd after the attention "
+                                          "and FFN blocks" + ("; two half-batches interleaved, reductions on the communication stream" if parts > 1 else "")}
+            for l_ in layers:
+                l_.fused_collective = False
+                l_.fused_attention = False
+            barrier()
+            tp_group.disable_fused_linear()
 
     # ---- secondary measurement: the same layer in decode (batch 64, KV length 4096) ----
     decode = None

@@ -10,6 +10,7 @@
 
 #include "copy.h"
 #include "device_utils.cuh"
+#include "diopi/functions_b200.h"
 
 namespace b200 {
 namespace {
@@ -376,6 +377,27 @@ diopiError_t diopiMm(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiCon
     B200_VIEW(va, input);
     B200_VIEW(vb, mat2);
     return mm_like(ctx, "diopiMm", vo, va, vb, nullptr, 1.0, 0.0, false);
+}
+
+// mat1 [M, K] x mat2 [K, N]: this rank's partial sum of a row-parallel linear, pushed into the peers' staging slots.
+diopiError_t diopiB200MmPush(diopiContextHandle_t ctx, diopiConstTensorHandle_t input, diopiConstTensorHandle_t mat2, const b200PeerSpace* space,
+                             int32_t slot, uint32_t epoch, uint32_t prev_epoch) {
+    B200_CHECK(space != nullptr, "diopiB200MmPush: NULL peer space");
+    B200_VIEW(va, input);
+    B200_VIEW(vb, mat2);
+    B200_CHECK(va.ndim == 2 && vb.ndim == 2 && va.shape[1] == vb.shape[0], "diopiB200MmPush: expected [M, K] x [K, N]");
+    B200_CHECK(va.device == diopi_device && vb.device == diopi_device, "diopiB200MmPush: operands must be device tensors");
+    B200_CHECK(va.dtype == vb.dtype && (va.dtype == diopi_dtype_bfloat16 || va.dtype == diopi_dtype_float16),
+               "diopiB200MmPush: operands must both be bfloat16 or float16");
+    GemmProblem g;
+    g.M = va.shape[0]; g.K = va.shape[1]; g.N = vb.shape[1];
+    g.A = va.data; g.a_sm = va.stride[0]; g.a_sk = va.stride[1];
+    g.B = vb.data; g.b_sk = vb.stride[0]; g.b_sn = vb.stride[1];
+    g.C = nullptr; g.c_sm = g.N; g.c_sn = 1;
+    g.ab_dtype = va.dtype; g.c_dtype = va.dtype;
+    B200_CHECK(gemm_tc_eligible(g), "diopiB200MmPush: operands do not meet the tensor-core kernel's layout rules (16-byte aligned pointers, pitches "
+               "that are multiples of 8 elements, K or N contiguous)");
+    return gemm_tc2_push_launch(g, *space, slot, epoch, prev_epoch, stream_of(ctx));
 }
 
 diopiError_t diopiAddmm(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input, diopiConstTensorHandle_t mat1,

@@ -4,6 +4,7 @@
 #include "common.h"
 
 struct CUtensorMap_st;  // the driver API's tensor-map descriptor (cuda.h)
+struct b200PeerSpace;   // dipu_b200/peer_space.h
 
 namespace b200 {
 
@@ -33,6 +34,11 @@ diopiError_t gemm_tc_launch(const GemmProblem& g, cudaStream_t stream);
 // CTA-pair variant (cta_group::2, 256 x 256 tiles) for large products; gemm_tc_launch hands over to it when it applies.
 bool gemm_tc2_applies(const GemmProblem& g);
 diopiError_t gemm_tc2_launch(const GemmProblem& g, cudaStream_t stream);
+
+// The CTA-pair kernel with a pushing epilogue: g.C is ignored, every 32 x 256 piece of the product goes to the staging slot
+// of the rank that owns its rows (dipu_b200/peer_space.h) and raises that piece's ready flag with `epoch`.
+diopiError_t gemm_tc2_push_launch(const GemmProblem& g, const ::b200PeerSpace& space, int slot, uint32_t epoch, uint32_t prev_epoch,
+                                  cudaStream_t stream);
 
 // Shared by the tensor-core translation units.
 bool tc_encode_map(::CUtensorMap_st* map, diopiDtype_t dtype, const void* base, int64_t inner, int64_t rows, int64_t batch, int64_t row_pitch_elems,

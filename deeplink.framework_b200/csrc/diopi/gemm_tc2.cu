@@ -13,11 +13,19 @@
 //   empty[s]  (each CTA)  the leader commits the MMAs that read stage s to its own and to the partner's barrier
 //   acc_full  (each CTA)  the leader commits the tile's last MMA to both CTAs' barriers
 //   acc_empty (leader's)  the 8 epilogue warps of the pair arrive (the partner's remotely) when an accumulator is drained
+//
+// PUSH variant (row-parallel linear of a tensor-parallel group, C = this rank's partial sum): instead of storing the tile
+// into a local C, each epilogue warp writes its 32 x 256 piece into the staging block of the rank that owns those rows -
+// plain 16-byte stores to peer memory mapped over NVLink, 128 contiguous bytes per row segment - and then raises the
+// piece's ready flag there (fence.sys + st.release.sys). The transfer of one tile overlaps the MMAs of the next ones; the
+// kernel never waits for a peer except for the (normally long satisfied) permission to overwrite a staging slot. Each
+// rank starts its tile order at the rows of the next rank, so that at any moment the ranks push to different owners.
 #include <cuda.h>
 
 #include <cstdlib>
 
 #include "device_utils.cuh"
+#include "dipu_b200/peer_space.h"
 #include "gemm.h"
 #include "gemm_sm100.cuh"
 
@@ -45,6 +53,7 @@ struct PairParams {
     int M, N, K, batch;
     int m_pairs, n_blocks, k_blocks;
     int group_m;  // row-pair blocks per tile group (tile order: all tiles of a group before the next group)
+    int m_rot;    // the tile order starts at row-pair block m_rot (and wraps around)
     int64_t ldc, stride_cb;
     void* C;
     const void* bias;
@@ -56,6 +65,38 @@ struct PairParams {
     uint32_t* status;
 };
 
+struct PushParams {
+    b200PeerSpace space;
+    int slot;
+    uint32_t epoch;       // this call's number: written into the ready flags
+    uint32_t prev_epoch;  // number of the last call that used this slot (0: none); its reduction must be over before we write
+    int rows_per_rank;    // M / nranks, a multiple of 128
+};
+
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_peer16(void* p, const uint4& v) {
+    asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Bounded wait until *flag >= target (flags only grow); raises the CTA's abort flag on time-out.
+__device__ __forceinline__ bool flag_wait_ge(const uint32_t* flag, uint32_t target, volatile uint32_t* abort_flag) {
+    if (static_cast<int32_t>(ld_acquire_sys_u32(flag) - target) >= 0) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    while (true) {
+        if (static_cast<int32_t>(ld_acquire_sys_u32(flag) - target) >= 0) return true;
+        if (*abort_flag != 0) return false;
+        if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+
 __device__ __forceinline__ void pair_tile_coords(int tile, const PairParams& p, int* b, int* mp, int* nb) {
     const int per_batch = p.m_pairs * p.n_blocks;
     *b = tile / per_batch;
@@ -65,14 +106,15 @@ __device__ __forceinline__ void pair_tile_coords(int tile, const PairParams& p, 
     const int first = g * p.group_m;
     const int rows = min(p.m_pairs - first, p.group_m);
     const int r = t - g * group_sz;
-    *mp = first + r % rows;
+    *mp = first + r % rows + p.m_rot;
+    if (*mp >= p.m_pairs) *mp -= p.m_pairs;
     *nb = r / rows;
 }
 
-template <typename TOut>
+template <typename TOut, bool PUSH>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
-                    const PairParams p) {
+                    const PairParams p, const __grid_constant__ PushParams q) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* smem_a = smem;
@@ -198,6 +240,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int quarter = warp & 3;
         int local = 0;
         uint32_t store_seq = 0;
+        uint32_t checked = 0;  // PUSH: owners whose staging slot is known to be free for this call
+        uint32_t* pending_flag = nullptr;  // PUSH: ready flag of the piece pushed last, not raised yet
         bool ok = true;
         constexpr int PIECE_COLS = 128 / static_cast<int>(sizeof(TOut));
         constexpr int LOADS = PIECE_COLS / 32;
@@ -209,17 +253,42 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const uint32_t acc_phase = (local >> 1) & 1u;
             if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
+            if constexpr (PUSH) {
+                // st.release.sys orders the whole warp's stores of the previous tile (they were followed by __syncwarp) before
+                // the flag, at system scope
+                if (pending_flag != nullptr && lane == 0) st_release_sys_u32(pending_flag, q.epoch);
+                pending_flag = nullptr;
+            }
             const int row_base = mp * (2 * BM) + static_cast<int>(rank) * BM + quarter * 32;
             const int row = row_base + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+            int owner = 0, local_row0 = 0;
+            uint8_t* push_dst = nullptr;  // PUSH: where this warp's 32 rows start in the owner's staging slot (column 0)
+            if constexpr (PUSH) {
+                owner = row_base / q.rows_per_rank;
+                if (((checked >> owner) & 1u) == 0) {
+                    int fine = 1;
+                    if (lane == 0) {
+                        fine = flag_wait_ge(q.space.flags[q.space.rank] + b200_peer_sfree_off(&q.space, q.slot, owner), q.prev_epoch, abort_flag) ? 1 : 0;
+                    }
+                    fine = __shfl_sync(0xffffffffu, fine, 0);
+                    if (!fine) { ok = false; break; }
+                    checked |= 1u << owner;
+                }
+                local_row0 = row_base - owner * q.rows_per_rank;
+                push_dst = static_cast<uint8_t*>(q.space.stage[owner]) + static_cast<size_t>(q.slot) * q.space.slot_bytes +
+                           (static_cast<size_t>(q.space.rank) * q.rows_per_rank + local_row0) * p.N * sizeof(TOut);
+            }
             if (row_base < p.M) {
 #pragma unroll 1
                 for (int c = 0; c < BN / PIECE_COLS; ++c) {
                     const int col0 = nb * BN + c * PIECE_COLS;
                     if (col0 >= p.N) break;  // warp-uniform
                     uint8_t* buf = stage_base + (store_seq & 1) * (32 * 128);
-                    if (lane == 0) tma_store_wait_read<1>();
-                    __syncwarp();
+                    if constexpr (!PUSH) {
+                        if (lane == 0) tma_store_wait_read<1>();
+                        __syncwarp();
+                    }
                     uint32_t r[LOADS][32];
 #pragma unroll
                     for (int l = 0; l < LOADS; ++l) tmem_ld_32x32(t_row + c * PIECE_COLS + l * 32, r[l]);
@@ -258,18 +327,40 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             *reinterpret_cast<uint4*>(buf + lane * 128 + ((chunk ^ (lane & 7)) * 16)) = *reinterpret_cast<const uint4*>(&o);
                         }
                     }
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_3d(&map_c, buf, col0, row_base, b);
-                        tma_store_commit();
+                    if constexpr (PUSH) {
+                        // read the piece back row-wise: 8 lanes cover the 128 bytes of a row segment, 4 rows per instruction
+                        __syncwarp();
+                        const int sub = lane & 7, rsel = lane >> 3;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int rr = i * 4 + rsel;
+                            const uint4 w = *reinterpret_cast<const uint4*>(buf + rr * 128 + ((sub ^ (rr & 7)) * 16));
+                            st_peer16(push_dst + (static_cast<size_t>(rr) * p.N + col0) * sizeof(TOut) + sub * 16, w);
+                        }
+                        __syncwarp();
+                    } else {
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_3d(&map_c, buf, col0, row_base, b);
+                            tma_store_commit();
+                        }
                     }
                     ++store_seq;
                 }
             }
+            if constexpr (PUSH) {
+                // The piece is on its way. Its flag is raised when the next tile's accumulator is ready (or after the
+                // last tile): by then the stores have long been acknowledged and the release costs next to nothing.
+                const uint32_t unit = static_cast<uint32_t>(local_row0 / B200_PEER_PIECE_ROWS) * p.n_blocks + nb;
+                pending_flag = q.space.flags[owner] + b200_peer_ready_off(&q.space, q.slot, q.space.rank, unit);
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(leader_acc_empty0 + acc * 8);
+        }
+        if constexpr (PUSH) {
+            if (ok && pending_flag != nullptr && lane == 0) st_release_sys_u32(pending_flag, q.epoch);
         }
         if (lane == 0) tma_store_wait_all<0>();
     }
@@ -292,13 +383,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
-template <typename TOut>
-cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const PairParams& p, int grid, cudaStream_t stream) {
+template <typename TOut, bool PUSH>
+cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const PairParams& p, const PushParams& q, int grid,
+                        cudaStream_t stream) {
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<TOut, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
@@ -314,7 +406,51 @@ cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUte
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<TOut>, ma, mb, mc, p);
+    return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<TOut, PUSH>, ma, mb, mc, p, q);
+}
+
+// Tensor maps of A and B and the tile geometry: shared by the storing and the pushing launch.
+diopiError_t pair_setup(const GemmProblem& g, CUtensorMap* ma, CUtensorMap* mb, PairParams* pp) {
+    const bool is_bf16 = g.ab_dtype == diopi_dtype_bfloat16;
+    const bool b_mn = g.b_sk != 1;
+    B200_CHECK(tc_encode_map(ma, g.ab_dtype, g.A, g.K, g.M, g.batch, g.a_sm, g.batch > 1 ? g.a_sb : g.a_sm * g.M, BM),
+               "gemm: cuTensorMapEncodeTiled failed for A");
+    if (!b_mn) {
+        B200_CHECK(tc_encode_map(mb, g.ab_dtype, g.B, g.K, g.N, g.batch, g.b_sn, g.batch > 1 ? g.b_sb : g.b_sn * g.N, BNH),
+                   "gemm: cuTensorMapEncodeTiled failed for B (K-major)");
+    } else {
+        B200_CHECK(tc_encode_map(mb, g.ab_dtype, g.B, g.N, g.K, g.batch, g.b_sk, g.batch > 1 ? g.b_sb : g.b_sk * g.K, BK),
+                   "gemm: cuTensorMapEncodeTiled failed for B (MN-major)");
+    }
+    PairParams& p = *pp;
+    p.M = static_cast<int>(g.M); p.N = static_cast<int>(g.N); p.K = static_cast<int>(g.K); p.batch = static_cast<int>(g.batch);
+    p.m_pairs = static_cast<int>((g.M + 2 * BM - 1) / (2 * BM));
+    p.n_blocks = static_cast<int>((g.N + BN - 1) / BN);
+    p.group_m = kGroupM;
+    if (const char* e = std::getenv("B200_GEMM_GROUP_M")) {
+        const int v = std::atoi(e);
+        if (v >= 1 && v <= 64) p.group_m = v;
+    }
+    p.m_rot = 0;
+    p.k_blocks = static_cast<int>((g.K + BK - 1) / BK);
+    p.ldc = g.c_sm; p.stride_cb = g.c_sb; p.C = g.C;
+    p.bias = g.bias; p.bias_sb = g.bias_sb; p.bias_sr = g.bias_sm; p.bias_sc = g.bias_sn;
+    p.alpha = g.alpha; p.beta = g.beta;
+    p.idesc = make_idesc_f16(is_bf16 ? 1 : 0, b_mn, 2 * BM, BN);
+    p.b_mn_major = b_mn ? 1 : 0;
+    const int64_t c_es = dtype_size(g.c_dtype);
+    p.bias_vec_ok = (g.bias != nullptr && g.bias_sn == 1 && (reinterpret_cast<uintptr_t>(g.bias) & 15u) == 0 && (g.bias_sm * c_es) % 16 == 0 &&
+                     (g.bias_sb * c_es) % 16 == 0) ? 1 : 0;
+    p.status = g.status_override != nullptr ? g.status_override : tc_status_word();
+    B200_CHECK(p.status != nullptr, "gemm: could not allocate the kernel status word");
+    return diopiSuccess;
+}
+
+int pair_grid(const PairParams& p) {
+    const int64_t total = static_cast<int64_t>(p.batch) * p.m_pairs * p.n_blocks;
+    int64_t clusters = sm_count() / 2;
+    if (clusters > total) clusters = total;
+    return static_cast<int>(clusters * 2);
 }
 
 }  // namespace
@@ -332,51 +468,56 @@ bool gemm_tc2_applies(const GemmProblem& g) {
 }
 
 diopiError_t gemm_tc2_launch(const GemmProblem& g, cudaStream_t stream) {
-    const bool is_bf16 = g.ab_dtype == diopi_dtype_bfloat16;
-    const bool b_mn = g.b_sk != 1;
     CUtensorMap ma, mb, mc;
-    B200_CHECK(tc_encode_map(&ma, g.ab_dtype, g.A, g.K, g.M, g.batch, g.a_sm, g.batch > 1 ? g.a_sb : g.a_sm * g.M, BM),
-               "gemm: cuTensorMapEncodeTiled failed for A");
-    if (!b_mn) {
-        B200_CHECK(tc_encode_map(&mb, g.ab_dtype, g.B, g.K, g.N, g.batch, g.b_sn, g.batch > 1 ? g.b_sb : g.b_sn * g.N, BNH),
-                   "gemm: cuTensorMapEncodeTiled failed for B (K-major)");
-    } else {
-        B200_CHECK(tc_encode_map(&mb, g.ab_dtype, g.B, g.N, g.K, g.batch, g.b_sk, g.batch > 1 ? g.b_sb : g.b_sk * g.K, BK),
-                   "gemm: cuTensorMapEncodeTiled failed for B (MN-major)");
-    }
+    PairParams p;
+    if (diopiError_t err = pair_setup(g, &ma, &mb, &p); err != diopiSuccess) return err;
     B200_CHECK(tc_encode_map(&mc, g.c_dtype, g.C, g.N, g.M, g.batch, g.c_sm, g.batch > 1 ? g.c_sb : g.c_sm * g.M, 32),
                "gemm: cuTensorMapEncodeTiled failed for C");
-    PairParams p;
-    p.M = static_cast<int>(g.M); p.N = static_cast<int>(g.N); p.K = static_cast<int>(g.K); p.batch = static_cast<int>(g.batch);
-    p.m_pairs = static_cast<int>((g.M + 2 * BM - 1) / (2 * BM));
-    p.n_blocks = static_cast<int>((g.N + BN - 1) / BN);
-    p.group_m = kGroupM;
-    if (const char* e = std::getenv("B200_GEMM_GROUP_M")) {
-        const int v = std::atoi(e);
-        if (v >= 1 && v <= 64) p.group_m = v;
-    }
-    p.k_blocks = static_cast<int>((g.K + BK - 1) / BK);
-    p.ldc = g.c_sm; p.stride_cb = g.c_sb; p.C = g.C;
-    p.bias = g.bias; p.bias_sb = g.bias_sb; p.bias_sr = g.bias_sm; p.bias_sc = g.bias_sn;
-    p.alpha = g.alpha; p.beta = g.beta;
-    p.idesc = make_idesc_f16(is_bf16 ? 1 : 0, b_mn, 2 * BM, BN);
-    p.b_mn_major = b_mn ? 1 : 0;
-    const int64_t c_es = dtype_size(g.c_dtype);
-    p.bias_vec_ok = (g.bias != nullptr && g.bias_sn == 1 && (reinterpret_cast<uintptr_t>(g.bias) & 15u) == 0 && (g.bias_sm * c_es) % 16 == 0 &&
-                     (g.bias_sb * c_es) % 16 == 0) ? 1 : 0;
-    p.status = g.status_override != nullptr ? g.status_override : tc_status_word();
-    B200_CHECK(p.status != nullptr, "gemm: could not allocate the kernel status word");
-    const int64_t total = static_cast<int64_t>(p.batch) * p.m_pairs * p.n_blocks;
-    int64_t clusters = sm_count() / 2;
-    if (clusters > total) clusters = total;
-    const int grid = static_cast<int>(clusters * 2);
+    PushParams q = {};
+    const int grid = pair_grid(p);
     cudaError_t e;
-    if (g.c_dtype == diopi_dtype_bfloat16) e = launch_pair<bf16>(ma, mb, mc, p, grid, stream);
-    else if (g.c_dtype == diopi_dtype_float16) e = launch_pair<fp16>(ma, mb, mc, p, grid, stream);
-    else e = launch_pair<float>(ma, mb, mc, p, grid, stream);
+    if (g.c_dtype == diopi_dtype_bfloat16) e = launch_pair<bf16, false>(ma, mb, mc, p, q, grid, stream);
+    else if (g.c_dtype == diopi_dtype_float16) e = launch_pair<fp16, false>(ma, mb, mc, p, q, grid, stream);
+    else e = launch_pair<float, false>(ma, mb, mc, p, q, grid, stream);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
         B200_FAIL("gemm: tcgen05 pair kernel launch failed: %s", cudaGetErrorString(e));
+    }
+    return diopiSuccess;
+}
+
+// This rank's partial product, pushed tile by tile into the staging slots of the ranks that own the rows. g.C is not used.
+diopiError_t gemm_tc2_push_launch(const GemmProblem& g, const b200PeerSpace& space, int slot, uint32_t epoch, uint32_t prev_epoch,
+                                  cudaStream_t stream) {
+    const int n = space.nranks;
+    B200_CHECK(n >= 1 && n <= B200_PEER_MAX_RANKS && space.rank >= 0 && space.rank < n, "mm push: bad peer space (rank %d of %d)", space.rank, n);
+    B200_CHECK(slot >= 0 && slot < space.slots, "mm push: slot %d outside [0, %d)", slot, space.slots);
+    B200_CHECK(g.batch == 1 && g.bias == nullptr && g.c_dtype == g.ab_dtype, "mm push: one plain product with the operands' dtype as result");
+    B200_CHECK(g.M % (2 * BM) == 0 && g.M % (static_cast<int64_t>(BM) * n) == 0 && g.N % BN == 0 && g.K >= BK,
+               "mm push: rows must be a multiple of %d x ranks and columns of %d (got %lld x %lld, %d ranks)", BM, BN, (long long)g.M, (long long)g.N, n);
+    const int64_t es = dtype_size(g.ab_dtype);
+    B200_CHECK(static_cast<uint64_t>(g.M * g.N * es) <= space.slot_bytes, "mm push: result of %lld bytes exceeds the slot size %llu",
+               (long long)(g.M * g.N * es), (unsigned long long)space.slot_bytes);
+    const int64_t units = (g.M / n / B200_PEER_PIECE_ROWS) * (g.N / B200_PEER_PIECE_COLS);
+    B200_CHECK(units <= static_cast<int64_t>(space.max_units), "mm push: %lld pieces per rank exceed the space's %u", (long long)units, space.max_units);
+    CUtensorMap ma, mb;
+    PairParams p;
+    if (diopiError_t err = pair_setup(g, &ma, &mb, &p); err != diopiSuccess) return err;
+    // each rank starts at the rows of the next rank and ends with its own
+    const int64_t start_row = (static_cast<int64_t>(space.rank + 1) % n) * (g.M / n);
+    p.m_rot = static_cast<int>(start_row / (2 * BM));
+    PushParams q;
+    q.space = space;
+    q.slot = slot;
+    q.epoch = epoch;
+    q.prev_epoch = prev_epoch;
+    q.rows_per_rank = static_cast<int>(g.M / n);
+    const int grid = pair_grid(p);
+    cudaError_t e = g.ab_dtype == diopi_dtype_bfloat16 ? launch_pair<bf16, true>(ma, mb, ma, p, q, grid, stream)
+                                                       : launch_pair<fp16, true>(ma, mb, ma, p, q, grid, stream);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        B200_FAIL("mm push: tcgen05 pair kernel launch failed: %s", cudaGetErrorString(e));
     }
     return diopiSuccess;
 }

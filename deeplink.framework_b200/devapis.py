@@ -103,6 +103,11 @@ _SIGS = {
     "b200_dicl_comm_rank": [_vp, ctypes.POINTER(_i), ctypes.POINTER(_i)],
     "b200_dicl_peer_reduce_create": [ctypes.POINTER(_vp), _vp, _sz, _vp], "b200_dicl_peer_all_reduce": [_vp, _vp, _vp, _sz, _i, _vp],
     "b200_dicl_peer_reduce_destroy": [_vp],
+    "b200_dicl_peer_space_create": [ctypes.POINTER(_vp), _vp, _sz, _i, _vp],
+    "b200_dicl_peer_space_create_emulated": [ctypes.POINTER(_vp), _i, _sz, _i],
+    "b200_dicl_peer_space_describe": [_vp, _vp],
+    "b200_dicl_peer_reduce_gather": [_vp, _i, ctypes.c_uint32, _vp, ctypes.c_int64, ctypes.c_int64, _i, _i, _vp],
+    "b200_dicl_peer_space_destroy": [_vp],
     "b200_expandable_create": [ctypes.POINTER(_vp), _i, _vp, _sz, ctypes.POINTER(_i), _i], "b200_expandable_destroy": [_vp],
     "b200_expandable_map": [_vp, _vp, _sz, ctypes.POINTER(_vp), ctypes.POINTER(_sz)],
     "b200_expandable_unmap": [_vp, _vp, _sz, ctypes.POINTER(_vp), ctypes.POINTER(_sz)], "b200_expandable_add_peer": [_vp, _i],
@@ -114,6 +119,10 @@ for _n in ("b200_stream_not_null", "b200_is_stream_empty", "b200_is_pinned_ptr",
     getattr(_v, _n).restype = ctypes.c_int
 _v.b200_dicl_peer_reduce_status.argtypes = [_vp]
 _v.b200_dicl_peer_reduce_status.restype = ctypes.c_int
+_v.b200_dicl_peer_space_status.argtypes = [_vp]
+_v.b200_dicl_peer_space_status.restype = ctypes.c_int
+_v.b200_dicl_peer_space_result.argtypes = [_vp, _i]
+_v.b200_dicl_peer_space_result.restype = _vp
 _v.b200_expandable_ptr.argtypes = [_vp]
 _v.b200_expandable_ptr.restype = _vp
 _v.b200_expandable_size.argtypes = [_vp]
@@ -125,7 +134,7 @@ _v.b200_is_stream_empty.argtypes = [_vp]
 _v.b200_is_pinned_ptr.argtypes = [_vp]
 
 C_SYMBOLS = sorted(list(_SIGS) + ["b200_stream_not_null", "b200_is_stream_empty", "b200_is_pinned_ptr", "b200_dicl_unique_id_bytes",
-                                  "b200_last_error", "b200_dicl_peer_reduce_status", "b200_expandable_ptr", "b200_expandable_size", "b200_expandable_mapped_bytes"])
+                                  "b200_last_error", "b200_dicl_peer_reduce_status", "b200_dicl_peer_space_status", "b200_dicl_peer_space_result", "b200_expandable_ptr", "b200_expandable_size", "b200_expandable_mapped_bytes"])
 
 
 def last_error():
@@ -526,6 +535,83 @@ class PeerAllReduce:
     def close(self):
         if self.handle:
             _check(_v.b200_dicl_peer_reduce_destroy(self.handle), "peer reduce destroy")
+            self.handle = None
+
+
+class _DeviceBytes:
+    """A device address range in the form torch.as_tensor() accepts (CUDA array interface, version 2)."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
+
+
+def tensorFromDevicePtr(ptr, shape, dtype, device):
+    """A torch tensor that views `shape` elements of `dtype` at device address `ptr` (no copy; the memory's owner must
+    outlive the tensor)."""
+    import torch
+    n = 1
+    for d in shape:
+        n *= int(d)
+    raw = torch.as_tensor(_DeviceBytes(ptr, n * torch.empty((), dtype=dtype).element_size()), device=device)
+    return raw.view(dtype).view(*shape)
+
+
+class _PeerSpaceDesc(ctypes.Structure):
+    """b200PeerSpace (include/dipu_b200/peer_space.h)."""
+    _fields_ = [("rank", ctypes.c_int32), ("nranks", ctypes.c_int32), ("slots", ctypes.c_int32), ("max_units", ctypes.c_uint32),
+                ("ctas", ctypes.c_uint32), ("pad_", ctypes.c_uint32), ("slot_bytes", ctypes.c_uint64),
+                ("stage", ctypes.c_void_p * 8), ("gout", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8)]
+
+
+class PeerSpace:
+    """Staging / result slots shared by a communicator's ranks for row-parallel linears whose all-reduce is fused into the
+    compute kernels (no reference counterpart; b200_dicl_peer_space_* in include/dipu_b200/vendor_c_api.h). Creation is
+    collective. One fused linear is `diopi.diopiB200MmPush(ctx, x, w_t, space, slot, epoch, prev)` followed by
+    `space.reduce_gather(slot, epoch, residual, rows, cols, dtype, stream)`; begin() hands out (epoch, prev) for a slot."""
+
+    def __init__(self, comm, slot_bytes, slots, stream, _handle=None):
+        if _handle is None:
+            h = _vp()
+            _check(_v.b200_dicl_peer_space_create(ctypes.byref(h), comm, slot_bytes, int(slots), stream), "peer space create")
+            _handle = h.value
+        self.handle, self.slot_bytes, self.slots = _handle, slot_bytes, slots
+        self.desc = _PeerSpaceDesc()
+        _check(_v.b200_dicl_peer_space_describe(self.handle, ctypes.addressof(self.desc)), "peer space describe")
+        self.epoch = 0
+        self.last = [0] * slots  # epoch of the last call on each slot
+        self.final_wait = 1
+
+    @classmethod
+    def emulated(cls, nranks, slot_bytes, slots):
+        """A group of `nranks` in this process on the current device (tests): returns one PeerSpace per rank. Enqueue the
+        products of all ranks first, then the reductions, on one stream."""
+        arr = (ctypes.c_void_p * nranks)()
+        _check(_v.b200_dicl_peer_space_create_emulated(arr, int(nranks), slot_bytes, int(slots)), "peer space create (emulated)")
+        out = [cls(None, slot_bytes, slots, None, _handle=arr[r]) for r in range(nranks)]
+        for s in out:
+            s.final_wait = 0
+        return out
+
+    def begin(self, slot):
+        """Numbers for the next fused linear on `slot`: (epoch, epoch of the previous call on that slot). Every rank must
+        call this in the same order."""
+        self.epoch += 1
+        prev, self.last[slot] = self.last[slot], self.epoch
+        return self.epoch, prev
+
+    def result_ptr(self, slot):
+        return _v.b200_dicl_peer_space_result(self.handle, int(slot))
+
+    def reduce_gather(self, slot, epoch, residual_ptr, rows, cols, datatype, stream):
+        _check(_v.b200_dicl_peer_reduce_gather(self.handle, int(slot), int(epoch), residual_ptr or None, int(rows), int(cols), int(datatype),
+                                               int(self.final_wait), stream), "peer reduce-gather")
+
+    def status(self):
+        return _v.b200_dicl_peer_space_status(self.handle)
+
+    def close(self):
+        if self.handle:
+            _check(_v.b200_dicl_peer_space_destroy(self.handle), "peer space destroy")
             self.handle = None
 
 

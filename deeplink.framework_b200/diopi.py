@@ -86,7 +86,7 @@ class Handle:
             raise DiopiError("could not create a tensor handle")
 
     def __del__(self):
-        if getattr(self, "ptr", None):
+        if getattr(self, "ptr", None) and _host is not None:  # at interpreter exit the module globals may already be gone
             _host.minihostFreeTensor(self.ptr)
             self.ptr = None
 
@@ -286,6 +286,19 @@ def diopiIndex(ctx, self_tensor, indices):
         from . import devapis
         devapis.memCopyD2DAsync(ctx.stream, nbytes, ctx.device, result.data_ptr(), ctx.device, data.value)
     return result
+
+
+def diopiB200MmPush(ctx, mat1, mat2, space, slot, epoch, prev_epoch):
+    """This rank's partial product mat1 [M, K] x mat2 [K, N], pushed piece by piece into the peers' staging slots (see
+    include/diopi/functions_b200.h). `space` is a devapis.PeerSpace; pair every call with space.reduce_gather()."""
+    fn = _lib.diopiB200MmPush
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_uint32, ctypes.c_uint32]
+    fn.restype = ctypes.c_int
+    h1, h2 = handle(mat1), handle(mat2)
+    rc = fn(ctx.ptr, h1.ptr, h2.ptr, ctypes.addressof(space.desc), int(slot), int(epoch), int(prev_epoch))
+    if rc != 0:
+        raise DiopiError("diopiB200MmPush failed with code %d: %s" % (rc, last_error()))
+    return rc
 
 
 def last_error():

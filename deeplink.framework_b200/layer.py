@@ -47,12 +47,67 @@ class TpGroup:
         self.comm = devapis.diclCommInitRank(size, unique_id, rank, device)
         self.stream = devapis.getStreamFromPool(device)
         self.peer = None  # one-kernel all-reduce over peer memory for small messages (enable_peer_reduce)
+        self.space = None  # staging / result slots for row-parallel linears with the all-reduce fused in (enable_fused_linear)
 
     def enable_peer_reduce(self, max_bytes=1 << 20):
         """Collective: from now on dense bf16 / fp16 / fp32 messages of up to max_bytes are summed by one kernel over peer
         memory on the compute stream itself (no stream hop, no library call); larger ones keep going through diclAllReduce."""
         self.peer = devapis.PeerAllReduce(self.comm, max_bytes, self.stream)
         devapis.syncStream(self.stream)
+
+    def enable_fused_linear(self, part_rows, cols, parts, on_comm_stream=True, space=None):
+        """Collective: allocates the peer space for row-parallel linears of [part_rows, K] x [K, cols] whose all-reduce and
+        residual add are fused into the kernels (fused_row_linear). A layer call handles `parts` row blocks (1, or 2 when
+        two half-batches are interleaved), each with an attention and an FFN linear: 2 * parts slots, the slots of one
+        linear adjacent so that the parts' results form one [parts * part_rows, cols] tensor."""
+        self.space_parts, self.space_rows, self.space_cols = parts, part_rows, cols
+        self.fused_on_comm_stream = on_comm_stream
+        self.space = space or devapis.PeerSpace(self.comm, part_rows * cols * 2, 2 * parts, self.stream)
+        if self.stream is not None:
+            devapis.syncStream(self.stream)
+
+    def _torch_device(self):
+        return torch.device("cuda", self.device) if isinstance(self.device, int) else torch.device(self.device)
+
+    def disable_fused_linear(self):
+        """Collective: frees the peer space. A rank's last kernel writes flags into the peers' memory, so every rank first
+        drains its device and then meets the others in a small all-reduce before anything is unmapped."""
+        if self.space is None:
+            return
+        devapis.syncDevice()
+        token = torch.zeros(1, dtype=torch.float32, device=self._torch_device())
+        devapis.diclAllReduce(token.data_ptr(), token.data_ptr(), 1, diopi.DTYPE[token.dtype], devapis.ReduceOp.SUM, self.comm, self.stream)
+        devapis.syncStream(self.stream)
+        self.space.close()
+        self.space = None
+
+    def fused_result(self, which, dtype):
+        """The [parts * part_rows, cols] tensor the `which`-th linear (0: attention output, 1: FFN down) of a layer call fills."""
+        ptr = self.space.result_ptr(which * self.space_parts)
+        return devapis.tensorFromDevicePtr(ptr, (self.space_parts * self.space_rows, self.space_cols), dtype, self._torch_device())
+
+    def fused_row_linear(self, ctx, x, w_t, residual, which, part):
+        """residual + sum over ranks of x @ w_t, for row block `part` of the layer call's `which`-th row-parallel linear:
+        the product pushes its tiles to the owners of their rows while it runs (diopiB200MmPush), then one kernel sums the
+        pieces this rank owns, adds the residual rows and writes the finished rows into every rank's result slot. Returns
+        an event to wait for before reading the result (None when the reduction runs on the compute stream itself)."""
+        sp = self.space
+        slot = which * self.space_parts + part
+        epoch, prev = sp.begin(slot)
+        diopi.diopiB200MmPush(ctx, x, w_t, sp, slot, epoch, prev)
+        rows, cols = x.shape[0], w_t.shape[1]
+        dt = diopi.DTYPE[x.dtype]
+        if not self.fused_on_comm_stream:
+            sp.reduce_gather(slot, epoch, residual.data_ptr() if residual is not None else None, rows, cols, dt, ctx.stream)
+            return None
+        pre = devapis.getEventFromPool()
+        devapis.recordEvent(pre, ctx.stream)
+        devapis.streamWaitEvent(self.stream, pre)
+        devapis.restoreEventToPool(pre)
+        sp.reduce_gather(slot, epoch, residual.data_ptr() if residual is not None else None, rows, cols, dt, self.stream)
+        post = devapis.getEventFromPool()
+        devapis.recordEvent(post, self.stream)
+        return post
 
     def all_reduce_(self, tensor, compute_stream):
         """In-place SUM all-reduce of a dense tensor; the compute stream waits for the result without a host block."""
@@ -85,6 +140,7 @@ class TpGroup:
         if self.peer is not None:
             self.peer.close()
             self.peer = None
+        self.disable_fused_linear()
         devapis.diclCommDestroy(self.comm)
         self.comm = None
 
@@ -107,6 +163,7 @@ class DecoderLayer:
         self.overlap_comm = True  # prefill: interleave two half-batches so the all-reduces overlap compute
         self.scores_by_baddbmm = False  # prefill attention scores through one baddbmm instead of bmm, div, add
         self.fused_attention = False  # prefill attention through the fused operator (no score tensor, no transposes)
+        self.fused_collective = False  # prefill: row-parallel linears push their tiles to the peers (TpGroup.enable_fused_linear)
         d, r = self.head_dim, tp_rank
         hq, hk, f = self.heads, self.kv_heads, self.ffn
 
@@ -180,15 +237,19 @@ class DecoderLayer:
         if self.tp_size > 1:
             self.tp_group.all_reduce_(t, ctx.stream)
 
-    def _ffn_partial(self, ctx, h):
-        """RMSNorm -> gate / up -> SiLU * up -> down projection: this rank's partial sum (before the all-reduce)."""
+    def _ffn_core(self, ctx, h):
+        """RMSNorm -> gate / up -> SiLU * up: the input of the (row-parallel) down projection."""
         hn = self._like(h)
         self._call(diopi.diopiRMSNorm, ctx, hn, None, h, [self.hidden], self.ffn_norm, None, self.eps)
         g = self._linear(ctx, hn, self.w1)
         u = self._linear(ctx, hn, self.w3)
         self._call(diopi.diopiSiluInp, ctx, g)
         self._call(diopi.diopiMulInp, ctx, g, u)
-        return self._linear(ctx, g, self.w2)
+        return g
+
+    def _ffn_partial(self, ctx, h):
+        """RMSNorm -> gate / up -> SiLU * up -> down projection: this rank's partial sum (before the all-reduce)."""
+        return self._linear(ctx, self._ffn_core(ctx, h), self.w2)
 
     def _ffn(self, ctx, h, out=None):
         dn = self._ffn_partial(ctx, h)
@@ -200,6 +261,10 @@ class DecoderLayer:
     # ---- prefill ---------------------------------------------------------------------------------------------------
     def _attention_partial(self, ctx, x, batch, seq):
         """RMSNorm -> q/k/v -> rotary -> causal attention through bmm + softmax -> o_proj: this rank's partial sum."""
+        return self._linear(ctx, self._attention_core(ctx, x, batch, seq), self.wo)
+
+    def _attention_core(self, ctx, x, batch, seq):
+        """Everything of the attention block before the (row-parallel) output projection: [batch*seq, local heads * D]."""
         t, d, hq, hk = batch * seq, self.head_dim, self.heads, self.kv_heads
         hn = self._like(x)
         self._call(diopi.diopiRMSNorm, ctx, hn, None, x, [self.hidden], self.attention_norm, None, self.eps)
@@ -213,7 +278,7 @@ class DecoderLayer:
             # one call on the [B, S, h, D] views: grouped heads share K / V inside the kernel, output lands merged
             merged = self._empty(batch, seq, hq, d)
             self._call(diopi.diopiMultiHeadAttention, ctx, q, k, v, 0.0, True, False, 1.0 / math.sqrt(d), merged, None, None, None)
-            return self._linear(ctx, merged.view(t, hq * d), self.wo)
+            return merged.view(t, hq * d)
         # [B, S, h, D] -> [B, h, S, D]: .transpose(1, 2).contiguous() is a copy_ from a strided view
         qt, kt, vt = self._empty(batch, hq, seq, d), self._empty(batch, hk, seq, d), self._empty(batch, hk, seq, d)
         self._call(diopi.diopiCopyInp, ctx, q.transpose(1, 2), qt)
@@ -235,11 +300,13 @@ class DecoderLayer:
         self._call(diopi.diopiBmm, ctx, av, scores, vt.view(batch * hq, seq, d))
         merged = self._empty(batch, seq, hq, d)
         self._call(diopi.diopiCopyInp, ctx, av.view(batch, hq, seq, d).transpose(1, 2), merged)
-        return self._linear(ctx, merged.view(t, hq * d), self.wo)
+        return merged.view(t, hq * d)
 
     def prefill(self, x, batch, seq, ctx=None):
         """x [batch*seq, hidden] -> [batch*seq, hidden]; causal attention through bmm + softmax."""
         ctx = ctx or diopi.Context()
+        if self.fused_collective and self.tp_group is not None and self.tp_group.space is not None:
+            return self._prefill_fused_collective(x, batch, seq, ctx)
         if self.tp_size > 1 and self.overlap_comm and batch % 2 == 0:
             return self._prefill_overlapped(x, batch, seq, ctx)
         attn = self._attention_partial(ctx, x, batch, seq)
@@ -275,6 +342,37 @@ class DecoderLayer:
             self._call(diopi.diopiAdd, ctx, outs[i], h[i], dn[i], 1)
         ctx.release_workspace()
         return out
+
+    def _prefill_fused_collective(self, x, batch, seq, ctx):
+        """Tensor-parallel prefill without library collectives and without separate residual adds: each row-parallel linear
+        pushes its output tiles to the ranks that own the rows while it is still multiplying, and one kernel per linear
+        sums the arrived pieces, adds the residual and hands the finished rows to every rank (TpGroup.fused_row_linear).
+        With two parts the reductions run on the communication stream while the other half-batch computes. The returned
+        tensor lives in the group's peer space: it keeps its content until the next call's FFN linear."""
+        grp, cs = self.tp_group, ctx.stream
+        parts = grp.space_parts
+        assert batch % parts == 0 and (batch // parts) * seq == grp.space_rows and self.hidden == grp.space_cols, \
+            "the peer space was sized for %d parts of %d rows" % (parts, grp.space_rows)
+        pb, rows = batch // parts, grp.space_rows
+        xs = [x[i * rows:(i + 1) * rows] for i in range(parts)]
+        h_all, out_all = grp.fused_result(0, self.dtype), grp.fused_result(1, self.dtype)
+        hs = [h_all[i * rows:(i + 1) * rows] for i in range(parts)]
+        ev = [None] * parts
+        for i in range(parts):
+            merged = self._attention_core(ctx, xs[i], pb, seq)
+            self.launches += 2
+            ev[i] = grp.fused_row_linear(ctx, merged, self.wo.t(), xs[i], 0, i)
+        for i in range(parts):
+            if ev[i] is not None:
+                grp.wait(ev[i], cs)
+            g = self._ffn_core(ctx, hs[i])
+            self.launches += 2
+            ev[i] = grp.fused_row_linear(ctx, g, self.w2.t(), hs[i], 1, i)
+        for i in range(parts):
+            if ev[i] is not None:
+                grp.wait(ev[i], cs)
+        ctx.release_workspace()
+        return out_all
 
     def capture_decode(self, x, k_cache, v_cache, position, ctx):
         """Captures one decode step (every DIOPI call, the KV append and, under tensor parallelism, the all-reduces on the

@@ -5,6 +5,7 @@
 #define DIOPI_FUNCTIONS_B200_H_
 
 #include "diopi/diopirt.h"
+#include "dipu_b200/peer_space.h"
 
 #ifdef __cplusplus
 extern "C" {
@@ -39,6 +40,21 @@ DIOPI_API int diopiB200GemmStatus(void);
 DIOPI_API diopiError_t diopiB200MmNoAlloc(diopiStreamHandle_t stream, void* out, const void* mat1, const void* mat2, int64_t m, int64_t n,
                                           int64_t k, int64_t ld1, int64_t ld2, int mat2_is_nk, int64_t ldo, diopiDtype_t dtype);
 DIOPI_API int diopiB200NoAllocStatus(void);
+
+/* No counterpart in the reference, where a row-parallel linear is diopiMm followed by an all-reduce of its result
+ * (ProcessGroupDICL::allreduce, dipu/torch_dipu/csrc_dipu/runtime/distributed/ProcessGroupDICL.cpp:539-567).
+ *
+ * input [M, K] x mat2 [K, N] (bfloat16 or float16, the layouts diopiMm takes on its tensor-core path) is this rank's
+ * partial sum. Nothing is stored locally: the kernel's epilogue writes every 32 x 256 piece into staging slot `slot` of
+ * the rank that owns the piece's rows (rank r owns rows [r * M / nranks, (r + 1) * M / nranks)) over peer memory and
+ * raises the piece's ready flag with `epoch`, while later tiles are still being multiplied. b200_dicl_peer_reduce_gather
+ * (include/dipu_b200/vendor_c_api.h), called next with the same slot and epoch on every rank, sums the pieces and
+ * distributes the result. `epoch` must grow from call to call and be the same on every rank; `prev_epoch` is the epoch of
+ * the previous call that used `slot` (0 if none): the kernel does not overwrite a peer's slot before that call's
+ * reduction has finished there (bounded wait; a time-out raises diopiB200GemmStatus).
+ * M must be a multiple of 256 and of 128 * nranks, N a multiple of 256, M * N elements must fit a slot. */
+DIOPI_API diopiError_t diopiB200MmPush(diopiContextHandle_t ctx, diopiConstTensorHandle_t input, diopiConstTensorHandle_t mat2,
+                                       const b200PeerSpace* space, int32_t slot, uint32_t epoch, uint32_t prev_epoch);
 
 #ifdef __cplusplus
 }

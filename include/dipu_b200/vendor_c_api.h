@@ -22,6 +22,8 @@
 #include <stdint.h>
 #include <sys/types.h>
 
+#include "dipu_b200/peer_space.h"
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -221,6 +223,32 @@ B200_API b200Status_t b200_dicl_peer_reduce_create(void** handle, b200Comm_t com
 B200_API b200Status_t b200_dicl_peer_all_reduce(void* handle, const void* send, void* recv, size_t count, int dtype, b200Stream_t stream);
 B200_API int b200_dicl_peer_reduce_status(void* handle);
 B200_API b200Status_t b200_dicl_peer_reduce_destroy(void* handle);
+
+/* Peer space: staging slots, result slots and flags every rank of a communicator allocates and maps from all peers
+ * (layout: dipu_b200/peer_space.h), for a row-parallel linear whose all-reduce is fused into the compute kernels: the
+ * matrix product pushes its tiles to the owners of their rows (diopiB200MmPush, include/diopi/functions_b200.h), and
+ * peer_reduce_gather then forms residual + sum of the partial products for the rows this rank owns and writes them into
+ * result slot `slot` of EVERY rank. The reference does this as mm followed by ProcessGroupDICL::allreduce
+ * (runtime/distributed/ProcessGroupDICL.cpp:539-567) and an aten add. No reference counterpart.
+ *   create            collective over `comm`; slot_bytes a multiple of 16384; the largest [rows, cols] result must fit a slot.
+ *   create_emulated   a group of `nranks` inside one process on the current device (tests): handles[r] is rank r's view.
+ *                     Launch the products of all ranks first, then the reductions with final_wait = 0, all on one stream.
+ *   describe          geometry and this process's mappings, by value, for diopiB200MmPush.
+ *   result            device address of result slot `slot` on this rank: [rows, cols] dense. It keeps its content until a
+ *                     later reduce_gather call on the same slot starts on ANY rank, so re-use a slot only after every reader
+ *                     of its old content has been ordered before this rank's next product on that slot.
+ *   reduce_gather     every rank, same order, same (slot, epoch, rows, cols); epoch as passed to the products. float16 (8)
+ *                     or bfloat16 (12); residual [rows, cols] dense, 16-byte aligned, or NULL (only the owned rows are read).
+ *                     All calls on one handle must be enqueued on one stream. final_wait = 1 except under emulation.
+ *   status            0, or 1 once a wait for a peer ran into its 1 s limit. */
+B200_API b200Status_t b200_dicl_peer_space_create(void** handle, b200Comm_t comm, size_t slot_bytes, int slots, b200Stream_t stream);
+B200_API b200Status_t b200_dicl_peer_space_create_emulated(void** handles, int nranks, size_t slot_bytes, int slots);
+B200_API b200Status_t b200_dicl_peer_space_describe(void* handle, b200PeerSpace* out);
+B200_API void* b200_dicl_peer_space_result(void* handle, int slot);
+B200_API b200Status_t b200_dicl_peer_reduce_gather(void* handle, int slot, uint32_t epoch, const void* residual, int64_t rows, int64_t cols,
+                                                   int dtype, int final_wait, b200Stream_t stream);
+B200_API int b200_dicl_peer_space_status(void* handle);
+B200_API b200Status_t b200_dicl_peer_space_destroy(void* handle);
 
 #ifdef __cplusplus
 }

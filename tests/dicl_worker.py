@@ -155,7 +155,7 @@ def main():
 
     class Group:
         def __init__(self):
-            self.rank, self.size, self.device, self.comm, self.stream, self.peer = rank, world, rank, comm, stream, None
+            self.rank, self.size, self.device, self.comm, self.stream, self.peer, self.space = rank, world, rank, comm, stream, None, None
     grp = L.TpGroup.__new__(L.TpGroup)
     grp.__dict__.update(Group().__dict__)
     lay = L.DecoderLayer(cfg, w, dtype=torch.float32, device=dev, tp_rank=rank, tp_size=world, tp_group=grp)
@@ -177,6 +177,35 @@ def main():
     assert err <= 2e-4, ("peer reduce", err)
     grp.peer.close()
     grp.peer = None
+
+    # row-parallel linears with the all-reduce and the residual add fused into the kernels: tiles pushed to the owners of
+    # their rows, one reduce-gather kernel per linear; against the op-by-op bf16 CPU oracle and against the NCCL path
+    seq = 128 * world
+    idsb = llama_cpu.make_token_ids(2, seq, seed=78)
+    refb = llama_cpu.decoder_layer_prefill(cfg, llama_cpu.round_weights(w, torch.bfloat16), llama_cpu.round_tensor(emb, torch.bfloat16), idsb,
+                                           step=llama_cpu.stepwise(torch.bfloat16))
+    ref32 = llama_cpu.decoder_layer_prefill(cfg, w, emb, idsb)
+    layb = L.DecoderLayer(cfg, w, dtype=torch.bfloat16, device=dev, tp_rank=rank, tp_size=world, tp_group=grp)
+    xb = L.embed(emb.to(torch.bfloat16).to(dev), idsb.to(dev))
+    y_nccl = layb.prefill(xb, 2, seq).float().cpu()
+    for parts, on_comm in ((2, True), (1, False), (2, False)):
+        grp.enable_fused_linear(2 * seq // parts, cfg.hidden, parts, on_comm_stream=on_comm)
+        layb.fused_collective = True
+        for _ in range(3):
+            y = layb.prefill(xb, 2, seq)
+        torch.cuda.synchronize()
+        assert grp.space.status() == 0 and pkg.diopi.gemm_status() == 0
+        got = y.float().cpu()
+        # The sum of the partial products and the residual add happen in fp32 with ONE rounding, where the op-by-op path
+        # rounds the all-reduced sum and then the add: closer to the fp32 layer, but no longer step-for-step the bf16 oracle.
+        # Whole-layer bounds as for the other fused paths: max-abs 2e-2, relative L2 1e-2 against either oracle.
+        for name, want in (("bf16 op-by-op oracle", refb), ("fp32 oracle", ref32), ("library all-reduce path", y_nccl)):
+            max_abs = (got - want).abs().max().item()
+            rel = ((got - want).norm() / want.norm()).item()
+            print("rank %d fused collective parts=%d comm_stream=%s vs %s: max_abs %.3e rel %.3e" % (rank, parts, on_comm, name, max_abs, rel), flush=True)
+            assert max_abs <= 2e-2 and rel <= 1e-2, ("fused collective", parts, on_comm, name, max_abs, rel)
+        layb.fused_collective = False
+        grp.disable_fused_linear()
 
     dv.diclCommDestroy(comm)
     print("rank %d ok" % rank, flush=True)
