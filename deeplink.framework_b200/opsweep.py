@@ -224,12 +224,17 @@ def attention_case(case, diopi, ctx, dev):
     return fns, 4.0 * 128 * pairs, per_set
 
 
+# (emulated ranks, rows, columns, K per rank): the 7B layer's o_proj / down_proj at TP 2 and 8, the 70B down_proj at TP 8
+FUSED_LINEAR_CASES = [(2, 16384, 4096, 2048), (2, 16384, 4096, 5504), (8, 16384, 4096, 512), (8, 16384, 4096, 1376), (8, 16384, 8192, 3584)]
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ops", default="all", help="comma list of: %s, gemm, attention, sampling" % ", ".join(MEM_OPS))
+    ap.add_argument("--ops", default="all", help="comma list of: %s, gemm, attention, sampling, fused_linear (not part of 'all')" % ", ".join(MEM_OPS))
     ap.add_argument("--tokens", default="1,64,1024,16384,65536")
     ap.add_argument("--gemm", default="all", help="comma list of indices into the GEMM case table, or 'all'")
     ap.add_argument("--attention", default="all", help="comma list of indices into the attention case table, or 'all'")
+    ap.add_argument("--fused-linear", default="all", help="comma list of indices into the fused-linear case table, or 'all'")
     ap.add_argument("--iters", type=int, default=50)
     args = ap.parse_args()
 
@@ -246,6 +251,44 @@ def main():
     ops = MEM_OPS + ["gemm", "attention", "sampling"] if args.ops == "all" else args.ops.split(",")
     tokens = [int(x) for x in args.tokens.split(",")]
     for op in ops:
+        if op == "fused_linear":
+            # Row-parallel linear with the all-reduce fused in, ranks emulated on this one device (all "peer" memory is local,
+            # so the figures show the kernels' own cost without NVLink): the storing product, the pushing product, and the
+            # reduce-gather kernel of rank 0 once every rank's pieces are there.
+            bf = torch.bfloat16
+            which = range(len(FUSED_LINEAR_CASES)) if args.fused_linear == "all" else [int(v) for v in args.fused_linear.split(",")]
+            for n, m, cols, k in [FUSED_LINEAR_CASES[i] for i in which]:
+                x = torch.randn((m, k), device=dev, dtype=bf)
+                w = torch.randn((cols, k), device=dev, dtype=bf) * 0.02
+                res = torch.randn((m, cols), device=dev, dtype=bf)
+                out = torch.empty((m, cols), device=dev, dtype=bf)
+                spaces = pkg.devapis.PeerSpace.emulated(n, m * cols * 2, 1)
+                sp = spaces[0]
+                flops = 2.0 * m * cols * k
+
+                def push():
+                    ep, _ = sp.begin(0)
+                    diopi.diopiB200MmPush(ctx, x, w.t(), sp, 0, ep, 0)
+                ms_mm = time_cases([lambda: diopi.diopiMm(ctx, out, x, w.t())], args.iters, stream)
+                ms_push = time_cases([push], args.iters, stream)
+                ep = 1 << 20
+                for s_ in spaces:
+                    diopi.diopiB200MmPush(ctx, x, w.t(), s_, 0, ep, 0)
+                ms_red = time_cases([lambda: sp.reduce_gather(0, ep, res.data_ptr(), m, cols, diopi.DTYPE[bf], stream.cuda_stream)], args.iters, stream)
+                shard = m * cols * 2 // n
+                alg = (n + 1) * shard + n * shard  # n partial shards + residual shard read, the finished shard written to n ranks
+                torch.cuda.synchronize()
+                print(json.dumps({"op": "fused_linear", "ranks_emulated": n, "m": m, "n": cols, "k": k, "mm_store_ms": round(ms_mm, 4),
+                                  "mm_store_tflops": round(flops / (ms_mm * 1e-3) / 1e12, 1), "mm_push_ms": round(ms_push, 4),
+                                  "mm_push_tflops": round(flops / (ms_push * 1e-3) / 1e12, 1), "reduce_gather_ms": round(ms_red, 4),
+                                  "reduce_gather_gbs": round(alg / (ms_red * 1e-3) / 1e9, 1),
+                                  "frac_of_%s_hbm" % src: round(alg / (ms_red * 1e-3) / 1e9 / hbm, 4),
+                                  "status": [diopi.gemm_status(), sp.status()]}), flush=True)
+                for s_ in spaces:
+                    s_.close()
+                del x, w, res, out
+                ctx.release_workspace()
+            continue
         if op == "sampling":
             # one sampling step over a [64, 32000] fp32 logits matrix, each operator timed on its own
             b, v = 64, 32000
