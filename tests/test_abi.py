@@ -101,3 +101,7 @@ def test_torch_abi_library_has_dipu_devapis_signatures(pkg):
     selftest = handle.b200_torchabi_generator_selftest
     selftest.restype = ctypes.c_int
     assert selftest() == 0
+    # the copy_ policy object registered with setDipuCopyInstance: which path each kind of copy takes (metadata-only tensors)
+    copytest = handle.b200_torchabi_copy_selftest
+    copytest.restype = ctypes.c_int
+    assert copytest() == 0
