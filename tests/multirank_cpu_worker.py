@@ -29,8 +29,29 @@ def main():
     dist.all_reduce(attn, op=dist.ReduceOp.SUM)
     h = x + attn
     ffn = llama_cpu.feed_forward(ws, llama_cpu.rms_norm(h, w["ffn_norm"], cfg.eps))
+    ffn_partial = ffn.clone()
     dist.all_reduce(ffn, op=dist.ReduceOp.SUM)
     out = h + ffn
+    # The fused row-parallel linear's decomposition of that all-reduce + add: rank r owns rows [r * T / n, (r + 1) * T / n);
+    # every rank hands each owner its partial sums of the owner's rows (the pushing product), the owner adds them in rank
+    # order to its residual rows (the reduce-gather kernel) and every rank receives every owner's finished rows.
+    rows = ffn_partial.shape[0] // world
+    mine = [torch.empty(rows, cfg.hidden) for _ in range(world)]
+    reqs = []
+    for peer in range(world):
+        if peer == rank:
+            mine[rank] = ffn_partial[rank * rows:(rank + 1) * rows]
+        else:
+            reqs.append(dist.isend(ffn_partial[peer * rows:(peer + 1) * rows].contiguous(), dst=peer))
+            reqs.append(dist.irecv(mine[peer], src=peer))
+    for q in reqs:
+        q.wait()
+    owned = h[rank * rows:(rank + 1) * rows].clone()
+    for src in range(world):
+        owned += mine[src]
+    finished = [torch.empty_like(owned) for _ in range(world)]
+    dist.all_gather(finished, owned)
+    assert (torch.cat(finished) - out).abs().max().item() <= 1e-5
     err = (out - full).abs().max().item()
     assert err <= 1e-4, err
     # every rank holds the same result (replicated after the all-reduce)
