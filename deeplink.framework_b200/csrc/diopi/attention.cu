@@ -89,6 +89,10 @@ __device__ __forceinline__ int blocks_of_tile(const AttnParams& p, int q_lo) {
 // Named barrier over `count` threads (two partner warps of a row group); barrier 0 is the CTA-wide one.
 __device__ __forceinline__ void pair_barrier(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
 
+// Position of block j's keys / values in the producer's load order (K0, K1, V0, K2, V1, ..., K(n-1), V(n-2), V(n-1)).
+__device__ __forceinline__ int load_of_k(int j) { return j == 0 ? 0 : 2 * j - 1; }
+__device__ __forceinline__ int load_of_v(int j, int n) { return min(2 * j + 2, 2 * n - 1); }
+
 // SPLIT = threads per query row (1 or 2). With 2, the two threads of a row own 64 score columns each (warps w and w + 4 of
 // the tile's eight softmax warps share a 32-lane quarter of tensor memory), which halves the length of the serial
 // load -> max -> exponentiate -> pack chain that separates a tile's score product from its P V product. Row maxima and
@@ -109,7 +113,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     uint64_t* s_full = bars + 1 + 2 * kRing;   // [2] MMA -> softmax: scores of the block are in TMEM
     uint64_t* p_full = s_full + 2;             // [2] softmax -> MMA: P is in shared memory, S may be overwritten
     uint64_t* pv_done = p_full + 2;            // [2] MMA -> softmax: O holds the block, P may be overwritten
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+    uint64_t* s_free = pv_done + 2;            // [2] softmax -> MMA: the scores are in registers, S may be overwritten
+    uint64_t* turn = s_free + 2;               // [4 quarters][2] softmax warp -> its partner of the other tile: exponentials done
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(turn + 8);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);      // [tile][128 rows]: pair exchange (SPLIT = 2)
     volatile uint8_t* xfail = reinterpret_cast<uint8_t*>(bars) + 256 + 1024;            // [tile][128 rows]: a wait of the pair failed
@@ -132,13 +138,15 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         mbar_init(q_full, 1);
         for (int s = 0; s < kRing; ++s) {
             mbar_init(&kv_full[s], 1);
-            mbar_init(&kv_empty[s], 1);
+            mbar_init(&kv_empty[s], 2);  // one arrival per Q tile (a tile that is alone on a block arrives twice)
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(&s_full[t], 1);
             mbar_init(&p_full[t], 4 * SPLIT);  // one arrival per softmax warp of the tile
             mbar_init(&pv_done[t], 1);
+            mbar_init(&s_free[t], 4 * SPLIT);
         }
+        for (int i = 0; i < 8; ++i) mbar_init(&turn[i], 1);
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async();
@@ -168,26 +176,39 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     tma_load_4d(smem_q + t * kTileBytes + g * kHalfBytes, &map_q, q_full, g * 64, p.q_hfirst ? h : row, p.q_hfirst ? row : h, b);
                 }
             }
+            // Order: K0, then for every block i: K(i+1) if there is one, V(i). The keys run a block ahead of the values because
+            // a tile's next score product is issued as soon as its softmax has read the current scores out of tensor memory,
+            // long before the probabilities for the current values are ready.
             for (int r = 0; r < 2 * nmax; ++r) {
                 const int slot = r % kRing;
                 const uint32_t phase = static_cast<uint32_t>(r / kRing) & 1u;
                 if (!mbar_wait(&kv_empty[slot], phase ^ 1u, abort_flag)) break;
                 mbar_arrive_expect_tx(&kv_full[slot], kTileBytes);
-                const CUtensorMap* m = (r & 1) ? &map_v : &map_k;
-                const int hfirst = (r & 1) ? p.v_hfirst : p.k_hfirst;
-                const int row = (r >> 1) * kBlockKv;
+                const bool is_v = r == 2 * nmax - 1 || (r != 0 && (r & 1) == 0);
+                const int blk = is_v ? (r == 2 * nmax - 1 ? nmax - 1 : (r - 2) / 2) : (r + 1) / 2;
+                const CUtensorMap* m = is_v ? &map_v : &map_k;
+                const int hfirst = is_v ? p.v_hfirst : p.k_hfirst;
+                const int row = blk * kBlockKv;
                 for (int g = 0; g < 2; ++g) {
                     tma_load_4d(smem_kv + slot * kTileBytes + g * kHalfBytes, m, &kv_full[slot], g * 64, hfirst ? hk : row, hfirst ? row : hk, b);
                 }
             }
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
+    } else if (warp == 1 || warp == 3) {
+        // ---------------- MMA issuers: warp 1 for Q tile 0, warp 3 for Q tile 1 ----------------
+        // tcgen05.mma keeps the issuing thread until the product has been taken by the tensor core, so one thread issuing for
+        // both tiles also serialises its own bookkeeping (barrier polls, commits) with the products. With one issuer per
+        // tile the bookkeeping of one overlaps the products of the other. Per tile and block j: S(j+1) goes as soon as the
+        // softmax warps have pulled S(j) into registers (s_free) and K(j+1) has landed - the next scores are computed while
+        // the softmax is still exponentiating the current ones; P V(j) goes when the probabilities are in shared memory
+        // (p_full) and V(j) has landed. Every K / V slot gets two arrivals, one per tile.
         if (lane == 0) {
-            const int nt[2] = {n0, n1};
+            const int t = warp == 1 ? 0 : 1;
+            const int n_t = t == 0 ? n0 : n1;
+            const int n_o = t == 0 ? n1 : n0;
             // Q is always waited for, also when no block is visible: no copy may still be in flight when the CTA ends
-            bool ok = mbar_wait(q_full, 0, abort_flag) && nmax > 0;
-            auto issue_s = [&](int t, int slot) {
+            bool ok = mbar_wait(q_full, 0, abort_flag) && n_t > 0;
+            auto issue_s = [&](int slot) {
                 const uint32_t qa = smem_u32(smem_q + t * kTileBytes);
                 const uint32_t ka = smem_u32(smem_kv + slot * kTileBytes);
 #pragma unroll
@@ -197,7 +218,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                                 k != 0 ? 1u : 0u);
                 }
             };
-            auto issue_pv = [&](int t, int slot, bool accumulate) {
+            auto issue_pv = [&](int slot, bool accumulate) {
                 const uint32_t pa = smem_u32(smem_p + t * kTileBytes);
                 const uint32_t va = smem_u32(smem_kv + slot * kTileBytes);
 #pragma unroll
@@ -207,50 +228,31 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                                 make_smem_desc_sw128(va + k * 2048, kHalfBytes, 1024), p.idesc_pv, (accumulate || k != 0) ? 1u : 0u);
                 }
             };
-            int r = 0;
-            if (ok) {
-                ok = mbar_wait(&kv_full[0], 0, abort_flag);
-                if (ok) {
-                    tc_fence_after();
-                    for (int t = 0; t < 2; ++t) {
-                        if (nt[t] > 0) {
-                            issue_s(t, 0);
-                            umma_commit(&s_full[t]);
-                        }
-                    }
-                    umma_commit(&kv_empty[0]);
-                    r = 1;
-                }
-            }
-            for (int j = 0; j < nmax && ok; ++j) {
-                const int sv = r % kRing;
-                if (!mbar_wait(&kv_full[sv], static_cast<uint32_t>(r / kRing) & 1u, abort_flag)) { ok = false; break; }
-                ++r;
-                const int sk = r % kRing;
-                const uint32_t sk_phase = static_cast<uint32_t>(r / kRing) & 1u;
-                bool k_ready = false;
-                for (int t = 0; t < 2 && ok; ++t) {
-                    if (j < nt[t]) {
-                        if (!mbar_wait(&p_full[t], static_cast<uint32_t>(j) & 1u, abort_flag)) { ok = false; break; }
-                        tc_fence_after();
-                        issue_pv(t, sv, j > 0);
-                        umma_commit(&pv_done[t]);
-                    }
-                    if (t == 1) umma_commit(&kv_empty[sv]);  // V_j is free once both tiles' products have read it
-                    if (j + 1 < nt[t]) {
-                        if (!k_ready) {
-                            if (!mbar_wait(&kv_full[sk], sk_phase, abort_flag)) { ok = false; break; }
-                            tc_fence_after();
-                            k_ready = true;
-                        }
-                        issue_s(t, sk);
-                        umma_commit(&s_full[t]);
-                    }
-                }
-                if (ok && j + 1 < nmax) {
-                    umma_commit(&kv_empty[sk]);
-                    ++r;
-                }
+            // hands block j's slot back: once for this tile, once more for the other tile if it never visits block j
+            auto release = [&](int slot, int j) {
+                umma_commit(&kv_empty[slot]);
+                if (n_o <= j) umma_commit(&kv_empty[slot]);
+            };
+            auto scores = [&](int j) -> bool {
+                const int r = load_of_k(j);
+                if (j > 0 && !mbar_wait(&s_free[t], static_cast<uint32_t>(j - 1) & 1u, abort_flag)) return false;
+                if (!mbar_wait(&kv_full[r % kRing], static_cast<uint32_t>(r / kRing) & 1u, abort_flag)) return false;
+                tc_fence_after();
+                issue_s(r % kRing);
+                umma_commit(&s_full[t]);
+                release(r % kRing, j);
+                return true;
+            };
+            if (ok) ok = scores(0);
+            for (int j = 0; j < n_t && ok; ++j) {
+                if (j + 1 < n_t && !scores(j + 1)) { ok = false; break; }
+                const int r = load_of_v(j, nmax);
+                if (!mbar_wait(&p_full[t], static_cast<uint32_t>(j) & 1u, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&kv_full[r % kRing], static_cast<uint32_t>(r / kRing) & 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                issue_pv(r % kRing, j > 0);
+                umma_commit(&pv_done[t]);
+                release(r % kRing, j);
             }
         }
     } else if (warp >= 4) {
@@ -297,9 +299,6 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         };
         for (int j = 0; j < n_t; ++j) {
             bool my_ok = mbar_wait(&s_full[t], static_cast<uint32_t>(j) & 1u, abort_flag);
-            // P of the previous block has been consumed and O is at rest: the tensor core runs this tile's products in
-            // issue order, so once the scores of block j have landed the P V product of block j-1 is complete as well
-            if (my_ok && j > 0) my_ok = mbar_wait(&pv_done[t], static_cast<uint32_t>(j - 1) & 1u, abort_flag);
             my_ok = __all_sync(0xffffffffu, my_ok);
             if (SPLIT == 1 && !my_ok) {
                 ok = false;
@@ -310,6 +309,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
             for (int c = 0; c < NCH; ++c) tmem_ld_32x32(s_tmem + c * 32, s[c]);
             tmem_ld_wait();
+            // the scores are in registers: the tensor core may write the next block's scores over them right away
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_free[t]);
             const int k0 = j * kBlockKv;
             // warp-uniform: does any element of this tile x block need the mask?
             const bool need_mask = (k0 + kBlockKv > p.Skv) || (p.causal && k0 + kBlockKv - 1 > q_lo + p.causal_off);
@@ -341,29 +344,40 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
             // The running maximum only moves when some row of the warp outgrew it by more than the threshold: P stays
             // below 2^8 and most blocks need no pass over O. Both threads of a row see the same maxima, hence decide alike.
+            bool rescale = false;
+            float factor = 1.f;
             if (j == 0) {
                 m_used = mx;
             } else {
-                const bool rescale = __any_sync(0xffffffffu, mx > m_used + kRescaleThreshold);
+                rescale = __any_sync(0xffffffffu, mx > m_used + kRescaleThreshold);
                 if (rescale) {
                     const float m_new = fmaxf(m_used, mx);
-                    const float factor = (m_used == neg_inf) ? 0.f : fast_exp2(m_used - m_new);
+                    factor = (m_used == neg_inf) ? 0.f : fast_exp2(m_used - m_new);
                     m_used = m_new;
                     l_sum *= factor;
-#pragma unroll 1
-                    for (int c = 0; c < NCH; ++c) {
-                        uint32_t o[32];
-                        tmem_ld_32x32(o_tmem + c * 32, o);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-                        tmem_st_32x32(o_tmem + c * 32, o);
-                    }
-                    tmem_st_wait();
                 }
             }
             const float base = (m_used == neg_inf) ? 0.f : m_used;
             float parts[4] = {0.f, 0.f, 0.f, 0.f};
+            // The two warps of a scheduler (same quarter, one per tile) take turns at the exponentials: the special-function
+            // unit serves 4 lanes per cycle, so two warps exponentiating at once both crawl and then both sit in the phases
+            // that need no such unit (score load, maximum, P store, barriers). In turns, one warp's other phases hide behind
+            // its partner's exponentials. Order: tile 0 block j, tile 1 block j, tile 0 block j + 1, ... as far as both exist.
+            if (SPLIT == 1) {
+                bool go = true;
+                if (t == 0) {
+                    if (j > 0 && j - 1 < n1) go = mbar_wait(&turn[quarter * 2 + 0], static_cast<uint32_t>(j - 1) & 1u, abort_flag);
+                } else {
+                    if (j < n0) go = mbar_wait(&turn[quarter * 2 + 1], static_cast<uint32_t>(j) & 1u, abort_flag);
+                }
+                go = __all_sync(0xffffffffu, go);
+                if (!go) {
+                    ok = false;
+                    break;
+                }
+            }
+            // exponentials first, packed in place (two probabilities per register): nothing here needs the previous block's
+            // P V product, which is still running
 #pragma unroll
             for (int c = 0; c < NCH; ++c) {
 #pragma unroll
@@ -375,11 +389,53 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                         e[u] = fast_exp2(fmaf(__uint_as_float(s[c][i + u]), p.scale_log2, -base));
                         parts[u & 3] += e[u];
                     }
+                    s[c][i / 2 + 0] = pack2<T>(e[0], e[1]);
+                    s[c][i / 2 + 1] = pack2<T>(e[2], e[3]);
+                    s[c][i / 2 + 2] = pack2<T>(e[4], e[5]);
+                    s[c][i / 2 + 3] = pack2<T>(e[6], e[7]);
+                }
+            }
+            if (SPLIT == 1) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&turn[quarter * 2 + (t == 0 ? 1 : 0)]);
+            }
+            // P of the previous block has been consumed and O is at rest once that block's P V product is complete
+            if (j > 0) {
+                bool done = mbar_wait(&pv_done[t], static_cast<uint32_t>(j - 1) & 1u, abort_flag);
+                done = __all_sync(0xffffffffu, done);
+                if (SPLIT == 2) {
+                    // both warps of a row pair must leave together: vote through the shared flag
+                    if (!done) *fail = 1;
+                    pair_barrier(bar_id, 64);
+                    done = __all_sync(0xffffffffu, *fail == 0);
+                }
+                if (!done) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+            }
+            if (rescale) {
+#pragma unroll 1
+                for (int c = 0; c < NCH; ++c) {
+                    uint32_t o[32];
+                    tmem_ld_32x32(o_tmem + c * 32, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+                    tmem_st_32x32(o_tmem + c * 32, o);
+                }
+                tmem_st_wait();
+            }
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
                     uint4 w;
-                    w.x = pack2<T>(e[0], e[1]);
-                    w.y = pack2<T>(e[2], e[3]);
-                    w.z = pack2<T>(e[4], e[5]);
-                    w.w = pack2<T>(e[6], e[7]);
+                    w.x = s[c][i / 2 + 0];
+                    w.y = s[c][i / 2 + 1];
+                    w.z = s[c][i / 2 + 2];
+                    w.w = s[c][i / 2 + 3];
                     // 16-byte chunk `chunk` of the row sits at position chunk ^ (row & 7): the 128-byte swizzle of a
                     // K-major tensor-core operand; columns 0..63 and 64..127 are separate 16 KiB halves
                     const int col = coff + c * 32 + i;
