@@ -4,14 +4,22 @@
 // dicp/dicp/vendor/AscendGraph/ext_ops.py:52-86 (prompt_attention_inference: causal, grouped K/V heads).
 //
 // One CTA per (batch, head, 256 query rows), 384 threads:
-//   warp 0       TMA producer: the two 128-row Q tiles once, then K and V blocks of 128 keys through a 3-slot ring
-//   warp 1       MMA issuer (one thread): S_t = Q_t K_j^T and O_t += P_t V_j with tcgen05.mma, accumulators in TMEM
+//   warp 0       TMA producer: the two 128-row Q tiles once, then K and V blocks of 128 keys through a 3-slot ring, the keys
+//                one block ahead of the values (K0, K1, V0, K2, V1, ...)
+//   warp 1, 3    MMA issuers (one thread each) for Q tile 0 and Q tile 1: S_t = Q_t K_j^T and O_t += P_t V_j with
+//                tcgen05.mma, accumulators in TMEM. tcgen05.mma holds its issuing thread while the product is taken, so
+//                with one issuer per tile the barrier polls and commits of one overlap the products of the other
 //   warp 2       TMEM allocation (512 columns: S_0, S_1, O_0, O_1, 128 fp32 columns each)
 //   warps 4..7   softmax of Q tile 0, warps 8..11 of Q tile 1: one thread per query row reads its 128 scores from
 //                TMEM, keeps the running maximum and sum, writes P (bf16 / fp16) into swizzled shared memory as the A
 //                operand of the second product, and rescales O in TMEM only when the maximum grew by more than 2^8
-// The two Q tiles alternate on the tensor core: while one tile's scores are being exponentiated the other tile's
-// products run. Causal blocks above the diagonal are skipped; only diagonal blocks pay for the element mask.
+// Hand-over per tile and block j: as soon as the softmax warps hold S_j in registers (s_free) the issuer sends S_(j+1), so
+// the next scores are ready before the softmax of block j is over and the softmax warps never wait for the tensor core;
+// P_j is written after P V_(j-1) has completed (pv_done), then p_full releases P V_j. The special-function unit (4 lanes
+// per cycle and scheduler) is what the softmax is bound by: the two warps of a scheduler (same TMEM quarter, one per tile)
+// take turns at the exponentials, so that one warp's other phases (score load, maximum, P store, barriers) run in the
+// shadow of its partner's exponentials. Causal blocks above the diagonal are skipped; only diagonal blocks pay for the
+// element mask.
 // Every wait is bounded (gemm_sm100.cuh); a time-out ends the kernel and is reported through the status word.
 #include <cuda.h>
 #include <cuda_bf16.h>
