@@ -1,7 +1,7 @@
 """Timing of the eager adapter: a plain-torch Llama-style block on torch.device("dipu") at the 7B prefill shape, and the
 host cost of one wrapper call.
 
-    python deeplink.framework_b200/adapter_bench.py [--batch 8 --seq 2048 --steps 10]
+    python adapter_bench.py [--batch 8 --seq 2048 --steps 10]
 
 Prints one JSON line: ms per layer step and tokens/s through torch dispatch + wrapper + DIOPI (the path DIPU's generated
 wrappers take, reference dipu/scripts/autogen_diopi_wrapper/diopi_wrapper_template.py:100-142), the number of DIOPI
@@ -19,7 +19,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 

@@ -12,6 +12,11 @@ work is fixed, so scaling is "strong".
 A step is one layer forward over the 16384 tokens. `value` times steps whose input hidden states are resident in HBM;
 `e2e` times the call a user makes with host buffers: token ids copied from pinned host memory, embedding lookup, layer,
 and the layer output copied back to pinned host memory, every step. One JSON line is printed by rank 0.
+
+Beside the timings the run checks what it timed, outside every timed region: the last output of each variant against the
+CPU oracle on the rows of sequence 0 (`parity`), the decode outputs on four of the 64 sequences, with N > 1 every
+collective of the communicator against closed-form values (`checks`), and at N = 1 the per-op sweep of the memory-bound
+operators (`op_sweep`). A failed parity or collective check makes the process exit non-zero after the line is printed.
 """
 import argparse
 import json
@@ -25,6 +30,8 @@ import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+
+import bench_checks  # noqa: E402  (untimed checks: collectives against closed forms, parity figures against the CPU oracle)
 
 SEED = 1234
 VOCAB = 32000
@@ -113,6 +120,23 @@ def make_device_weights(cfg, device, dtype, seed=SEED):
     }
 
 
+def workload_config(workload, cfg, batch, seq, n_layers, world):
+    """The `config` object: the same for this repository's arm and for the reference arm of the same run."""
+    tokens = batch * seq
+    name = ("llama2-7b-shaped decoder layer, prefill, batch %d x seq %d, bmm+softmax attention" % (batch, seq)) if workload == "7b" \
+        else ("stack of 4 llama2-70b-shaped decoder layers (GQA 64/8), prefill, batch %d x seq %d, bmm+softmax attention" % (batch, seq))
+    weight_mb = (2 * (2 * cfg.hidden * cfg.heads * cfg.head_dim + 2 * cfg.hidden * cfg.kv_heads * cfg.head_dim + 3 * cfg.hidden * cfg.ffn)) >> 20
+    return {"workload": name, "layers": n_layers, "kv_heads": cfg.kv_heads, "hidden": cfg.hidden, "heads": cfg.heads, "head_dim": cfg.head_dim,
+            "ffn": cfg.ffn, "tokens_per_step": tokens, "parallelism": "tp%d" % world,
+            "l2": "inputs larger than L2: weights %d MB per layer + %d MB per activation tensor, no flush" % (weight_mb, (tokens * cfg.hidden * 2) >> 20)}
+
+
+def workload_shape(args):
+    if args.workload == "70b":
+        return Cfg(hidden=8192, heads=64, kv_heads=8, head_dim=128, ffn=28672), 4, 4096, 4
+    return Cfg(), args.batch, args.seq, 1
+
+
 def layer_flops(cfg, batch, seq, tp):
     t = batch * seq
     d = cfg.head_dim
@@ -124,31 +148,42 @@ def layer_flops(cfg, batch, seq, tp):
 # ---------------------------------------------------------------------------------------------------------------------------
 def run_reference(args, rank, world):
     """The reference's own CPU implementation of the path: DIPU's forced CPU fallback executes torch CPU aten kernels
-    (CPUFallback.cpp:130). Timed on the host cores with all threads, each step a bounded sample of the workload."""
+    (CPUFallback.cpp:130). Timed on the host cores with all threads; a step is one forward pass over the whole batch of the
+    workload (the same tokens per step as this repository's arm), fp32."""
     if rank != 0:
         return
     from oracle import llama_cpu
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    cfg = llama_cpu.LayerConfig(hidden=4096, heads=32, kv_heads=32, head_dim=128, ffn=11008)
-    sample_batch, seq = 1, 2048
-    w = llama_cpu.make_weights(cfg, seed=SEED)
+    cfg, batch, seq, n_layers = workload_shape(args)
+    ws = [llama_cpu.make_weights(cfg, seed=SEED + 100 * li) for li in range(n_layers)]
     emb = llama_cpu.make_embedding(VOCAB, cfg.hidden, seed=SEED)
-    ids = llama_cpu.make_token_ids(8, seq, seed=SEED)[:sample_batch]
+    ids = llama_cpu.make_token_ids(batch, seq, seed=SEED)
+
+    def step():
+        # the sequences of a batch are independent under the causal mask; they run one after the other so that the score
+        # tensor of one sequence (heads x seq x seq fp32) is what is resident, as a host with bounded memory would run it
+        for b in range(batch):
+            x = emb[ids[b]]
+            for w in ws:
+                x = llama_cpu.decoder_layer_prefill_from_hidden(cfg, w, x, 1, seq)
+        return x
+
     with torch.no_grad():
-        for _ in range(max(args.warmup, 1)):
-            llama_cpu.decoder_layer_prefill(cfg, w, emb, ids)
+        for _ in range(max(min(args.warmup, 2), 1)):
+            step()
         t0 = time.perf_counter()
         for _ in range(args.steps):
-            llama_cpu.decoder_layer_prefill(cfg, w, emb, ids)
+            step()
         dt = time.perf_counter() - t0
-    value = sample_batch * seq * args.steps / dt
-    sample = "1 of the 8 sequences per step (2048 tokens), fp32, torch CPU aten, %d threads" % cores
+    tokens = batch * seq
+    value = tokens * args.steps / dt
+    sample = "the whole batch per step (%d sequences x %d tokens, one sequence at a time), fp32, torch CPU aten, %d threads" % (batch, seq, cores)
     line = {
         "impl": "reference", "metric": "decoder-layer tokens/s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "llama2-7b-shaped decoder layer, prefill, batch 8 x seq 2048, bmm+softmax attention", "sample": sample},
+        "config": workload_config(args.workload, cfg, batch, seq, n_layers, args.gpus),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -178,6 +213,72 @@ def cpu_baseline_leg():
 
 
 # ---------------------------------------------------------------------------------------------------------------------------
+PREFILL_FORMS = {
+    # name -> keyword arguments of the oracle's layer: all-fp32, and the op-by-op bf16 CPU path (every materialised tensor
+    # rounded to bf16, what the reference's CPU fallback computes on bf16 tensors) in the three op orders that are timed
+    "fp32": {},
+    "bf16_stepwise": {"stepwise": True},
+    "bf16_stepwise_baddbmm": {"stepwise": True, "scores_by_baddbmm": True},
+    "bf16_stepwise_fused": {"stepwise": True, "fused": True},
+}
+
+
+def prefill_oracle_refs(cfg, host_weights, x0, seq, rank, dist, forms):
+    """CPU oracle outputs for ONE sequence (rows [0, seq) of the batch: sequences are independent under the causal mask),
+    computed on rank 0 from the same bf16-rounded weights and embedding rows the device holds, then handed to every rank.
+    x0: [seq, hidden] float32 on the host (rank 0)."""
+    out = {}
+    if rank == 0:
+        from oracle import llama_cpu
+        torch.set_num_threads(os.cpu_count() or 1)
+        with torch.no_grad():
+            for name in forms:
+                kw = dict(PREFILL_FORMS[name])
+                step = llama_cpu.stepwise(torch.bfloat16) if kw.pop("stepwise", False) else (lambda t: t)
+                h = x0
+                for w in host_weights:
+                    h = llama_cpu.decoder_layer_prefill_from_hidden(cfg, w, h, 1, seq, step, **kw)
+                out[name] = h.contiguous()
+    if dist is not None:
+        for name in forms:
+            t = out[name] if rank == 0 else torch.empty((seq, cfg.hidden), dtype=torch.float32)
+            dist.broadcast(t, src=0)
+            out[name] = t
+    return out
+
+
+def decode_oracle_refs(cfg, w, x4, kc4, vc4, position, world, rank, dist):
+    """CPU oracle outputs of the decode step for the first sequences of the batch. kc4 / vc4: this rank's cache shard
+    [n, local kv heads, L, D]; every rank fills its shard from the same seed, so the unsharded cache is the shard repeated
+    over the ranks along the head dimension."""
+    names = ("fp32", "bf16_stepwise", "bf16_stepwise_fused")
+    out = {}
+    if rank == 0:
+        from oracle import llama_cpu
+        kc, vc = kc4.float().cpu().repeat(1, world, 1, 1), vc4.float().cpu().repeat(1, world, 1, 1)
+        xf = x4.float().cpu()
+        bf = llama_cpu.stepwise(torch.bfloat16)
+        with torch.no_grad():
+            out["fp32"] = llama_cpu.decoder_layer_decode(cfg, w, xf, kc, vc, position)[0]
+            out["bf16_stepwise"] = llama_cpu.decoder_layer_decode(cfg, w, xf, kc, vc, position, step=bf)[0]
+            out["bf16_stepwise_fused"] = llama_cpu.decoder_layer_decode(cfg, w, xf, kc, vc, position, step=bf, fused=True)[0]
+    if dist is not None:
+        for name in names:
+            t = out[name].contiguous() if rank == 0 else torch.empty((x4.shape[0], cfg.hidden), dtype=torch.float32)
+            dist.broadcast(t, src=0)
+            out[name] = t
+    return out
+
+
+def all_ranks(flag, dist):
+    """True when `flag` is true on every rank."""
+    if dist is None:
+        return bool(flag)
+    t = torch.tensor([1 if flag else 0], dtype=torch.int64)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(t.item())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -188,6 +289,9 @@ def main():
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the secondary decode measurement")
+    ap.add_argument("--no-parity", action="store_true", help="skip the (untimed) comparison of every variant's output with the CPU oracle")
+    ap.add_argument("--no-checks", action="store_true", help="N > 1: skip the (untimed) closed-form checks of the collectives")
+    ap.add_argument("--no-op-sweep", action="store_true", help="N = 1: skip the per-op sweep of the memory-bound operators")
     ap.add_argument("--no-caching-allocator", action="store_true", help="let torch use its own allocator for tensors")
     ap.add_argument("--workload", default="7b", choices=["7b", "70b"],
                     help="7b: one Llama-2-7B-shaped layer, batch 8 x seq 2048 (default). 70b: a stack of four Llama-2-70B-shaped "
@@ -229,19 +333,19 @@ def main():
         tp_group = L.TpGroup(rank, world, uid[0], local_rank)
 
     dtype = torch.bfloat16
+    cfg, batch, seq, n_layers = workload_shape(args)
     if args.workload == "70b":
-        cfg = Cfg(hidden=8192, heads=64, kv_heads=8, head_dim=128, ffn=28672)
-        batch, seq, n_layers = 4, 4096, 4
         args.no_decode = True
         args.no_cpu_baseline = True
-    else:
-        cfg = Cfg()
-        batch, seq, n_layers = args.batch, args.seq, 1
+        args.no_op_sweep = True
     tokens = batch * seq
     layers = []
+    host_weights = []  # rank 0: the full (unsharded) bf16 weights as float32 on the host, for the oracle of the parity checks
     for li in range(n_layers):
         weights = make_device_weights(cfg, device, dtype, seed=SEED + 100 * li)
         layers.append(L.DecoderLayer(cfg, weights, dtype=dtype, device=device, tp_rank=rank, tp_size=world, tp_group=tp_group))
+        if rank == 0 and not args.no_parity:
+            host_weights.append({k: v.float().cpu() for k, v in weights.items()})
         del weights
     for l_ in layers:
         l_.overlap_comm = (world >= 4) if args.overlap == "auto" else (args.overlap == "on")
@@ -359,6 +463,42 @@ def main():
     devapis.syncStream(copy_stream)
     ms_e2e = max_over_ranks(e0.elapsed_time(e1))
 
+    # ---- parity of what was timed (outside every timed region) ----
+    parity = {}
+    refs = None
+    # Whole prefill layer at the benchmarked shapes: 1e-2 against the op-by-op bf16 CPU path, and against fp32 no further than
+    # 1.25 x that CPU path's own distance from fp32 (bench_checks.py states why); "fp32" below stands for that bound.
+    SW, LOOSE = bench_checks.REL_LOOSE, bench_checks.REL_LOOSE
+    if not args.no_parity:
+        forms = ["fp32", "bf16_stepwise", "bf16_stepwise_fused"] + (["bf16_stepwise_baddbmm"] if args.workload == "7b" else [])
+        x0 = x[:seq].float().cpu() if rank == 0 else None
+        refs = prefill_oracle_refs(cfg, host_weights, x0, seq, rank, dist, forms)
+
+    def record_parity(name, y, against):
+        """Rows of sequence 0 of a variant's last output against the oracle forms in `against` ({form: relative-L2 bound});
+        every rank checks its own (replicated) copy."""
+        if refs is None:
+            return
+        bf16_form = [f for f in against if f != "fp32"][0]
+        bounds = {f: (b if f != "fp32" else bench_checks.fp32_bound(refs[bf16_form], refs["fp32"])) for f, b in against.items()}
+        entry = bench_checks.parity_entry(y[:seq], {f: (refs[f], bounds[f]) for f in against})
+        entry["cpu_bf16_path_vs_fp32_rel_l2"] = round(bench_checks.errors(refs[bf16_form], refs["fp32"])[1], 6)
+        entry["all_ranks_ok"] = all_ranks(entry["ok"], dist)
+        entry["rows_checked"] = "sequence 0 (%d tokens)" % seq
+        parity[name] = entry
+
+    y_lit = step_resident()
+    torch.cuda.synchronize()
+    record_parity("literal", y_lit, {"bf16_stepwise": SW, "fp32": LOOSE})
+    if refs is not None and row_hi > row_lo:
+        # the end-to-end leg's last host copy holds the rows this rank returns: the same bits as the device-resident result
+        last = (e2e_state["i"] - 1) & 1
+        got, want = out_host[last][: row_hi - row_lo].float(), y_lit[row_lo:row_hi].float().cpu()
+        gap = (got - want).abs().max().item()
+        parity["e2e_host_copy"] = {"equals_device_result_bitwise": bool(torch.equal(got, want)), "max_abs_vs_device_result": gap,
+                                   "ok": bool(gap <= bench_checks.MAX_ABS), "all_ranks_ok": all_ranks(gap <= bench_checks.MAX_ABS, dist)}
+    del y_lit
+
     # ---- per-op device times: the same step with events around every DIOPI call ----
     per_op = {}
 
@@ -399,12 +539,16 @@ def main():
             else:
                 bmm_flops, bmm_ms = fl, ms
         else:
+            # bytes moved: every tensor argument once per appearance (an output that is also an input, diopiSoftmax(x, x),
+            # is read and written), plus the write of the first operand of an in-place function; a gather reads rows, not
+            # the table
             by = 0.0
             for _, _, a in recs:
-                seen = set()
+                if name == "diopiIndexSelect":
+                    by += 2 * a[0].numel() * a[0].element_size() + a[3].numel() * a[3].element_size()
+                    continue
                 for t in a:
-                    if isinstance(t, torch.Tensor) and t.is_cuda and t.data_ptr() not in seen:
-                        seen.add(t.data_ptr())
+                    if isinstance(t, torch.Tensor) and t.is_cuda:
                         by += t.numel() * t.element_size()
                 if name.endswith("Inp") or name.endswith("InpScalar"):
                     by += a[0].numel() * a[0].element_size()  # read-modify-write of the first operand
@@ -424,22 +568,30 @@ def main():
                 "peak_source": "%s bf16 cuBLAS, sustained (kernel timed inside a long step)" % peaks["source"],
                 "flops_per_launch": mm_flops / max(mm_calls, 1), "ms_per_launch": mm_ms / max(mm_calls, 1), "traffic": traffic,
                 "traffic_unit": "bytes per launch (mean over the 7 launches), ncu dram__bytes_read.sum + dram__bytes_write.sum",
+                "traffic_source": "one ncu capture of the three projection shapes (profiles/gemm_tc_pair_kernel_prefill_gate_up_16384x11008x4096.md); "
+                                  "a constant of that capture, not re-measured in this run",
                 "algorithmic_bytes_per_launch": (4 * 302.0e6 + 3 * 585.1e6) / 7 if traffic else None}
 
     # ---- variant: attention scores through one baddbmm (scale and mask-add in the GEMM epilogue) ----
     # `value` above is the reference block's literal op order (bmm, div, add, softmax, bmm). A model written with
     # torch.baddbmm(mask, q, k^T, alpha=1/sqrt(d)) reaches diopiBaddbmm instead; timed here with the same K steps.
+    def time_steps():
+        """Three warm-up steps, then K timed steps (device events, max over ranks). Returns (ms, the last step's output)."""
+        y = None
+        for _ in range(3):
+            step_resident()
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            y = step_resident()
+        e1.record(stream)
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1)), y
+
     for l_ in layers:
         l_.scores_by_baddbmm = True
-    for _ in range(3):
-        step_resident()
-    barrier()
-    e0.record(stream)
-    for _ in range(args.steps):
-        step_resident()
-    e1.record(stream)
-    barrier()
-    ms_badd = max_over_ranks(e0.elapsed_time(e1))
+    ms_badd, y_v = time_steps()
+    record_parity("attention_scores_by_baddbmm", y_v, {("bf16_stepwise_baddbmm" if args.workload == "7b" else "bf16_stepwise"): SW, "fp32": LOOSE})
     for l_ in layers:
         l_.scores_by_baddbmm = False
     variants = {"attention_scores_by_baddbmm": {"value": tokens * args.steps / (ms_badd * 1e-3), "unit": "tokens/s",
@@ -449,36 +601,20 @@ def main():
     # ---- variant: attention through the fused operator (diopiMultiHeadAttention: no score tensor, no transposes) ----
     for l_ in layers:
         l_.fused_attention = True
-    for _ in range(3):
-        step_resident()
-    barrier()
-    e0.record(stream)
-    for _ in range(args.steps):
-        step_resident()
-    e1.record(stream)
-    barrier()
-    ms_fused = max_over_ranks(e0.elapsed_time(e1))
+    ms_fused, y_v = time_steps()
+    # the fused operator rounds its probabilities at another point than any op-by-op evaluation can: whole-layer bound 1e-2
+    record_parity("fused_attention", y_v, {"bf16_stepwise_fused": LOOSE, "fp32": LOOSE})
     for l_ in layers:
         l_.fused_attention = False
     variants["fused_attention"] = {"value": tokens * args.steps / (ms_fused * 1e-3), "unit": "tokens/s", "ms_per_step": ms_fused / args.steps,
                                    "note": "diopiMultiHeadAttention (causal) replaces the transposes, diopiBmm, diopiDivInpScalar, diopiAddInp, "
                                            "diopiSoftmax, diopiBmm of the attention core"}
+    del y_v
 
     # ---- variants (N > 1): row-parallel linears with the all-reduce and the residual add fused into the kernels ----
     # diopiB200MmPush pushes each output tile to the rank that owns its rows while the product is still running; one
     # reduce-gather kernel per linear sums the pieces, adds the residual and writes the finished rows to every rank. No
     # library collective and no separate diopiAdd on this path.
-    def time_steps():
-        for _ in range(3):
-            step_resident()
-        barrier()
-        e0.record(stream)
-        for _ in range(args.steps):
-            step_resident()
-        e1.record(stream)
-        barrier()
-        return max_over_ranks(e0.elapsed_time(e1))
-
     if world > 1 and tokens % (256 * world) == 0 and cfg.hidden % 256 == 0:
         choices = [1, 2] if args.fused_collective_parts == "both" else [int(args.fused_collective_parts)]
         for parts in choices:
@@ -494,9 +630,12 @@ def main():
             for fused_attn in (False, True):
                 for l_ in layers:
                     l_.fused_attention = fused_attn
-                ms_v = time_steps()
+                ms_v, y_v = time_steps()
                 ok = tp_group.space.status() == 0 and diopi.gemm_status() == 0
                 name = ("fused_attention_" if fused_attn else "") + "fused_collective" + ("_interleaved_halves" if parts > 1 else "")
+                # one rounding (fp32 sum + residual) where the op-by-op path has two: whole-layer bound 1e-2 against either oracle
+                record_parity(name, y_v, {("bf16_stepwise_fused" if fused_attn else "bf16_stepwise"): LOOSE, "fp32": LOOSE})
+                del y_v
                 variants[name] = {"value": tokens * args.steps / (ms_v * 1e-3), "unit": "tokens/s", "ms_per_step": ms_v / args.steps, "status_ok": ok,
                                   "note": "diopiB200MmPush + peer reduce-gather replace diopiMm + diclAllReduce + diopiAdd after the attention "
                                           "and FFN blocks" + ("; two half-batches interleaved, reductions on the communication stream" if parts > 1 else "")}
@@ -509,25 +648,43 @@ def main():
     # ---- secondary measurement: the same layer in decode (batch 64, KV length 4096) ----
     decode = None
     if not args.no_decode:
-        decode = run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ranks, peaks)
+        decode = run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ranks, peaks, rank, dist,
+                            host_weights[0] if host_weights else None, not args.no_parity)
+        if decode.get("parity") is not None:
+            parity["decode"] = decode.pop("parity")
+
+    # ---- N > 1: every collective of the communicator against closed-form values, at the world size of this run ----
+    checks = None
+    if world > 1 and not args.no_checks:
+        def exchange(obj, src):
+            box = [obj]
+            dist.broadcast_object_list(box, src=src)
+            return box[0]
+        barrier()
+        checks = bench_checks.collective_checks(devapis, diopi.DTYPE, tp_group.comm, tp_group.stream, rank, world, device, exchange)
+        barrier()
+        checks.update(bench_checks.peer_all_reduce_checks(devapis, diopi.DTYPE, tp_group.comm, tp_group.stream, rank, world, device))
+        barrier()
+        mine = all(v for k, v in checks.items() if isinstance(v, bool))
+        checks["all_ranks_ok"] = all_ranks(mine, dist)
+
+    # ---- N = 1: the per-op sweep of the memory-bound operators (bf16 [T, 4096], T in {1, 64, 1024, 16384, 65536}) ----
+    op_sweep = None
+    if world == 1 and not args.no_op_sweep:
+        op_sweep = run_op_sweep(diopi, ctx, device, stream, peaks)
 
     if rank == 0:
         lin, attn = layer_flops(cfg, batch, seq, world)
         lin, attn = lin * n_layers, attn * n_layers
-        workload = ("llama2-7b-shaped decoder layer, prefill, batch %d x seq %d, bmm+softmax attention" % (batch, seq)) if args.workload == "7b" \
-            else ("stack of 4 llama2-70b-shaped decoder layers (GQA 64/8), prefill, batch %d x seq %d, bmm+softmax attention" % (batch, seq))
         value = tokens * args.steps / (ms_total * 1e-3)
         e2e_value = tokens * args.steps / (ms_e2e * 1e-3)
         line = {
             "metric": "decoder-layer tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": workload, "layers": n_layers, "kv_heads": cfg.kv_heads,
-                       "hidden": cfg.hidden, "heads": cfg.heads, "head_dim": cfg.head_dim, "ffn": cfg.ffn, "tokens_per_step": tokens,
-                       "parallelism": "tp%d" % world, "overlap_allreduce": bool(lay.overlap_comm and world > 1), "l2": "inputs larger than L2: weights %d MB per layer and rank + %d MB per activation tensor, no flush"
-                             % ((2 * (2 * cfg.hidden * cfg.heads * cfg.head_dim + 2 * cfg.hidden * cfg.kv_heads * cfg.head_dim
-                                      + 3 * cfg.hidden * cfg.ffn) // world) >> 20, (tokens * cfg.hidden * 2) >> 20),
-                       "allocator": "torch default" if args.no_caching_allocator else "b200 caching allocator (pluggable)"},
+            "config": workload_config(args.workload, cfg, batch, seq, n_layers, world),
+            "setup": {"overlap_allreduce": bool(lay.overlap_comm and world > 1),
+                      "allocator": "torch default" if args.no_caching_allocator else "b200 caching allocator (pluggable)"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": ids_host.numel() * 8,
                     "d2h_bytes_per_step": tokens * cfg.hidden * 2,
                     "note": "result copied back on a pool stream, overlapping the next step's compute"
@@ -539,6 +696,9 @@ def main():
             "ops": ops,
             "variants": variants,
             "decode": decode,
+            "parity": parity if not args.no_parity else None,
+            "checks": checks,
+            "op_sweep": op_sweep,
             "gemm_status": diopi.gemm_status(),
         }
         if world == 1 and not args.no_cpu_baseline:
@@ -546,16 +706,70 @@ def main():
         else:
             line["cpu_baseline"] = None
         print(json.dumps(line), flush=True)
+    failed = [k for k, v in parity.items() if not (v.get("ok", True) and v.get("all_ranks_ok", True))]
+    if checks is not None and not checks.get("all_ranks_ok", True):
+        failed.append("checks")
     if tp_group is not None:
         barrier()
         tp_group.close()
     if dist is not None:
         dist.destroy_process_group()
+    if failed:
+        sys.stderr.write("bench.py: rank %d: checks failed: %s\n" % (rank, ", ".join(failed)))
+        sys.exit(1)
 
 
-def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ranks, peaks):
+def run_op_sweep(diopi, ctx, device, stream, peaks):
+    """The op sweep of the workload description: each memory-bound operator on bf16 [T, 4096], T in {1, 64, 1024, 16384,
+    65536} (cases, buffers and algorithmic bytes as in opsweep.py: enough distinct buffer sets per case to exceed L2,
+    CUDA events on the launching stream). T >= 16384 is reported as GB/s and fraction of the measured copy bandwidth, the
+    small T as latency: `us` with one host call per launch (the host's per-call cost bounds it), `us_graph` with the same
+    launches replayed from one CUDA graph (the device's own pace), the latter also as GB/s."""
+    import opsweep
+    from dipu_b200 import devapis
+    out = {"unit": "GB/s of algorithmic bytes; frac = of %s HBM copy bandwidth (%.0f GB/s)" % (peaks["source"], peaks["hbm_gbs"]), "ops": {}}
+
+    def graph_time(fns, iters):
+        devapis.graphBeginCapture(stream.cuda_stream)
+        try:
+            for i in range(iters):
+                fns[i % len(fns)]()
+        finally:
+            graph = devapis.graphEndCapture(stream.cuda_stream)
+        devapis.graphLaunch(graph, stream.cuda_stream)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        devapis.graphLaunch(graph, stream.cuda_stream)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        devapis.graphDestroy(graph)
+        return e0.elapsed_time(e1) / iters
+
+    for op in ("rmsnorm", "layernorm", "softmax", "rope", "silu_mul", "cast_up", "cast_down", "embedding", "add"):
+        rec = {}
+        for t in (1, 64, 1024, 16384, 65536):
+            fns, alg = opsweep.mem_case(op, t, diopi, ctx, device)
+            ms = opsweep.time_cases(fns, 30 if t >= 16384 else 100, stream)
+            gbs = alg / (ms * 1e-3) / 1e9
+            if t >= 16384:
+                rec["T=%d" % t] = {"us": round(ms * 1e3, 2), "gbs": round(gbs, 1), "frac": round(gbs / peaks["hbm_gbs"], 4)}
+            else:
+                ms_g = graph_time(fns, 100)
+                rec["T=%d" % t] = {"us": round(ms * 1e3, 2), "us_graph": round(ms_g * 1e3, 2), "gbs_graph": round(alg / (ms_g * 1e-3) / 1e9, 1),
+                                   "frac_graph": round(alg / (ms_g * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)}
+            del fns
+            ctx.release_workspace()
+        out["ops"][op] = rec
+    torch.cuda.synchronize()
+    return out
+
+
+def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ranks, peaks, rank=0, dist=None, host_w=None, check=False):
     """7B-shaped layer in decode: batch 64, one new token per sequence, bf16 KV cache of length 4096 per sequence."""
     b, length = 64, 4096
+    n_check = 4  # sequences whose output is compared with the CPU oracle
+    outs = {}
     g = torch.Generator(device=device)
     g.manual_seed(SEED + 3)
     kc = torch.randn((b, lay.kv_heads, length, cfg.head_dim), generator=g, device=device, dtype=torch.float32).to(dtype)
@@ -572,9 +786,10 @@ def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ra
     e1.record(stream)
     barrier()
     ms_eager = max_over_ranks(e0.elapsed_time(e1)) / steps
+    outs["eager"] = lay.decode(xd, kc, vc, length - 1, ctx)[:n_check].clone()
     # the same step captured once into a CUDA graph and replayed: one launch per step instead of ~30 host-side calls
     from dipu_b200 import devapis
-    replay, _ = lay.capture_decode(xd, kc, vc, length - 1, ctx)
+    replay, out_g = lay.capture_decode(xd, kc, vc, length - 1, ctx)
     for _ in range(5):
         replay()
     barrier()
@@ -585,12 +800,13 @@ def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ra
     e1.record(stream)
     barrier()
     ms = max_over_ranks(e0.elapsed_time(e1)) / steps
+    outs["graph"] = out_g[:n_check].clone()
     devapis.graphDestroy(replay.graph)
     # variant: the attention core through the fused operator (K and V read once, no score tensor), again graph-replayed
     lay.fused_attention = True
     for _ in range(3):
         lay.decode(xd, kc, vc, length - 1, ctx)
-    replay, _ = lay.capture_decode(xd, kc, vc, length - 1, ctx)
+    replay, out_g = lay.capture_decode(xd, kc, vc, length - 1, ctx)
     for _ in range(5):
         replay()
     barrier()
@@ -600,6 +816,7 @@ def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ra
     e1.record(stream)
     barrier()
     ms_fused = max_over_ranks(e0.elapsed_time(e1)) / steps
+    outs["fused_attention"] = out_g[:n_check].clone()
     devapis.graphDestroy(replay.graph)
     # tensor parallel: the two 512 KiB partial sums per step reduced by ONE kernel over peer memory on the compute stream
     # (b200_dicl_peer_all_reduce) instead of ncclAllReduce on the communication stream; fused attention stays on
@@ -615,7 +832,7 @@ def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ra
         barrier()
         for _ in range(3):
             lay.decode(xd, kc, vc, length - 1, ctx)
-        replay, _ = lay.capture_decode(xd, kc, vc, length - 1, ctx)
+        replay, out_g = lay.capture_decode(xd, kc, vc, length - 1, ctx)
         for _ in range(5):
             replay()
         barrier()
@@ -625,16 +842,34 @@ def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ra
         e1.record(stream)
         barrier()
         ms_peer = max_over_ranks(e0.elapsed_time(e1)) / steps
+        outs["fused_attention_peer_all_reduce"] = out_g[:n_check].clone()
         devapis.graphDestroy(replay.graph)
         assert lay.tp_group.peer.status() == 0, "a peer all-reduce wait timed out"
         lay.tp_group.peer.close()
         lay.tp_group.peer = None
     lay.fused_attention = False
+    parity = None
+    if check:
+        # four of the 64 sequences against the CPU oracle: op-by-op variants within 5e-3 of the op-by-op bf16 CPU path, the
+        # fused-attention variants within 5e-3 of the oracle's fused form, everything within 1e-2 of fp32
+        torch.cuda.synchronize()
+        refs = decode_oracle_refs(cfg, host_w, xd[:n_check], kc[:n_check], vc[:n_check], length - 1, world, rank, dist)
+        parity = {}
+        for name, got in outs.items():
+            form = "bf16_stepwise_fused" if name.startswith("fused") else "bf16_stepwise"
+            sw = bench_checks.REL_STEPWISE if world == 1 else bench_checks.REL_LOOSE  # TP: partial sums travel rounded to bf16
+            entry = bench_checks.parity_entry(got, {form: (refs[form], sw), "fp32": (refs["fp32"], bench_checks.fp32_bound(refs[form], refs["fp32"]))})
+            entry["all_ranks_ok"] = all_ranks(entry["ok"], dist)
+            parity[name] = entry
+        parity["ok"] = all(v["ok"] for v in parity.values())
+        parity["all_ranks_ok"] = all(v["all_ranks_ok"] for k, v in parity.items() if isinstance(v, dict))
+        parity["rows_checked"] = "%d of the %d sequences" % (n_check, b)
     d = cfg.head_dim
     weight_bytes = 2 * (cfg.hidden * lay.heads * d * 2 + cfg.hidden * lay.kv_heads * d * 2 + 3 * cfg.hidden * lay.ffn)
     kv_bytes = 2 * 2 * b * lay.kv_heads * length * d
     gbs = (weight_bytes + kv_bytes) / (ms * 1e-3) / 1e9
-    return {"workload": "decode, batch 64, KV length 4096, tp%d, step replayed from a CUDA graph" % world, "tokens_per_s": b / (ms * 1e-3),
+    return {"parity": parity,
+            "workload": "decode, batch 64, KV length 4096, tp%d, step replayed from a CUDA graph" % world, "tokens_per_s": b / (ms * 1e-3),
             "ms_per_step": ms, "eager_tokens_per_s": b / (ms_eager * 1e-3), "eager_ms_per_step": ms_eager,
             "algorithmic_bytes_per_step_per_gpu": weight_bytes + kv_bytes, "achieved_gbs": round(gbs, 1),
             "hbm_frac": round(gbs / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],

@@ -531,14 +531,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 template <typename T, int SPLIT>
 cudaError_t launch_prefill_split(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, const AttnParams& p,
                                  int grid, cudaStream_t stream) {
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<T, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
-        if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
-    }
+    if (cudaError_t e = tc_ensure_smem_attr(reinterpret_cast<const void*>(attn_prefill_kernel<T, SPLIT>), kAttnSmem); e != cudaSuccess) return e;
     attn_prefill_kernel<T, SPLIT><<<grid, 128 + 256 * SPLIT, kAttnSmem, stream>>>(mq, mk, mv, mo, p);
     return cudaPeekAtLastError();
 }

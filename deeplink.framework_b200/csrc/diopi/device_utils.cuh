@@ -94,6 +94,51 @@ __device__ __forceinline__ void st16_stream(T* p, const Vec16<T>& r) {
     __stcs(reinterpret_cast<uint4*>(p), *reinterpret_cast<const uint4*>(&r));
 }
 
+// ---- packed pairs -------------------------------------------------------------------------------
+// The row kernels work on two elements at a time: a 32-bit word of two 2-byte elements is widened to a float2 (bf16: a
+// shift and a mask), the arithmetic uses the two-wide fp32 instructions of sm_100 (fma / mul / add .f32x2: one issue slot
+// for two results), and a float2 is narrowed back with one cvt.rn.<t>x2.f32. Same values as the element-wise forms.
+template <typename T> struct Pair;
+template <> struct Pair<bf16> {
+    static __device__ __forceinline__ float2 widen(uint32_t w) { return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u)); }
+    static __device__ __forceinline__ uint32_t narrow(float2 v) {
+        uint32_t r;
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(v.y), "f"(v.x));
+        return r;
+    }
+};
+template <> struct Pair<fp16> {
+    static __device__ __forceinline__ float2 widen(uint32_t w) { return __half22float2(*reinterpret_cast<const __half2*>(&w)); }
+    static __device__ __forceinline__ uint32_t narrow(float2 v) {
+        uint32_t r;
+        asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(v.y), "f"(v.x));
+        return r;
+    }
+};
+
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tadd.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+__device__ __forceinline__ uint32_t word(const uint4& v, int j) { return j == 0 ? v.x : (j == 1 ? v.y : (j == 2 ? v.z : v.w)); }
+__device__ __forceinline__ uint4 ld16_stream_raw(const void* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ void st16_stream_raw(void* p, const uint4& v) { __stcs(reinterpret_cast<uint4*>(p), v); }
+
 // ---- reductions --------------------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

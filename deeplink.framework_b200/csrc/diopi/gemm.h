@@ -47,6 +47,10 @@ bool tc_encode_map(::CUtensorMap_st* map, diopiDtype_t dtype, const void* base, 
 bool tc_encode_map4(::CUtensorMap_st* map, diopiDtype_t dtype, const void* base, const int64_t dims[4], const int64_t pitch_elems[3], int box1,
                     int box2);
 uint32_t* tc_status_word();
+// Raises a kernel's dynamic shared-memory limit once per (device, kernel); safe to call from concurrent threads.
+cudaError_t tc_ensure_smem_attr(const void* kernel, int bytes);
+// Limit of the pushing kernel's wait for the permission to overwrite a peer's staging slot (0 = the default of 2 s).
+void gemm_tc2_set_push_wait_limit_ns(unsigned long long ns);
 
 // Fused attention (attention.cu).
 bool attention_prefill_applies(const TensorView& q, const TensorView& k, const TensorView& v, const TensorView& out);

@@ -22,6 +22,8 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <set>
+#include <utility>
 
 #include "gemm.h"
 #include "diopi/functions_b200.h"
@@ -591,8 +593,22 @@ bool encode_map(CUtensorMap* map, diopiDtype_t dtype, const void* base, int64_t 
     return r == CUDA_SUCCESS;
 }
 
+cudaError_t ensure_smem_attr(const void* kernel, int bytes) {
+    static std::mutex mu;
+    static std::set<std::pair<int, const void*>> done;
+    int dev = 0;
+    if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> lock(mu);
+    const auto key = std::make_pair(dev, kernel);
+    if (done.count(key) != 0) return cudaSuccess;
+    if (cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); e != cudaSuccess) return e;
+    done.insert(key);
+    return cudaSuccess;
+}
+
 uint32_t* status_word() {
-    // one status word per device, allocated on first use and kept for the life of the process
+    // one status word per device, kept for the life of the process: allocated by diopiB200Init when the host announces the
+    // device, or on first use when it did not
     static uint32_t* words[64] = {nullptr};
     static std::mutex mu;
     int dev = 0;
@@ -610,14 +626,7 @@ uint32_t* status_word() {
 template <int BN, typename TOut, int EPI>
 cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const TcParams& p, int grid, cudaStream_t stream) {
     using Cfg = TileCfg<BN, EPI>;
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, TOut, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-        if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
-    }
+    if (cudaError_t e = ensure_smem_attr(reinterpret_cast<const void*>(gemm_tc_kernel<BN, TOut, EPI>), Cfg::kSmemBytes); e != cudaSuccess) return e;
     gemm_tc_kernel<BN, TOut, EPI><<<grid, 64 + 32 * EPI, Cfg::kSmemBytes, stream>>>(ma, mb, mc, p);
     return cudaPeekAtLastError();
 }
@@ -638,14 +647,7 @@ cudaError_t launch_tc_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, c
 template <int BN, typename TOut>
 cudaError_t launch_splitk(const CUtensorMap& ma, const CUtensorMap& mb, const SplitKParams& p, int grid, cudaStream_t stream) {
     using Cfg = TileCfg<BN>;
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_splitk_kernel<BN, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-        if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
-    }
+    if (cudaError_t e = ensure_smem_attr(reinterpret_cast<const void*>(gemm_tc_splitk_kernel<BN, TOut>), Cfg::kSmemBytes); e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid));
     cfg.blockDim = dim3(kThreads);
@@ -715,6 +717,7 @@ bool tc_encode_map4(::CUtensorMap_st* map, diopiDtype_t dtype, const void* base,
     return r == CUDA_SUCCESS;
 }
 uint32_t* tc_status_word() { return status_word(); }
+cudaError_t tc_ensure_smem_attr(const void* kernel, int bytes) { return ensure_smem_attr(kernel, bytes); }
 
 bool gemm_tc_eligible(const GemmProblem& g) {
     if (!(g.ab_dtype == diopi_dtype_bfloat16 || g.ab_dtype == diopi_dtype_float16)) return false;
@@ -839,6 +842,18 @@ diopiError_t gemm_tc_launch(const GemmProblem& g, cudaStream_t stream) {
 }
 
 }  // namespace b200
+
+// One-time set-up on the current device, for hosts that want it out of the first operator call: allocates and clears the
+// status word of the tensor-core kernels (a cudaMalloc and a synchronising memset that otherwise happen inside the first
+// product). Call it where the host initialises a device (DIPU: initializeVendor / the first setDevice); calling it again is
+// free. Operators work without it.
+extern "C" DIOPI_API diopiError_t diopiB200Init(void) {
+    using namespace b200;
+    B200_CHECK(status_word() != nullptr, "diopiB200Init: could not allocate the kernels' status word on the current device");
+    return diopiSuccess;
+}
+
+extern "C" DIOPI_API void diopiB200SetPushWaitLimitNs(unsigned long long ns) { b200::gemm_tc2_set_push_wait_limit_ns(ns); }
 
 // Status of the tensor-core kernels on the current device: 0 = no wait has ever timed out.
 // Synchronises the device. Not part of DIOPI; exported for tests and health checks.

@@ -71,6 +71,7 @@ struct PushParams {
     uint32_t epoch;       // this call's number: written into the ready flags
     uint32_t prev_epoch;  // number of the last call that used this slot (0: none); its reduction must be over before we write
     int rows_per_rank;    // M / nranks, a multiple of 128
+    unsigned long long wait_ns;  // limit of the wait for the permission to overwrite a peer's staging slot
 };
 
 __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
@@ -84,13 +85,13 @@ __device__ __forceinline__ void st_peer16(void* p, const uint4& v) {
 }
 
 // Bounded wait until *flag >= target (flags only grow); raises the CTA's abort flag on time-out.
-__device__ __forceinline__ bool flag_wait_ge(const uint32_t* flag, uint32_t target, volatile uint32_t* abort_flag) {
+__device__ __forceinline__ bool flag_wait_ge(const uint32_t* flag, uint32_t target, volatile uint32_t* abort_flag, unsigned long long limit_ns) {
     if (static_cast<int32_t>(ld_acquire_sys_u32(flag) - target) >= 0) return true;
     const unsigned long long t0 = globaltimer_ns();
     while (true) {
         if (static_cast<int32_t>(ld_acquire_sys_u32(flag) - target) >= 0) return true;
         if (*abort_flag != 0) return false;
-        if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        if (globaltimer_ns() - t0 > limit_ns) {
             *abort_flag = 1;
             return false;
         }
@@ -269,7 +270,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (((checked >> owner) & 1u) == 0) {
                     int fine = 1;
                     if (lane == 0) {
-                        fine = flag_wait_ge(q.space.flags[q.space.rank] + b200_peer_sfree_off(&q.space, q.slot, owner), q.prev_epoch, abort_flag) ? 1 : 0;
+                        fine = flag_wait_ge(q.space.flags[q.space.rank] + b200_peer_sfree_off(&q.space, q.slot, owner), q.prev_epoch, abort_flag, q.wait_ns) ? 1 : 0;
                     }
                     fine = __shfl_sync(0xffffffffu, fine, 0);
                     if (!fine) { ok = false; break; }
@@ -386,14 +387,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 template <typename TOut, bool PUSH>
 cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const PairParams& p, const PushParams& q, int grid,
                         cudaStream_t stream) {
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<TOut, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
-    }
+    if (cudaError_t e = tc_ensure_smem_attr(reinterpret_cast<const void*>(gemm_tc_pair_kernel<TOut, PUSH>), kSmemBytes); e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid));
     cfg.blockDim = dim3(kThreads);
@@ -426,11 +420,13 @@ diopiError_t pair_setup(const GemmProblem& g, CUtensorMap* ma, CUtensorMap* mb, 
     p.M = static_cast<int>(g.M); p.N = static_cast<int>(g.N); p.K = static_cast<int>(g.K); p.batch = static_cast<int>(g.batch);
     p.m_pairs = static_cast<int>((g.M + 2 * BM - 1) / (2 * BM));
     p.n_blocks = static_cast<int>((g.N + BN - 1) / BN);
-    p.group_m = kGroupM;
-    if (const char* e = std::getenv("B200_GEMM_GROUP_M")) {
-        const int v = std::atoi(e);
-        if (v >= 1 && v <= 64) p.group_m = v;
-    }
+    // read once: the environment is not consulted on the launch path
+    static const int group_m_env = [] {
+        const char* e = std::getenv("B200_GEMM_GROUP_M");
+        const int v = e != nullptr ? std::atoi(e) : 0;
+        return (v >= 1 && v <= 64) ? v : 0;
+    }();
+    p.group_m = group_m_env != 0 ? group_m_env : kGroupM;
     p.m_rot = 0;
     p.k_blocks = static_cast<int>((g.K + BK - 1) / BK);
     p.ldc = g.c_sm; p.stride_cb = g.c_sb; p.C = g.C;
@@ -445,6 +441,8 @@ diopiError_t pair_setup(const GemmProblem& g, CUtensorMap* ma, CUtensorMap* mb, 
     B200_CHECK(p.status != nullptr, "gemm: could not allocate the kernel status word");
     return diopiSuccess;
 }
+
+unsigned long long g_push_wait_ns = kWaitLimitNs;
 
 int pair_grid(const PairParams& p) {
     const int64_t total = static_cast<int64_t>(p.batch) * p.m_pairs * p.n_blocks;
@@ -486,6 +484,8 @@ diopiError_t gemm_tc2_launch(const GemmProblem& g, cudaStream_t stream) {
     return diopiSuccess;
 }
 
+void gemm_tc2_set_push_wait_limit_ns(unsigned long long ns) { g_push_wait_ns = ns == 0 ? kWaitLimitNs : ns; }
+
 // This rank's partial product, pushed tile by tile into the staging slots of the ranks that own the rows. g.C is not used.
 diopiError_t gemm_tc2_push_launch(const GemmProblem& g, const b200PeerSpace& space, int slot, uint32_t epoch, uint32_t prev_epoch,
                                   cudaStream_t stream) {
@@ -512,6 +512,7 @@ diopiError_t gemm_tc2_push_launch(const GemmProblem& g, const b200PeerSpace& spa
     q.epoch = epoch;
     q.prev_epoch = prev_epoch;
     q.rows_per_rank = static_cast<int>(g.M / n);
+    q.wait_ns = g_push_wait_ns;
     const int grid = pair_grid(p);
     cudaError_t e = g.ab_dtype == diopi_dtype_bfloat16 ? launch_pair<bf16, true>(ma, mb, ma, p, q, grid, stream)
                                                        : launch_pair<fp16, true>(ma, mb, ma, p, q, grid, stream);

@@ -9,8 +9,12 @@
 // Arithmetic follows the reference's CPU restatements: half-split pairs (i, i + dim/2)
 // (dicp/dicp/vendor/AscendGraph/ext_ops.py:24-33) and interleaved pairs (2i, 2i+1), i.e. complex multiplication
 // (dicp/test/model/llama/model.py:58-69). Products and sums are formed in fp32 and rounded once.
+#include <cstdlib>
+
 #include "copy.h"
 #include "device_utils.cuh"
+#include "gemm.h"
+#include "row_pipe.cuh"
 
 namespace b200 {
 namespace {
@@ -66,17 +70,86 @@ __global__ void __launch_bounds__(256) rope_half_kernel(const T* x, T* out, cons
 #pragma unroll
             for (int e = 0; e < 8; ++e) { c1[e] = c0[e]; s1[e] = s0[e]; }
         }
-        Vec16<T> o0, o1;
+        // pairs of elements: widened words, two-wide fp32 arithmetic, one narrowing conversion per pair
+        const uint4 ra = *reinterpret_cast<const uint4*>(&x0), rb = *reinterpret_cast<const uint4*>(&x1);
+        uint32_t o0[4], o1[4];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const float a = to_f32(x0.v[e]), b = to_f32(x1.v[e]);
-            o0.v[e] = from_f32<T>(a * c0[e] - b * (sin_sign * s0[e]));
-            o1.v[e] = from_f32<T>(b * c1[e] + a * (sin_sign * s1[e]));
+        for (int j = 0; j < 4; ++j) {
+            const float2 va = Pair<T>::widen(word(ra, j)), vb = Pair<T>::widen(word(rb, j));
+            const float2 cc0 = make_float2(c0[2 * j], c0[2 * j + 1]), ns0 = make_float2(-sin_sign * s0[2 * j], -sin_sign * s0[2 * j + 1]);
+            const float2 cc1 = make_float2(c1[2 * j], c1[2 * j + 1]), ss1 = make_float2(sin_sign * s1[2 * j], sin_sign * s1[2 * j + 1]);
+            o0[j] = Pair<T>::narrow(fma2(vb, ns0, mul2(va, cc0)));   // a * cos - b * sin
+            o1[j] = Pair<T>::narrow(fma2(va, ss1, mul2(vb, cc1)));   // b * cos + a * sin
         }
         T* po = out + th * dim + c * 8;
-        st16_stream(po, o0);
-        st16_stream(po + half, o1);
+        st16_stream_raw(po, make_uint4(o0[0], o0[1], o0[2], o0[3]));
+        st16_stream_raw(po + half, make_uint4(o1[0], o1[1], o1[2], o1[3]));
     }
+}
+
+// Half-split layout with [rows, dim/2] tables, pipelined (row_pipe.cuh): a "row" of a warp's ring is one token, heads * dim
+// elements. Lane l rotates the 8 pairs of items l, l + 32, ... where item = (head, chunk of 8 pairs); 32 is a multiple of the
+// chunks per head, so a lane's chunk is the same for all its items: it reads the 8 + 8 angles of that chunk once per token,
+// and reads them for its NEXT token before it rotates the current one (the table row comes from L2; its latency would
+// otherwise sit in every iteration).
+template <typename T, typename TC>
+__global__ void __launch_bounds__(512) rope_wpipe_kernel(const T* x, T* out, const TC* __restrict__ cos_t, const TC* __restrict__ sin_t, int64_t tokens,
+                                                         int heads, int dim, int64_t table_rows, float sin_sign, uint32_t* status) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ rowpipe::Ctl ctl;
+    const int half = dim / 2;
+    const int chunks = half / 8;
+    const int items = heads * chunks;
+    const uint32_t row_bytes = static_cast<uint32_t>(heads) * dim * 2;
+    rowpipe::init_ctl(&ctl, blockDim.x >> 5);
+    rowpipe::WarpRing ring = rowpipe::make_ring(&ctl, smem, x, row_bytes, tokens);
+    ring.start();
+    const int lane = threadIdx.x & 31;
+    const int c = lane % chunks;
+    float cn[8], sn[8];
+    int64_t r = ring.first;
+    if (r < tokens) {
+        load_angles8<TC>(cos_t + (r % table_rows) * half + c * 8, cn);
+        load_angles8<TC>(sin_t + (r % table_rows) * half + c * 8, sn);
+    }
+    bool failed = false;
+    int k = 0;
+    for (; r < tokens; r += ring.stride, ++k) {
+        float2 cc[4], ss[4], ns[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            cc[j] = make_float2(cn[2 * j], cn[2 * j + 1]);
+            ss[j] = make_float2(sin_sign * sn[2 * j], sin_sign * sn[2 * j + 1]);
+            ns[j] = make_float2(-ss[j].x, -ss[j].y);
+        }
+        const int64_t rn = r + ring.stride;
+        if (rn < tokens) {
+            load_angles8<TC>(cos_t + (rn % table_rows) * half + c * 8, cn);
+            load_angles8<TC>(sin_t + (rn % table_rows) * half + c * 8, sn);
+        }
+        const unsigned char* slot = ring.acquire(k);
+        if (slot == nullptr) {
+            failed = true;
+            break;
+        }
+        char* orow = reinterpret_cast<char*>(out) + r * static_cast<int64_t>(row_bytes);
+#pragma unroll 2
+        for (int it = lane; it < items; it += 32) {
+            const size_t off = (static_cast<size_t>(it / chunks) * dim + static_cast<size_t>(c) * 8) * 2;
+            const uint4 a = rowpipe::lds16(slot + off), b = rowpipe::lds16(slot + off + static_cast<size_t>(half) * 2);
+            uint32_t o0[4], o1[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 va = Pair<T>::widen(word(a, j)), vb = Pair<T>::widen(word(b, j));
+                o0[j] = Pair<T>::narrow(fma2(vb, ns[j], mul2(va, cc[j])));   // a * cos - b * sin
+                o1[j] = Pair<T>::narrow(fma2(va, ss[j], mul2(vb, cc[j])));   // b * cos + a * sin
+            }
+            st16_stream_raw(orow + off, make_uint4(o0[0], o0[1], o0[2], o0[3]));
+            st16_stream_raw(orow + off + static_cast<size_t>(half) * 2, make_uint4(o1[0], o1[1], o1[2], o1[3]));
+        }
+        ring.release(k);
+    }
+    if (failed) rowpipe::leave_after_timeout(status);
 }
 
 // General variant: any float dtype for x and the tables, either layout, one pair per thread.
@@ -143,6 +216,44 @@ extern "C" diopiError_t diopiRotaryEmbedding(diopiContextHandle_t ctx, diopiTens
     const float sign = conj ? -1.f : 1.f;
     const bool two_byte = vx.dtype == diopi_dtype_bfloat16 || vx.dtype == diopi_dtype_float16;
     const bool tables_ok = (vc.dtype == vx.dtype || vc.dtype == diopi_dtype_float32) && vc.aligned(16) && vs.aligned(16) && (table_cols % 8 == 0);
+    // pipelined kernel: one token (heads * dim elements, 1 to 16 KiB) per ring slot, [rows, dim/2] tables
+    const int64_t token_bytes = heads * dim * 2;
+    const int64_t chunks64 = dim / 16;
+    static const bool pipe_off = std::getenv("B200_NO_ROW_PIPE") != nullptr;
+    if (!pipe_off && !interleaved && two_byte && (dim / 2) % 8 == 0 && table_cols == dim / 2 && vx.aligned(16) && vo.aligned(16) && tables_ok && token_bytes >= 1024 &&
+        token_bytes <= 16384 && chunks64 >= 1 && 32 % chunks64 == 0 && tokens < 0x7fffffffLL) {
+        const int warps = rowpipe::warps_for(token_bytes, 0);
+        const unsigned smem = static_cast<unsigned>(static_cast<int64_t>(warps) * rowpipe::kStages * token_bytes);
+        uint32_t* status = tc_status_word();
+        bool launched = false;
+#define LAUNCH_ROPE_PIPE(T, TC)                                                                                                             \
+    do {                                                                                                                                   \
+        const void* kfn = reinterpret_cast<const void*>(rope_wpipe_kernel<T, TC>);                                                          \
+        int occ = 0;                                                                                                                       \
+        if (warps >= 4 && tc_ensure_smem_attr(kfn, static_cast<int>(smem)) == cudaSuccess &&                                               \
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, rope_wpipe_kernel<T, TC>, warps * 32, smem) == cudaSuccess && occ >= 1) {   \
+            int64_t ctas = static_cast<int64_t>(sm_count()) * occ;                                                                         \
+            const int64_t need = (tokens + warps - 1) / warps;                                                                             \
+            if (ctas > need) ctas = need;                                                                                                  \
+            rope_wpipe_kernel<T, TC><<<static_cast<unsigned>(ctas), warps * 32, smem, stream>>>(                                            \
+                static_cast<const T*>(vx.data), static_cast<T*>(vo.data), static_cast<const TC*>(vc.data), static_cast<const TC*>(vs.data), \
+                tokens, (int)heads, (int)dim, table_rows, sign, status);                                                                  \
+            launched = true;                                                                                                               \
+        } else {                                                                                                                           \
+            (void)cudaGetLastError();                                                                                                      \
+        }                                                                                                                                  \
+    } while (0)
+        if (vx.dtype == diopi_dtype_bfloat16) {
+            if (vc.dtype == diopi_dtype_float32) LAUNCH_ROPE_PIPE(bf16, float); else LAUNCH_ROPE_PIPE(bf16, bf16);
+        } else {
+            if (vc.dtype == diopi_dtype_float32) LAUNCH_ROPE_PIPE(fp16, float); else LAUNCH_ROPE_PIPE(fp16, fp16);
+        }
+#undef LAUNCH_ROPE_PIPE
+        if (launched) {
+            B200_LAUNCH_CHECK("diopiRotaryEmbedding");
+            return diopiSuccess;
+        }
+    }
     if (!interleaved && two_byte && (dim / 2) % 8 == 0 && dim / 16 <= 256 && vx.aligned(16) && vo.aligned(16) && tables_ok) {
         const int64_t rows_per_block = 256 / (dim / 16);
         int64_t blocks = (tokens * heads + rows_per_block - 1) / rows_per_block;

@@ -497,7 +497,7 @@ __device__ __forceinline__ float uniform24(uint32_t r) { return static_cast<floa
 __global__ void __launch_bounds__(256) multinomial_kernel(const void* probs, diopiDtype_t dt, int64_t n, int64_t num_samples, int64_t* out,
                                                           uint64_t seed, uint64_t offset) {
     __shared__ float prefix[257];
-    __shared__ float warp_tot[8];
+    __shared__ float runs[256];
     const int64_t row = blockIdx.x;
     const int64_t base = row * n;
     const int64_t len = (n + 255) / 256;
@@ -505,19 +505,20 @@ __global__ void __launch_bounds__(256) multinomial_kernel(const void* probs, dio
     const int64_t j1 = j0 + len < n ? j0 + len : n;
     float run = 0.f;
     for (int64_t j = j0; j < j1; ++j) run += fmaxf(load_as<float>(probs, dt, base + j), 0.f);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    float incl = run;
-    for (int off = 1; off < 32; off <<= 1) {
-        const float t = __shfl_up_sync(0xffffffffu, incl, off);
-        if (lane >= off) incl += t;
-    }
-    if (lane == 31) warp_tot[warp] = incl;
+    runs[threadIdx.x] = run;
     __syncthreads();
-    float before = 0.f;
-    for (int w = 0; w < warp; ++w) before += warp_tot[w];
-    before += incl - run;
-    prefix[threadIdx.x] = before;
-    if (threadIdx.x == 255) prefix[256] = before + run;
+    // One thread adds the 256 run totals in order: prefix[t + 1] = prefix[t] + run[t] exactly, so the boundaries never
+    // decrease, a run without positive weight owns the EMPTY interval, and the intervals tile [0, total) - none of which a
+    // tree-shaped scan guarantees in floating point (a masked-out run could own a one-ulp interval and return a token of
+    // weight zero).
+    if (threadIdx.x == 0) {
+        float c = 0.f;
+        for (int t = 0; t < 256; ++t) {
+            prefix[t] = c;
+            c += runs[t];
+        }
+        prefix[256] = c;
+    }
     __syncthreads();
     const float total = prefix[256];
     const Philox gen(seed);
@@ -525,7 +526,7 @@ __global__ void __launch_bounds__(256) multinomial_kernel(const void* probs, dio
         const uint4 r = gen(static_cast<uint64_t>(row * num_samples + sidx), offset);
         float x = uniform24(r.x) * total;
         if (!(x < total)) x = 0.f;  // only when total is 0, inf or NaN: degenerate rows yield index of the first weight
-        // the owner: x in [prefix[t], prefix[t+1]) - the intervals tile [0, total) exactly because they come from one scan
+        // the owner: x in [prefix[t], prefix[t+1]), non-empty only for a run that holds positive weight
         if (x >= prefix[threadIdx.x] && x < prefix[threadIdx.x + 1]) {
             float c = prefix[threadIdx.x];
             int64_t pick = -1, last_pos = -1;
@@ -538,7 +539,7 @@ __global__ void __launch_bounds__(256) multinomial_kernel(const void* probs, dio
                     break;
                 }
             }
-            if (pick < 0) pick = last_pos >= 0 ? last_pos : j0;  // rounding at the end of the run
+            if (pick < 0) pick = last_pos >= 0 ? last_pos : j0;  // rounding at the end of the run: its last positive weight
             out[row * num_samples + sidx] = pick;
         } else if (total <= 0.f && threadIdx.x == 0) {
             out[row * num_samples + sidx] = 0;

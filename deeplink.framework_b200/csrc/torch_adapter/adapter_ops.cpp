@@ -399,9 +399,26 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, c10::SymInt, c10::Sym
     at::Tensor lse = at::empty({b, h, sq}, query.options().dtype(at::kFloat));
     const at::Tensor q = query.transpose(1, 2), k = key.transpose(1, 2), v = value.transpose(1, 2);
     CallContext ctx(out);
-    Wrapped wq(q), wk(k), wv(v), wo(out), wl(lse);
     const double sc = scale.has_value() ? *scale : 1.0 / std::sqrt(static_cast<double>(d));
-    DIPU_B200_CALL(diopiMultiHeadAttention(&ctx, &wq, &wk, &wv, dropout_p, is_causal, return_debug_mask, sc, &wo, &wl, nullptr, nullptr));
+    auto attend = [&](const at::Tensor& qv, const at::Tensor& kv, const at::Tensor& vv, const at::Tensor& ov, const at::Tensor& lv, bool causal) {
+        Wrapped wq(qv), wk(kv), wv(vv), wo(ov), wl(lv);
+        DIPU_B200_CALL(diopiMultiHeadAttention(&ctx, &wq, &wk, &wv, dropout_p, causal, return_debug_mask, sc, &wo, &wl, nullptr, nullptr));
+    };
+    const int64_t skv = key.size(2);
+    if (is_causal && sq != skv) {
+        // torch aligns the causal mask to the FIRST key (key j is visible to query i iff j <= i, the lower triangle of
+        // ones(L, S)); diopiMultiHeadAttention aligns it to the LAST key (j <= i + S - L). The two agree on square problems, so
+        // a rectangular one is served as square ones: fewer queries than keys see only the first L keys; with more queries than
+        // keys the first S queries form a square causal problem and the remaining ones see every key.
+        if (sq < skv) {
+            attend(q, k.narrow(1, 0, sq), v.narrow(1, 0, sq), out, lse, true);
+        } else {
+            attend(q.narrow(1, 0, skv), k, v, out.narrow(1, 0, skv), lse.narrow(2, 0, skv), true);
+            attend(q.narrow(1, skv, sq - skv), k, v, out.narrow(1, skv, sq - skv), lse.narrow(2, skv, sq - skv), false);
+        }
+    } else {
+        attend(q, k, v, out, lse, is_causal);
+    }
     const at::Tensor none = at::empty({0}, query.options().dtype(at::kLong));
     return {out.transpose(1, 2), lse, none, none, c10::SymInt(sq), c10::SymInt(key.size(2)), none, none, at::empty({0}, query.options())};
 }

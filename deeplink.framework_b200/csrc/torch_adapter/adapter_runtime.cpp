@@ -192,12 +192,64 @@ void device_copy(const at::Tensor& src, const at::Tensor& dst) {
     DIPU_B200_CALL(diopiCopyInp(&ctx, &s, &d));
 }
 
+// Between two devices the bytes travel dense and in one dtype through the copy engines (memCopyD2DAsync with the SOURCE device
+// current and on the source's stream, as DIPU does it, ops/DIPUCopy.hpp:142-148,371-372); a strided or differently typed side
+// is relayed through a dense tensor on its own device first / afterwards. The two devices' streams are ordered by events:
+// the source stream waits for what the destination stream has enqueued on the landing buffer, and the destination stream
+// waits for the transfer.
+void peer_copy(const at::Tensor& src, const at::Tensor& dst) {
+    const int sdev = src.device().index(), ddev = dst.device().index();
+    at::Tensor dense = src;
+    if (!src.is_contiguous()) {
+        const c10::DeviceGuard guard(src.device());
+        dense = at::empty(src.sizes(), src.options());
+        device_copy(src, dense);
+    }
+    const bool direct = dst.is_contiguous() && dst.scalar_type() == dense.scalar_type();
+    at::Tensor landing = dst;
+    if (!direct) {
+        const c10::DeviceGuard guard(dst.device());
+        landing = at::empty(dst.sizes(), dst.options().dtype(dense.scalar_type()));
+    }
+    b200Stream_t sstream = nullptr, dstream = nullptr;
+    b200Event_t ev = nullptr;
+    {
+        const c10::DeviceGuard guard(dst.device());
+        dstream = current_stream(ddev);
+        VENDOR_CHECK(b200_event_from_pool(&ev));
+        VENDOR_CHECK(b200_record_event(ev, dstream));
+    }
+    {
+        const c10::DeviceGuard guard(src.device());
+        sstream = current_stream(sdev);
+        VENDOR_CHECK(b200_stream_wait_event(sstream, ev));
+        VENDOR_CHECK(b200_event_to_pool(ev));
+        VENDOR_CHECK(b200_memcpy_d2d_async(sstream, dense.nbytes(), ddev, landing.data_ptr(), sdev, dense.data_ptr()));
+        VENDOR_CHECK(b200_event_from_pool(&ev));
+        VENDOR_CHECK(b200_record_event(ev, sstream));
+        // the landing buffer belongs to the destination's stream for the allocator; it is also in use on the source's
+        if (landing.has_storage() && landing.storage().data() != nullptr) (void)b200_cache_record_stream(landing.storage().mutable_data(), sstream);
+    }
+    {
+        const c10::DeviceGuard guard(dst.device());
+        VENDOR_CHECK(b200_stream_wait_event(dstream, ev));
+        VENDOR_CHECK(b200_event_to_pool(ev));
+        if (dense.has_storage() && dense.storage().data() != nullptr) (void)b200_cache_record_stream(dense.storage().mutable_data(), dstream);
+        if (!direct) device_copy(landing, dst);
+    }
+}
+
 at::Tensor copy_from(const at::Tensor& self, const at::Tensor& dst, bool non_blocking) {
     if (dst.numel() == 0) return dst;
     TORCH_CHECK(self.numel() == dst.numel() || self.sizes() != dst.sizes(), "copy_: size mismatch");
     if (!self.is_cpu() && !dst.is_cpu()) {
-        const c10::DeviceGuard guard(dst.device());
-        device_copy(self.sizes() == dst.sizes() ? self : self.expand(dst.sizes()), dst);
+        const at::Tensor src = self.sizes() == dst.sizes() ? self : self.expand(dst.sizes());
+        if (src.device() == dst.device()) {
+            const c10::DeviceGuard guard(dst.device());
+            device_copy(src, dst);
+            return dst;
+        }
+        peer_copy(src, dst);
         return dst;
     }
     ++stats().host_copies;

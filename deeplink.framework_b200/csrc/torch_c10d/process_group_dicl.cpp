@@ -8,9 +8,16 @@
 // from the pool after it has waited for the producing stream, an event recorded behind them, and Work::wait() making the
 // CURRENT stream wait for that event (no host block unless DICL_BLOCKING_WAIT=1). Tensors used on the communication stream
 // are reported to the caching allocator (record_stream), as the reference does with dipu::recordStream.
+// With DICL_BLOCKING_WAIT=1 the host polls the event and gives up with "Operation timed out!" after the time-out of the
+// wait() call, or of the process group when the call names none (reference: WorkDICL::synchronize,
+// ProcessGroupDICL.cpp:154-167, opTimeout_ at ProcessGroupDICL.h:40-41) - the path's failure detection for a peer that never
+// arrives. gather / scatter are built from point-to-point transfers plus one device-to-device copy for the root's own part,
+// the way the reference's proxy builds them (runtime/devproxy/diclproxy.cpp:61-105).
+#include <chrono>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <thread>
 
 #include <torch/csrc/distributed/c10d/Backend.hpp>
 #include <torch/csrc/distributed/c10d/Store.hpp>
@@ -46,10 +53,20 @@ void check_tensor(const at::Tensor& t, const char* what) {
     TORCH_CHECK(t.is_contiguous(), "dicl: ", what, " must be contiguous");
 }
 
+// Host-side wait of the blocking mode: polls `done` until it holds, throws once `limit` has passed (0 = no limit).
+template <typename Pred>
+void blocking_wait(Pred done, std::chrono::milliseconds limit) {
+    const auto t0 = std::chrono::steady_clock::now();
+    while (!done()) {
+        if (limit.count() > 0 && std::chrono::steady_clock::now() - t0 > limit) TORCH_CHECK(false, "Operation timed out!");
+        std::this_thread::sleep_for(std::chrono::microseconds(200));
+    }
+}
+
 class WorkDICL final : public c10d::Work {
   public:
-    WorkDICL(int rank, c10d::OpType op, int device, b200Comm_t comm, bool blocking)
-        : c10d::Work(rank, op), device_(device), comm_(comm), blocking_(blocking) {
+    WorkDICL(int rank, c10d::OpType op, int device, b200Comm_t comm, bool blocking, std::chrono::milliseconds op_timeout)
+        : c10d::Work(rank, op), device_(device), comm_(comm), blocking_(blocking), op_timeout_(op_timeout) {
         DICL_CHECK(b200_event_from_pool(&event_));
     }
     ~WorkDICL() override {
@@ -64,9 +81,9 @@ class WorkDICL final : public c10d::Work {
     }
     bool isSuccess() const override { return b200_dicl_get_comm_async_error(comm_) == B200_SUCCESS; }
     // The stream the caller computes on waits for the collective; the host only blocks when asked to.
-    bool wait(std::chrono::milliseconds /*timeout*/) override {
+    bool wait(std::chrono::milliseconds timeout) override {
         DICL_CHECK(b200_stream_wait_event(current_stream(device_), event_));
-        if (blocking_) DICL_CHECK(b200_wait_event(event_));
+        if (blocking_) blocking_wait([this] { return isCompleted(); }, timeout == kNoTimeout ? op_timeout_ : timeout);
         return true;
     }
     void synchronize() override { wait(std::chrono::milliseconds(0)); }
@@ -78,12 +95,14 @@ class WorkDICL final : public c10d::Work {
     int device_;
     b200Comm_t comm_;
     bool blocking_;
+    std::chrono::milliseconds op_timeout_;
     b200Event_t event_ = nullptr;
 };
 
 class ProcessGroupDICL final : public c10d::Backend {
   public:
-    ProcessGroupDICL(c10::intrusive_ptr<c10d::Store> store, int rank, int size) : c10d::Backend(rank, size), store_(std::move(store)) {
+    ProcessGroupDICL(c10::intrusive_ptr<c10d::Store> store, int rank, int size, std::chrono::milliseconds op_timeout)
+        : c10d::Backend(rank, size), store_(std::move(store)), op_timeout_(op_timeout) {
         const char* b = std::getenv("DICL_BLOCKING_WAIT");
         blocking_ = b != nullptr && std::strcmp(b, "1") == 0;
     }
@@ -191,6 +210,72 @@ class ProcessGroupDICL final : public c10d::Backend {
         });
     }
 
+    // root receives one part from every other rank and copies its own part; the others send theirs
+    c10::intrusive_ptr<c10d::Work> gather(std::vector<std::vector<at::Tensor>>& outputs, std::vector<at::Tensor>& inputs,
+                                          const c10d::GatherOptions& opts) override {
+        TORCH_CHECK(inputs.size() == 1, "dicl: gather expects one input tensor");
+        at::Tensor input = inputs[0];
+        check_tensor(input, "gather input");
+        const int root = static_cast<int>(opts.rootRank), me = getRank(), n = getSize();
+        std::vector<at::Tensor> outs;
+        if (me == root) {
+            TORCH_CHECK(outputs.size() == 1 && static_cast<int>(outputs[0].size()) == n, "dicl: gather expects world_size outputs on the root");
+            outs = outputs[0];
+            for (const at::Tensor& o : outs) {
+                check_tensor(o, "gather output");
+                TORCH_CHECK(o.numel() == input.numel() && o.scalar_type() == input.scalar_type(), "dicl: gather outputs must match the input");
+            }
+        } else {
+            TORCH_CHECK(outputs.empty() || outputs[0].empty(), "dicl: gather outputs are only given on the root");
+        }
+        const size_t count = static_cast<size_t>(input.numel());
+        const int dt = to_diopi_dtype(input.scalar_type());
+        return run(c10d::OpType::GATHER, {input}, outs, [&](b200Comm_t comm, b200Stream_t s) {
+            if (me != root) {
+                DICL_CHECK(b200_dicl_send(input.data_ptr(), count, dt, root, comm, s));
+                return;
+            }
+            const int dev = input.device().index();
+            for (int r = 0; r < n; ++r) {
+                if (r == root) DICL_CHECK(b200_memcpy_d2d_async(s, count * input.element_size(), dev, outs[r].data_ptr(), dev, input.data_ptr()));
+                else DICL_CHECK(b200_dicl_recv(outs[r].data_ptr(), count, dt, r, comm, s));
+            }
+        });
+    }
+
+    // root sends one part to every other rank and copies its own part; the others receive theirs
+    c10::intrusive_ptr<c10d::Work> scatter(std::vector<at::Tensor>& outputs, std::vector<std::vector<at::Tensor>>& inputs,
+                                           const c10d::ScatterOptions& opts) override {
+        TORCH_CHECK(outputs.size() == 1, "dicl: scatter expects one output tensor");
+        at::Tensor output = outputs[0];
+        check_tensor(output, "scatter output");
+        const int root = static_cast<int>(opts.rootRank), me = getRank(), n = getSize();
+        std::vector<at::Tensor> ins;
+        if (me == root) {
+            TORCH_CHECK(inputs.size() == 1 && static_cast<int>(inputs[0].size()) == n, "dicl: scatter expects world_size inputs on the root");
+            ins = inputs[0];
+            for (const at::Tensor& t : ins) {
+                check_tensor(t, "scatter input");
+                TORCH_CHECK(t.numel() == output.numel() && t.scalar_type() == output.scalar_type(), "dicl: scatter inputs must match the output");
+            }
+        } else {
+            TORCH_CHECK(inputs.empty() || inputs[0].empty(), "dicl: scatter inputs are only given on the root");
+        }
+        const size_t count = static_cast<size_t>(output.numel());
+        const int dt = to_diopi_dtype(output.scalar_type());
+        return run(c10d::OpType::SCATTER, ins, {output}, [&](b200Comm_t comm, b200Stream_t s) {
+            if (me != root) {
+                DICL_CHECK(b200_dicl_recv(output.data_ptr(), count, dt, root, comm, s));
+                return;
+            }
+            const int dev = output.device().index();
+            for (int r = 0; r < n; ++r) {
+                if (r == root) DICL_CHECK(b200_memcpy_d2d_async(s, count * output.element_size(), dev, output.data_ptr(), dev, ins[r].data_ptr()));
+                else DICL_CHECK(b200_dicl_send(ins[r].data_ptr(), count, dt, r, comm, s));
+            }
+        });
+    }
+
     c10::intrusive_ptr<c10d::Work> barrier(const c10d::BarrierOptions&) override {
         int dev = 0;
         DICL_CHECK(b200_current_device(&dev));
@@ -241,7 +326,7 @@ class ProcessGroupDICL final : public c10d::Backend {
         DICL_CHECK(b200_record_event(pre, current_stream(device)));
         DICL_CHECK(b200_stream_wait_event(comm_stream_, pre));
         DICL_CHECK(b200_event_to_pool(pre));
-        auto work = c10::make_intrusive<WorkDICL>(getRank(), op, device, comm_, blocking_);
+        auto work = c10::make_intrusive<WorkDICL>(getRank(), op, device, comm_, blocking_, op_timeout_);
         fn(comm_, comm_stream_);
         for (const auto* list : {&inputs, &outputs}) {
             for (const at::Tensor& t : *list) {
@@ -260,11 +345,25 @@ class ProcessGroupDICL final : public c10d::Backend {
     int device_ = -1;
     int comm_counter_ = 0;
     bool blocking_ = false;
+    std::chrono::milliseconds op_timeout_;
 };
 
 c10::intrusive_ptr<c10d::Backend> create_process_group_dicl(const c10::intrusive_ptr<c10d::Store>& store, int rank, int size,
-                                                            const std::chrono::duration<float>& /*timeout*/) {
-    return c10::make_intrusive<ProcessGroupDICL>(store, rank, size);
+                                                            const std::chrono::duration<float>& timeout) {
+    return c10::make_intrusive<ProcessGroupDICL>(store, rank, size, std::chrono::duration_cast<std::chrono::milliseconds>(timeout));
+}
+
+// Host-only exercise of the blocking wait: a condition that becomes true after `ready_after_ms` (never, when negative),
+// waited for with a limit of `timeout_ms`. Returns the milliseconds waited; throws "Operation timed out!" like Work::wait.
+double blocking_wait_selftest(int64_t timeout_ms, int64_t ready_after_ms) {
+    const auto t0 = std::chrono::steady_clock::now();
+    blocking_wait(
+        [&] {
+            if (ready_after_ms < 0) return false;
+            return std::chrono::steady_clock::now() - t0 >= std::chrono::milliseconds(ready_after_ms);
+        },
+        std::chrono::milliseconds(timeout_ms));
+    return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
 }
 
 }  // namespace
@@ -273,4 +372,5 @@ c10::intrusive_ptr<c10d::Backend> create_process_group_dicl(const c10::intrusive
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "c10d backend 'dicl' over the B200 DICL communicator";
     m.def("create_process_group_dicl", &dipu_b200::create_process_group_dicl, py::arg("store"), py::arg("rank"), py::arg("size"), py::arg("timeout"));
+    m.def("blocking_wait_selftest", &dipu_b200::blocking_wait_selftest, py::arg("timeout_ms"), py::arg("ready_after_ms"));
 }

@@ -102,7 +102,8 @@ _SIGS = {
     "b200_dicl_get_comm_name": [ctypes.c_char_p, _sz, _vp],
     "b200_dicl_comm_rank": [_vp, ctypes.POINTER(_i), ctypes.POINTER(_i)],
     "b200_dicl_peer_reduce_create": [ctypes.POINTER(_vp), _vp, _sz, _vp], "b200_dicl_peer_all_reduce": [_vp, _vp, _vp, _sz, _i, _vp],
-    "b200_dicl_peer_reduce_destroy": [_vp],
+    "b200_dicl_peer_reduce_destroy": [_vp], "b200_dicl_peer_reduce_reset_status": [_vp],
+    "b200_dicl_peer_space_check": [_vp], "b200_dicl_peer_space_reset_status": [_vp],
     "b200_dicl_peer_space_create": [ctypes.POINTER(_vp), _vp, _sz, _i, _vp],
     "b200_dicl_peer_space_create_emulated": [ctypes.POINTER(_vp), _i, _sz, _i],
     "b200_dicl_peer_space_describe": [_vp, _vp],
@@ -121,6 +122,8 @@ _v.b200_dicl_peer_reduce_status.argtypes = [_vp]
 _v.b200_dicl_peer_reduce_status.restype = ctypes.c_int
 _v.b200_dicl_peer_space_status.argtypes = [_vp]
 _v.b200_dicl_peer_space_status.restype = ctypes.c_int
+_v.b200_dicl_peer_set_wait_limit_ns.argtypes = [ctypes.c_ulonglong]
+_v.b200_dicl_peer_set_wait_limit_ns.restype = None
 _v.b200_dicl_peer_space_result.argtypes = [_vp, _i]
 _v.b200_dicl_peer_space_result.restype = _vp
 _v.b200_expandable_ptr.argtypes = [_vp]
@@ -134,7 +137,7 @@ _v.b200_is_stream_empty.argtypes = [_vp]
 _v.b200_is_pinned_ptr.argtypes = [_vp]
 
 C_SYMBOLS = sorted(list(_SIGS) + ["b200_stream_not_null", "b200_is_stream_empty", "b200_is_pinned_ptr", "b200_dicl_unique_id_bytes",
-                                  "b200_last_error", "b200_dicl_peer_reduce_status", "b200_dicl_peer_space_status", "b200_dicl_peer_space_result", "b200_expandable_ptr", "b200_expandable_size", "b200_expandable_mapped_bytes"])
+                                  "b200_last_error", "b200_dicl_peer_set_wait_limit_ns", "b200_dicl_peer_reduce_status", "b200_dicl_peer_space_status", "b200_dicl_peer_space_result", "b200_expandable_ptr", "b200_expandable_size", "b200_expandable_mapped_bytes"])
 
 
 def last_error():
@@ -532,10 +535,21 @@ class PeerAllReduce:
     def status(self):
         return _v.b200_dicl_peer_reduce_status(self.handle)
 
+    def reset_status(self):
+        _check(_v.b200_dicl_peer_reduce_reset_status(self.handle), "peer reduce reset status")
+
     def close(self):
+        """Collective: every rank drains its device and meets the others in a one-element all-reduce inside the call,
+        so no peer can still be reading this rank's staging or writing its flags when they are freed."""
         if self.handle:
             _check(_v.b200_dicl_peer_reduce_destroy(self.handle), "peer reduce destroy")
             self.handle = None
+
+
+def setPeerWaitLimitNs(ns):
+    """Limit of every flag wait in the peer-memory kernels (PeerAllReduce, PeerSpace.reduce_gather) launched from now on;
+    0 restores the default of one second."""
+    _v.b200_dicl_peer_set_wait_limit_ns(int(ns))
 
 
 class _DeviceBytes:
@@ -608,6 +622,14 @@ class PeerSpace:
 
     def status(self):
         return _v.b200_dicl_peer_space_status(self.handle)
+
+    def check(self):
+        """diclResult_t.DICL_SUCCESS while every bounded wait completed, DICL_ERR_UNDEF once one ran out (the failed call's
+        result is incomplete on every rank; last_error() says so). OR the value over the ranks before trusting a result."""
+        return diclResult_t.DICL_SUCCESS if _v.b200_dicl_peer_space_check(self.handle) == 0 else diclResult_t.DICL_ERR_UNDEF
+
+    def reset_status(self):
+        _check(_v.b200_dicl_peer_space_reset_status(self.handle), "peer space reset status")
 
     def close(self):
         if self.handle:

@@ -65,6 +65,21 @@ _lib.diopiGetLastErrorString.restype = ctypes.c_char_p
 _lib.diopiGetVendorName.restype = ctypes.c_char_p
 _lib.diopiGetImplVersion.restype = ctypes.c_char_p
 _lib.diopiB200GemmStatus.restype = ctypes.c_int
+_lib.diopiB200Init.restype = ctypes.c_int
+_lib.diopiB200SetPushWaitLimitNs.argtypes = [ctypes.c_ulonglong]
+_lib.diopiB200SetPushWaitLimitNs.restype = None
+_INITIALISED = set()
+
+
+def init_device(device):
+    """What a host does where it initialises a device: the library's one-time set-up (diopiB200Init) with that device
+    current, so that the first operator call neither allocates nor synchronises."""
+    if device in _INITIALISED or not torch.cuda.is_available():
+        return
+    with torch.cuda.device(device):
+        if _lib.diopiB200Init() != 0:
+            raise DiopiError("diopiB200Init failed: %s" % _lib.diopiGetLastErrorString().decode())
+    _INITIALISED.add(device)
 
 
 class Handle:
@@ -120,6 +135,7 @@ class Context:
             device = torch.cuda.current_device() if torch.cuda.is_available() else 0
         self.stream = int(stream)
         self.device = int(device)
+        init_device(self.device)
         self.ptr = _host.minihostMakeContext(ctypes.c_void_p(self.stream), self.device)
 
     def release_workspace(self):

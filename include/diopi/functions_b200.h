@@ -15,6 +15,11 @@ extern "C" {
  * device-side wait has ever timed out, 1 afterwards, -1 if it cannot be read. Synchronises the device. */
 DIOPI_API int diopiB200GemmStatus(void);
 
+/* No counterpart in the reference. One-time set-up on the current device for hosts that want it out of the first operator
+ * call: allocates and clears the tensor-core kernels' status word (otherwise a cudaMalloc and a synchronising memset inside
+ * the first matrix product on that device). Call it where the host initialises a device; repeated calls are free. */
+DIOPI_API diopiError_t diopiB200Init(void);
+
 /* No counterpart in the reference.
  *
  * Matrix product for callers that are not allowed to allocate device memory at the moment of the call: code running
@@ -33,8 +38,9 @@ DIOPI_API int diopiB200GemmStatus(void);
  * dimension outside [1, 2^31), is rejected with diopiErrorOccurred and a message, never served by another path.
  * The scratch need of this kernel does not grow with the problem, so the static block is always enough.
  *
- * The first call on a device looks up the block's device address and sets a kernel attribute; make that first call
- * before any stream capture. Every call clears the status word on `stream` before the kernel runs and all calls share
+ * The first call on a device looks up the block's device address, and the first call of each tile variant on a device (the
+ * variant depends on the problem's shape) raises that kernel's shared-memory limit; make a first call of every shape you
+ * will use before any stream capture. Every call clears the status word on `stream` before the kernel runs and all calls share
  * the block, which keeps the last call's value: calls that overlap on the GPU (different streams) race on it, so
  * serialise them. diopiB200NoAllocStatus() reads the word back (synchronises). */
 DIOPI_API diopiError_t diopiB200MmNoAlloc(diopiStreamHandle_t stream, void* out, const void* mat1, const void* mat2, int64_t m, int64_t n,
@@ -52,9 +58,11 @@ DIOPI_API int diopiB200NoAllocStatus(void);
  * distributes the result. `epoch` must grow from call to call and be the same on every rank; `prev_epoch` is the epoch of
  * the previous call that used `slot` (0 if none): the kernel does not overwrite a peer's slot before that call's
  * reduction has finished there (bounded wait; a time-out raises diopiB200GemmStatus).
- * M must be a multiple of 256 and of 128 * nranks, N a multiple of 256, M * N elements must fit a slot. */
+ * M must be a multiple of 256 and of 128 * nranks, N a multiple of 256, M * N elements must fit a slot.
+ * diopiB200SetPushWaitLimitNs: limit of that wait for the launches that follow (0 = the default of 2 s). */
 DIOPI_API diopiError_t diopiB200MmPush(diopiContextHandle_t ctx, diopiConstTensorHandle_t input, diopiConstTensorHandle_t mat2,
                                        const b200PeerSpace* space, int32_t slot, uint32_t epoch, uint32_t prev_epoch);
+DIOPI_API void diopiB200SetPushWaitLimitNs(unsigned long long ns);
 
 #ifdef __cplusplus
 }

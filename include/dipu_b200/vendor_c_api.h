@@ -218,11 +218,17 @@ B200_API b200Status_t b200_dicl_comm_rank(b200Comm_t comm, int* rank, int* nrank
  * create is collective over `comm` (handles are exchanged with the communicator's all-gather); every rank must call
  * all_reduce with the same count, in the same order; float16 / bfloat16 / float32, buffers 16-byte aligned, byte count a
  * multiple of 16 and at most max_bytes; in place (send == recv) is allowed. The sum is formed in fp32 in rank order, so
- * every rank gets bit-identical results. status: 0, or 1 once a wait for a peer ran into its 1 s limit. */
+ * every rank gets bit-identical results. status: 0, or 1 once a wait for a peer ran into its limit (1 s by default).
+ * destroy is collective too: each rank drains its device and meets the others in a one-element all-reduce before its
+ * blocks are unmapped and freed (a peer may still be reading this rank's staging when this rank's own kernel has ended).
+ * set_wait_limit_ns: limit of every flag wait in the peer-memory kernels this process launches afterwards (all-reduce and
+ * reduce-gather); 0 restores the default of one second. reset_status clears a reported time-out. */
 B200_API b200Status_t b200_dicl_peer_reduce_create(void** handle, b200Comm_t comm, size_t max_bytes, b200Stream_t stream);
 B200_API b200Status_t b200_dicl_peer_all_reduce(void* handle, const void* send, void* recv, size_t count, int dtype, b200Stream_t stream);
 B200_API int b200_dicl_peer_reduce_status(void* handle);
+B200_API b200Status_t b200_dicl_peer_reduce_reset_status(void* handle);
 B200_API b200Status_t b200_dicl_peer_reduce_destroy(void* handle);
+B200_API void b200_dicl_peer_set_wait_limit_ns(unsigned long long ns);
 
 /* Peer space: staging slots, result slots and flags every rank of a communicator allocates and maps from all peers
  * (layout: dipu_b200/peer_space.h), for a row-parallel linear whose all-reduce is fused into the compute kernels: the
@@ -240,7 +246,10 @@ B200_API b200Status_t b200_dicl_peer_reduce_destroy(void* handle);
  *   reduce_gather     every rank, same order, same (slot, epoch, rows, cols); epoch as passed to the products. float16 (8)
  *                     or bfloat16 (12); residual [rows, cols] dense, 16-byte aligned, or NULL (only the owned rows are read).
  *                     All calls on one handle must be enqueued on one stream. final_wait = 1 except under emulation.
- *   status            0, or 1 once a wait for a peer ran into its 1 s limit. */
+ *   status            0, or 1 once a wait for a peer ran into its limit (1 s by default). A CTA whose wait ran out does not
+ *                     announce completion, so the peers' final waits run out as well: every rank reports the failure.
+ *   check             B200_SUCCESS, or B200_ERR_TIMEOUT with a message once status is non-zero (DICL_ERR_UNDEF one level up).
+ *   reset_status      clears a reported time-out; the next calls on the space work as before. */
 B200_API b200Status_t b200_dicl_peer_space_create(void** handle, b200Comm_t comm, size_t slot_bytes, int slots, b200Stream_t stream);
 B200_API b200Status_t b200_dicl_peer_space_create_emulated(void** handles, int nranks, size_t slot_bytes, int slots);
 B200_API b200Status_t b200_dicl_peer_space_describe(void* handle, b200PeerSpace* out);
@@ -248,6 +257,8 @@ B200_API void* b200_dicl_peer_space_result(void* handle, int slot);
 B200_API b200Status_t b200_dicl_peer_reduce_gather(void* handle, int slot, uint32_t epoch, const void* residual, int64_t rows, int64_t cols,
                                                    int dtype, int final_wait, b200Stream_t stream);
 B200_API int b200_dicl_peer_space_status(void* handle);
+B200_API b200Status_t b200_dicl_peer_space_check(void* handle);
+B200_API b200Status_t b200_dicl_peer_space_reset_status(void* handle);
 B200_API b200Status_t b200_dicl_peer_space_destroy(void* handle);
 
 #ifdef __cplusplus

@@ -1,7 +1,7 @@
 """Per-op sweep on one GPU: achieved HBM GB/s of the memory-bound DIOPI ops and TFLOP/s of the dense contractions.
 
-    python deeplink.framework_b200/opsweep.py                       # the whole sweep, one JSON line per case
-    python deeplink.framework_b200/opsweep.py --ops rmsnorm --tokens 16384 --iters 5    # one case (e.g. under a profiler)
+    python opsweep.py                       # the whole sweep, one JSON line per case
+    python opsweep.py --ops rmsnorm --tokens 16384 --iters 5    # one case (e.g. under a profiler)
 
 Memory-bound ops run on bf16 [T, 4096] tensors, T in {1, 64, 1024, 16384, 65536}, values N(0,1); the embedding gathers
 int64 ids uniform in [0, 32000) from a [32000, 4096] bf16 table. Each case cycles through enough distinct buffer sets that
@@ -18,7 +18,7 @@ import sys
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-ROOT = os.path.dirname(HERE)
+ROOT = HERE
 sys.path.insert(0, ROOT)
 
 H = 4096

@@ -64,6 +64,22 @@ def main():
             dist.recv(r_buf, prv)
             dist.send(s_buf, nxt)
         assert torch.equal(r_buf.cpu(), torch.full((32,), float(prv)))
+        # gather to / scatter from the last rank (the reference proxy's construction: point-to-point + one device copy)
+        root = world - 1
+        mine = torch.full((6,), float(rank) + 0.5, device=dev)
+        outs = [torch.empty((6,), device=dev) for _ in range(world)] if rank == root else None
+        dist.gather(mine, outs, dst=root)
+        if rank == root:
+            assert all(torch.equal(outs[r].cpu(), torch.full((6,), r + 0.5)) for r in range(world))
+        ins = [torch.arange(r * 6, r * 6 + 6, dtype=torch.float32).to(dev) for r in range(world)] if rank == root else None
+        got = torch.empty((6,), device=dev)
+        dist.scatter(got, ins, src=root)
+        assert torch.equal(got.cpu(), torch.arange(rank * 6, rank * 6 + 6).float())
+        # bool tensors stay [True, False, True] under SUM / MAX / MIN (they travel as uint8)
+        for op in (dist.ReduceOp.SUM, dist.ReduceOp.MAX, dist.ReduceOp.MIN):
+            b = torch.tensor([True, False, True]).to(dev)
+            dist.all_reduce(b, op=op)
+            assert torch.equal(b.cpu(), torch.tensor([True, False, True])), op
         w = dist.all_reduce(x, async_op=True)     # async form: a Work whose wait() orders the compute stream behind it
         w.wait()
         assert w.is_success()

@@ -41,108 +41,40 @@ def main():
     def sync():
         dv.syncStream(stream)
 
-    # all-reduce SUM / MAX / MIN on float, and on bool / uint8 which must stay [True, False, True]
-    x = torch.full((1000,), float(rank + 1), device=dev)
-    dv.diclAllReduce(x.data_ptr(), x.data_ptr(), x.numel(), DT[x.dtype], dv.ReduceOp.SUM, comm, stream)
-    sync()
-    assert torch.equal(x.cpu(), torch.full((1000,), float(world * (world + 1) // 2)))
-    for op, want in ((dv.ReduceOp.MAX, float(world)), (dv.ReduceOp.MIN, 1.0), (dv.ReduceOp.AVG, (world + 1) / 2.0)):
-        y = torch.full((257,), float(rank + 1), device=dev, dtype=torch.bfloat16)
-        dv.diclAllReduce(y.data_ptr(), y.data_ptr(), y.numel(), DT[y.dtype], op, comm, stream)
-        sync()
-        assert torch.equal(y.float().cpu(), torch.full((257,), want))
-    for dtype in (torch.bool, torch.uint8):
-        for op in (dv.ReduceOp.SUM, dv.ReduceOp.MAX, dv.ReduceOp.MIN):
-            b = torch.tensor([True, False, True], device=dev).to(dtype)
-            dv.diclAllReduce(b.data_ptr(), b.data_ptr(), 3, DT[dtype], op, comm, stream)
-            sync()
-            want = torch.tensor([True, False, True]).to(dtype)
-            if dtype == torch.uint8 and op == dv.ReduceOp.SUM:
-                want = want * world
-            assert torch.equal(b.cpu(), want), (dtype, op, b)
-    # broadcast from the last rank
-    z = torch.arange(16, device=dev, dtype=torch.int64) * (rank + 1)
-    dv.diclBroadcast(z.data_ptr(), z.data_ptr(), 16, DT[z.dtype], world - 1, comm, stream)
-    sync()
-    assert torch.equal(z.cpu(), torch.arange(16) * world)
-    # all-gather
-    g_in = torch.full((4,), float(rank), device=dev)
-    g_out = torch.empty((world * 4,), device=dev)
-    dv.diclAllGather(g_in.data_ptr(), g_out.data_ptr(), 4, DT[g_in.dtype], comm, stream)
-    sync()
-    assert torch.equal(g_out.cpu(), torch.arange(world).float().repeat_interleave(4))
-    # reduce to rank 0
-    r_in = torch.full((8,), float(rank + 1), device=dev)
-    r_out = torch.zeros((8,), device=dev)
-    dv.diclReduce(r_in.data_ptr(), r_out.data_ptr(), 8, DT[r_in.dtype], dv.ReduceOp.SUM, 0, comm, stream)
-    sync()
-    if rank == 0:
-        assert torch.equal(r_out.cpu(), torch.full((8,), float(world * (world + 1) // 2)))
-    # reduce-scatter
-    rs_in = torch.arange(world * 4, device=dev, dtype=torch.float32)
-    rs_out = torch.empty((4,), device=dev)
-    dv.diclReduceScatter(rs_in.data_ptr(), rs_out.data_ptr(), 4, DT[rs_in.dtype], dv.ReduceOp.SUM, comm, stream)
-    sync()
-    assert torch.equal(rs_out.cpu(), torch.arange(rank * 4, rank * 4 + 4).float() * world)
-    # send / recv around a ring
-    s_buf = torch.full((32,), float(rank), device=dev)
-    r_buf = torch.empty((32,), device=dev)
-    nxt, prv = (rank + 1) % world, (rank - 1) % world
-    if rank % 2 == 0:
-        dv.diclSend(s_buf.data_ptr(), 32, DT[s_buf.dtype], nxt, comm, stream)
-        dv.diclRecv(r_buf.data_ptr(), 32, DT[r_buf.dtype], prv, comm, stream)
-    else:
-        dv.diclRecv(r_buf.data_ptr(), 32, DT[r_buf.dtype], prv, comm, stream)
-        dv.diclSend(s_buf.data_ptr(), 32, DT[s_buf.dtype], nxt, comm, stream)
-    sync()
-    assert torch.equal(r_buf.cpu(), torch.full((32,), float(prv)))
-    # all-to-all, equal and unequal splits
-    a_in = (torch.arange(world * 2, device=dev, dtype=torch.float32) + 100 * rank)
-    a_out = torch.empty_like(a_in)
-    dv.diclAllToAllEqualSplit(a_in.data_ptr(), a_out.data_ptr(), 2, DT[a_in.dtype], comm, stream)
-    sync()
-    want = torch.cat([torch.arange(rank * 2, rank * 2 + 2).float() + 100 * r for r in range(world)])
-    assert torch.equal(a_out.cpu(), want)
-    send_counts = [r + 1 for r in range(world)]           # rank sends r+1 elements to rank r
-    recv_counts = [rank + 1 for _ in range(world)]        # and receives rank+1 from everyone
-    sd = [sum(send_counts[:r]) for r in range(world)]
-    rd = [sum(recv_counts[:r]) for r in range(world)]
-    u_in = torch.full((sum(send_counts),), float(rank), device=dev)
-    u_out = torch.empty((sum(recv_counts),), device=dev)
-    dv.diclAllToAllUnequalSplit(u_in.data_ptr(), send_counts, sd, u_out.data_ptr(), recv_counts, rd, DT[u_in.dtype], comm, stream)
-    sync()
-    assert torch.equal(u_out.cpu(), torch.arange(world).float().repeat_interleave(rank + 1))
+    # every collective of the interface against closed-form values (the cases bench.py also runs at its world size)
+    import bench_checks
+    counter = [0]
+
+    def exchange(obj, src):
+        """A small object from rank `src` to everybody, through files in the rendezvous directory."""
+        counter[0] += 1
+        box = os.path.join(rdv, "x%d" % counter[0])
+        if rank == src:
+            with open(box + ".tmp", "wb") as f:
+                f.write(obj)
+            os.rename(box + ".tmp", box)
+            return obj
+        t0 = time.time()
+        while not os.path.exists(box):
+            if time.time() - t0 > 60:
+                raise SystemExit("rank %d: nothing from rank %d after 60 s" % (rank, src))
+            time.sleep(0.02)
+        return open(box, "rb").read()
+
+    res = bench_checks.collective_checks(dv, DT, comm, stream, rank, world, dev, exchange)
+    bad = [k for k, v in res.items() if v is False] + [("%s: %s" % (k, v)) for k, v in res.items() if k.endswith("_error")]
+    assert not bad, bad
+    expected = {"all_reduce_sum", "all_reduce_max_min_avg", "all_reduce_bool_uint8", "broadcast", "all_gather", "reduce", "reduce_scatter",
+                "send_recv_ring", "gather_scatter_by_send_recv", "all_to_all_equal", "all_to_all_unequal", "comm_name_and_error_state"}
+    if world >= 4:
+        expected.add("sub_group")
+    assert expected <= set(res), sorted(expected - set(res))
 
     # all-reduce in one kernel over peer memory: closed-form sums, bit-identical on every rank, in place and out of place,
-    # sizes from one vector to the handle's limit, 40 calls back to back (the call counter lives on the device)
+    # sizes from one vector to the handle's limit, back-to-back calls (the call counter lives on the device)
     assert dv.diclCommRank(comm) == (rank, world)
-    peer = dv.PeerAllReduce(comm, 1 << 20, stream)
-    sync()
-    for dtype, n in ((torch.bfloat16, 8), (torch.bfloat16, 64 * 4096), (torch.float16, 4096 + 8), (torch.float32, 1 << 18), (torch.bfloat16, 1 << 19)):
-        src = (torch.arange(n, device=dev, dtype=torch.float32) % 13 + rank).to(dtype)
-        out = torch.empty_like(src)
-        peer.all_reduce(src.data_ptr(), out.data_ptr(), n, DT[dtype], stream)
-        sync()
-        want = sum((torch.arange(n, dtype=torch.float32) % 13 + r).to(dtype).float() for r in range(world)).to(dtype)
-        assert torch.equal(out.cpu(), want), (dtype, n)
-        peer.all_reduce(src.data_ptr(), src.data_ptr(), n, DT[dtype], stream)   # in place
-        sync()
-        assert torch.equal(src.cpu(), want), (dtype, n, "in place")
-    acc = torch.full((4096,), 1.0, device=dev, dtype=torch.float32)
-    for _ in range(40):
-        peer.all_reduce(acc.data_ptr(), acc.data_ptr(), 4096, DT[acc.dtype], stream)
-        dv.diclAllReduce(acc.data_ptr(), acc.data_ptr(), 1, DT[acc.dtype], dv.ReduceOp.MAX, comm, stream)  # a library collective in between
-    sync()
-    assert peer.status() == 0
-    assert torch.equal(acc.cpu(), torch.full((4096,), float(world) ** 40)) or world > 2
-    # a message above the limit is refused on the host
-    try:
-        big = torch.zeros((1 << 20) // 2 + 8, device=dev, dtype=torch.bfloat16)
-        peer.all_reduce(big.data_ptr(), big.data_ptr(), big.numel(), DT[big.dtype], stream)
-        raise SystemExit("oversized peer all-reduce was not refused")
-    except dv.VendorError:
-        pass
-    peer.close()
+    res = bench_checks.peer_all_reduce_checks(dv, DT, comm, stream, rank, world, dev)
+    assert res.get("peer_all_reduce") and res.get("peer_all_reduce_back_to_back") and res.get("peer_all_reduce_refuses_oversize"), res
 
     # tensor-parallel layer: every rank's output equals the unsharded CPU oracle
     from oracle import llama_cpu
@@ -175,7 +107,7 @@ def main():
     assert grp.peer.status() == 0
     err = (y.cpu() - ref).abs().max().item()
     assert err <= 2e-4, ("peer reduce", err)
-    grp.peer.close()
+    grp.peer.close()   # collective: the ranks meet inside before anything is unmapped
     grp.peer = None
 
     # row-parallel linears with the all-reduce and the residual add fused into the kernels: tiles pushed to the owners of

@@ -112,3 +112,39 @@ def test_fused_row_linear_rejects_bad_shapes(pkg, ctx):
     finally:
         for sp in spaces:
             sp.close()
+
+
+def test_reduce_gather_wait_runs_out_and_is_reported(pkg, ctx):
+    """A rank whose product is never enqueued: with the wait limit set to a few milliseconds the other ranks' reductions give
+    up, return, and report it - status word, DICL_ERR_UNDEF from check(), a message - instead of waiting for ever or handing
+    out stale rows; after a status reset the next call on the same slot works. Nothing faults: the kernels only stop waiting."""
+    dv = pkg.devapis
+    n, rows, k, cols = 2, 1024, 320, 512
+    spaces = dv.PeerSpace.emulated(n, rows * cols * 2, 1)
+    try:
+        xs, ws, res = _operands(n, rows, k, cols, seed=31, dtype=torch.bfloat16)
+        _check(_run(pkg, ctx, spaces, 0, xs, ws, res, torch.bfloat16), _reference(xs, ws, res))   # a healthy call first
+        dv.setPeerWaitLimitNs(5_000_000)   # 5 ms
+        try:
+            numbers = [sp.begin(0) for sp in spaces]
+            epoch, prev = numbers[0]
+            pkg.diopi.diopiB200MmPush(ctx, xs[0].to(DEV), ws[0].to(DEV).t(), spaces[0], 0, epoch, prev)   # rank 1's product is missing
+            rd = res.to(DEV)
+            for sp in spaces:
+                sp.reduce_gather(0, epoch, rd.data_ptr(), rows, cols, pkg.diopi.DTYPE[torch.bfloat16], ctx.stream)
+            torch.cuda.synchronize()
+        finally:
+            dv.setPeerWaitLimitNs(0)
+        assert pkg.diopi.gemm_status() == 0   # the product itself had nothing to wait for
+        for sp in spaces:
+            assert sp.status() == 1
+            assert sp.check() == dv.diclResult_t.DICL_ERR_UNDEF
+            assert "ran out" in dv.last_error()
+            sp.reset_status()
+            assert sp.status() == 0 and sp.check() == dv.diclResult_t.DICL_SUCCESS
+        # the slot is usable again
+        xs, ws, res = _operands(n, rows, k, cols, seed=32, dtype=torch.bfloat16)
+        _check(_run(pkg, ctx, spaces, 0, xs, ws, res, torch.bfloat16), _reference(xs, ws, res))
+    finally:
+        for sp in spaces:
+            sp.close()

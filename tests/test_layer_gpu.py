@@ -153,3 +153,120 @@ def test_tp_shards_sum_to_unsharded_layer_on_one_gpu(pkg):
         torch.cuda.synchronize()
         acc += y.cpu() - x
     np.testing.assert_allclose(acc.numpy(), full_attn.numpy(), rtol=1e-3, atol=2e-5)
+
+
+# ---- the benchmarked configurations at full size ----------------------------------------------------------------------
+# Weights and caches are drawn on the device (the host generator needs a minute for a 70B-shaped layer) and copied back for
+# the oracle, so both sides hold the same bf16 values. The oracle runs on a few sequences only: sequences are independent
+# under the causal mask, and a 2048-token sequence of the 7B-shaped layer costs the CPU about a second.
+def _device_weights(cfg, seed):
+    g = torch.Generator(device=DEV)
+    g.manual_seed(seed)
+    bf = torch.bfloat16
+
+    def n(*shape):
+        return (torch.randn(shape, generator=g, device=DEV, dtype=torch.float32) * 0.02).to(bf)
+
+    d = cfg.head_dim
+    w = {"wq": n(cfg.heads * d, cfg.hidden), "wk": n(cfg.kv_heads * d, cfg.hidden), "wv": n(cfg.kv_heads * d, cfg.hidden),
+         "wo": n(cfg.hidden, cfg.heads * d), "w1": n(cfg.ffn, cfg.hidden), "w3": n(cfg.ffn, cfg.hidden), "w2": n(cfg.hidden, cfg.ffn),
+         "attention_norm": (1.0 + 0.1 * torch.randn(cfg.hidden, generator=g, device=DEV)).to(bf),
+         "ffn_norm": (1.0 + 0.1 * torch.randn(cfg.hidden, generator=g, device=DEV)).to(bf)}
+    return w, {k: v.float().cpu() for k, v in w.items()}
+
+
+def _check_layer(y_rows, ref16, ref32, rel16):
+    """Bounds for outputs that are not of unit scale. max-abs: 2e-2 scaled by the reference's largest magnitude when that is
+    above 1 (a bf16 ulp at |x| = 16 is 0.125). Against fp32: 1e-2, or 1.25 x the distance of the CPU bf16 path itself from fp32
+    where that is larger (for max-abs and for the relative L2 norm alike) - at the 7B prefill shape the reference's own op-by-op bf16 evaluation is 1.8e-2 away from fp32 (scores
+    of standard deviation 1.6 are rounded to bf16 three times before the softmax), and a device path cannot be asked to be
+    nearer to fp32 than the oracle is."""
+    scale = max(1.0, ref32.abs().max().item())
+    max_abs, rel = _err(y_rows, ref16)
+    assert max_abs <= 2e-2 * scale and rel <= rel16, ("vs op-by-op bf16 CPU path", max_abs, rel, scale)
+    gap = ((ref16 - ref32).norm() / ref32.norm()).item()
+    gap_abs = (ref16 - ref32).abs().max().item()
+    max_abs, rel = _err(y_rows, ref32)
+    assert max_abs <= max(2e-2 * scale, 1.25 * gap_abs) and rel <= max(1e-2, 1.25 * gap), ("vs fp32 CPU", max_abs, rel, gap, gap_abs, scale)
+
+
+@pytest.mark.parametrize("mode", ["literal", "baddbmm", "fused"])
+def test_c3_prefill_layer_at_the_benchmarked_shape(pkg, mode):
+    """Llama-2-7B-shaped layer, batch 8 x seq 2048 (the shape bench.py times), against the oracle on the first and the last
+    sequence of the batch."""
+    from dipu_b200 import layer as L
+    cfg = llama_cpu.LayerConfig(hidden=4096, heads=32, kv_heads=32, head_dim=128, ffn=11008, eps=1e-6)
+    batch, seq = 8, 2048
+    wd, wh = _device_weights(cfg, seed=61)
+    g = torch.Generator(device=DEV)
+    g.manual_seed(62)
+    x = (torch.randn((batch * seq, cfg.hidden), generator=g, device=DEV, dtype=torch.float32) * 0.05).to(torch.bfloat16)
+    lay = L.DecoderLayer(cfg, wd, dtype=torch.bfloat16, device=DEV)
+    del wd
+    lay.scores_by_baddbmm = mode == "baddbmm"
+    lay.fused_attention = mode == "fused"
+    y = lay.prefill(x, batch, seq)
+    torch.cuda.synchronize()
+    assert pkg.diopi.gemm_status() == 0
+    step = llama_cpu.stepwise(torch.bfloat16)
+    for b in (0, batch - 1):
+        rows = slice(b * seq, (b + 1) * seq)
+        xb = x[rows].float().cpu()
+        ref32 = llama_cpu.decoder_layer_prefill_from_hidden(cfg, wh, xb, 1, seq)
+        ref16 = llama_cpu.decoder_layer_prefill_from_hidden(cfg, wh, xb, 1, seq, step, mode == "baddbmm", mode == "fused")
+        _check_layer(y[rows], ref16, ref32, 1e-2)   # a whole layer at this size: 1e-2 against the op-by-op bf16 CPU path
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_c4_decode_layer_at_the_benchmarked_shape(pkg, fused):
+    """Llama-2-7B-shaped layer in decode, batch 64, KV length 4096 (the shape bench.py times), against the oracle on four of
+    the 64 sequences (first, two inner, last); the cache slots other than the appended one stay untouched."""
+    from dipu_b200 import layer as L
+    cfg = llama_cpu.LayerConfig(hidden=4096, heads=32, kv_heads=32, head_dim=128, ffn=11008, eps=1e-6)
+    b, length = 64, 4096
+    pos = length - 1
+    bf = torch.bfloat16
+    wd, wh = _device_weights(cfg, seed=71)
+    g = torch.Generator(device=DEV)
+    g.manual_seed(72)
+    kc = torch.randn((b, cfg.kv_heads, length, cfg.head_dim), generator=g, device=DEV, dtype=torch.float32).to(bf)
+    vc = torch.randn((b, cfg.kv_heads, length, cfg.head_dim), generator=g, device=DEV, dtype=torch.float32).to(bf)
+    x = (torch.randn((b, cfg.hidden), generator=g, device=DEV, dtype=torch.float32) * 0.5).to(bf)
+    pick = [0, 21, 42, 63]
+    kh, vh, xh = kc[pick].float().cpu(), vc[pick].float().cpu(), x[pick].float().cpu()
+    before = kc[pick, :, : pos].clone()
+    lay = L.DecoderLayer(cfg, wd, dtype=bf, device=DEV)
+    del wd
+    lay.fused_attention = fused
+    y = lay.decode(x, kc, vc, pos)
+    torch.cuda.synchronize()
+    assert pkg.diopi.gemm_status() == 0
+    ref32, kref, _ = llama_cpu.decoder_layer_decode(cfg, wh, xh, kh, vh, pos)
+    ref16, _, _ = llama_cpu.decoder_layer_decode(cfg, wh, xh, kh, vh, pos, step=llama_cpu.stepwise(bf), fused=fused)
+    _check_layer(y[pick], ref16, ref32, 5e-3)
+    ka, _ = _err(kc[pick, :, pos], kref[:, :, pos])
+    assert ka <= 2e-2 * max(1.0, kref[:, :, pos].abs().max().item())   # rotated keys reach several units: two bf16 roundings
+    assert torch.equal(kc[pick, :, : pos], before)
+
+
+@pytest.mark.parametrize("mode", ["literal", "fused"])
+def test_c5_gqa_layer_70b_shape(pkg, mode):
+    """Llama-2-70B-shaped layer (hidden 8192, 64 query / 8 key-value heads x 128, FFN 28672) at a reduced token count
+    (2 x 512): grouped heads through the expand copy (literal) and inside the fused attention kernel."""
+    from dipu_b200 import layer as L
+    cfg = llama_cpu.LayerConfig(hidden=8192, heads=64, kv_heads=8, head_dim=128, ffn=28672, eps=1e-6)
+    batch, seq = 2, 512
+    wd, wh = _device_weights(cfg, seed=81)
+    g = torch.Generator(device=DEV)
+    g.manual_seed(82)
+    x = (torch.randn((batch * seq, cfg.hidden), generator=g, device=DEV, dtype=torch.float32) * 0.05).to(torch.bfloat16)
+    lay = L.DecoderLayer(cfg, wd, dtype=torch.bfloat16, device=DEV)
+    del wd
+    lay.fused_attention = mode == "fused"
+    y = lay.prefill(x, batch, seq)
+    torch.cuda.synchronize()
+    assert pkg.diopi.gemm_status() == 0
+    xh = x.float().cpu()
+    ref32 = llama_cpu.decoder_layer_prefill_from_hidden(cfg, wh, xh, batch, seq)
+    ref16 = llama_cpu.decoder_layer_prefill_from_hidden(cfg, wh, xh, batch, seq, llama_cpu.stepwise(torch.bfloat16), False, mode == "fused")
+    _check_layer(y, ref16, ref32, 1e-2)

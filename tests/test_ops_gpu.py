@@ -2,6 +2,7 @@
 DIPU's forced CPU fallback. Shapes and tolerances of the small cases come from the reference's own unit tests
 (dipu/tests/python/unittests/test_*.py, cited per test); the bf16 [T, 4096] cases are the op-sweep configuration with
 the stated tolerance: max-abs <= 2e-2 and rel-L2 <= 5e-3 against the fp32 CPU result; index / copy work is bit-exact.
+The sweeps run at every T of the op-sweep configuration, the benchmarked 16384 and 65536 included.
 """
 import math
 
@@ -31,7 +32,7 @@ def check_close(got, ref, rtol=1e-5, atol=1e-5):
 
 
 # ---- copy / cast -------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("t", [1, 64, 1024, 4097])
+@pytest.mark.parametrize("t", [1, 64, 1024, 4097, 16384, 65536])
 def test_cast_bf16_fp32_roundtrip_bit_exact(diopi, ctx, t):
     x = rnd((t, 4096), torch.bfloat16, seed=t)
     xd = x.to(DEV)
@@ -109,7 +110,7 @@ def test_copy_empty(diopi, ctx):
 
 
 # ---- gather ----------------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("t", [1, 64, 1024])
+@pytest.mark.parametrize("t", [1, 64, 1024, 16384, 65536])
 def test_embedding_gather_bit_exact(diopi, ctx, t):
     rng = np.random.default_rng(t)
     table = rnd((32000, 4096), torch.bfloat16, seed=11, scale=0.02)
@@ -186,7 +187,7 @@ def test_integer_and_mixed_dtype_arithmetic(diopi, ctx):
     assert torch.equal(o.cpu(), x.float() * w)
 
 
-@pytest.mark.parametrize("t", [1, 64, 1024, 4096])
+@pytest.mark.parametrize("t", [1, 64, 1024, 4096, 16384, 65536])
 def test_sweep_silu_mul_add_bf16(diopi, ctx, t):
     a, b = rnd((t, 4096), torch.bfloat16, seed=t), rnd((t, 4096), torch.bfloat16, seed=t + 1)
     ad, bd = a.to(DEV), b.to(DEV)
@@ -356,7 +357,7 @@ def test_mean_sum(diopi, ctx):
     check_close(o2, y.mean(-1, keepdim=True), 1e-4, 1e-6)
 
 
-@pytest.mark.parametrize("t", [1, 64, 1024, 4096])
+@pytest.mark.parametrize("t", [1, 64, 1024, 4096, 16384, 65536])
 def test_sweep_rmsnorm_bf16(diopi, ctx, t):
     x = rnd((t, 4096), torch.bfloat16, seed=t)
     w = (1.0 + 0.1 * rnd((4096,), torch.float32, seed=1)).to(torch.bfloat16)
@@ -396,7 +397,7 @@ def test_rmsnorm_decomposed_equals_fused(diopi, ctx):
     check_close(y, fused.cpu(), 1e-5, 1e-6)
 
 
-@pytest.mark.parametrize("t", [1, 64, 1024])
+@pytest.mark.parametrize("t", [1, 64, 1024, 16384, 65536])
 def test_sweep_layernorm_bf16(diopi, ctx, t):
     x = rnd((t, 4096), torch.bfloat16, seed=t)
     w = (1.0 + 0.1 * rnd((4096,), seed=1)).to(torch.bfloat16)
@@ -435,7 +436,7 @@ def test_layernorm_reference_cases(diopi, ctx):
     assert out.is_contiguous()
 
 
-@pytest.mark.parametrize("t", [1, 64, 1024, 4096])
+@pytest.mark.parametrize("t", [1, 64, 1024, 4096, 16384, 65536])
 def test_sweep_softmax_bf16(diopi, ctx, t):
     x = rnd((t, 4096), torch.bfloat16, seed=t, scale=3.0)
     out = torch.empty((t, 4096), dtype=torch.bfloat16, device=DEV)
@@ -496,7 +497,7 @@ def _rope_half_ref(x, cos, sin):
     return torch.cat((x0 * c - x1 * s, x0 * s + x1 * c), -1)
 
 
-@pytest.mark.parametrize("t", [1, 64, 1024])
+@pytest.mark.parametrize("t", [1, 64, 1024, 16384, 65536])
 def test_sweep_rope_bf16(diopi, ctx, t):
     x = rnd((t, 32, 128), torch.bfloat16, seed=t)
     cos, sin = _tables(128, t)

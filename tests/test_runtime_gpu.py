@@ -228,3 +228,130 @@ def test_caching_allocator_with_expandable_segments(devapis):
         A.configure("expandable_segments:False")
         devapis.destroyStream(s)
     devapis.checkLastError()
+
+
+def test_memory_stats_identities(devapis):
+    """dipu/tests/python/individual_scripts/test_memory_stats.py:6-82: every tensor of numel float32 elements raises
+    `allocated` by at least ((4 * numel - 1) | 511) + 1, reserved >= allocated throughout; once everything is freed
+    allocated == 0 while reserved > 0, until empty_cache() brings reserved to 0 as well; peaks hold and reset."""
+    A = devapis.CachingAllocator
+    A.useFakeBackend(0)
+    devapis.setDevice(0)
+    s = devapis.getDefaultStream(0)
+    devapis.syncDevice()
+    A.emptyCache()
+    assert A.stats(0)["allocated_bytes"] == 0 and A.stats(0)["reserved_bytes"] == 0
+    A.resetPeakStats(0)
+    ptrs, expect = [], 0
+    for numel in [1, 7, 128, 129, 1000, 4096, 100000, 1 << 20, 3 << 20, (10 << 20) + 1, 50 << 20]:
+        before = A.stats(0)["allocated_bytes"]
+        ptrs.append(A.allocate(4 * numel, 0, s))
+        nbytes = ((4 * numel - 1) | 511) + 1
+        expect += nbytes
+        st = A.stats(0)
+        assert st["allocated_bytes"] - before >= nbytes
+        assert st["allocated_bytes"] >= expect
+        assert st["reserved_bytes"] >= st["allocated_bytes"]
+        assert st["allocated_bytes_peak"] >= st["allocated_bytes"] and st["reserved_bytes_peak"] >= st["reserved_bytes"]
+    peak = A.stats(0)["allocated_bytes_peak"]
+    for p in ptrs:
+        A.free(p)
+    st = A.stats(0)
+    assert st["allocated_bytes"] == 0 and st["reserved_bytes"] > 0
+    assert st["allocated_bytes_peak"] == peak      # the peak outlives the tensors
+    A.resetPeakStats(0)
+    assert A.stats(0)["allocated_bytes_peak"] == 0
+    A.emptyCache()
+    st = A.stats(0)
+    assert st["allocated_bytes"] == 0 and st["reserved_bytes"] == 0
+
+
+def test_one_thread_per_device_with_its_own_current_device(devapis):
+    """dipu/tests/python/individual_scripts/test_multi_thread.py:6-16: one thread per device, each setting its device and
+    working there; the current device is per thread, so no thread disturbs another or the main thread."""
+    import threading
+    n = devapis.getDeviceCount()
+    devapis.setDevice(0)
+    errors = []
+    barrier = threading.Barrier(max(n, 2))
+
+    def worker(num):
+        try:
+            index = num % n
+            devapis.setDevice(index)
+            barrier.wait(timeout=30)   # every thread has chosen its device before any of them works
+            assert devapis.current_device() == index
+            stream = devapis.getDefaultStream(index)
+            st, p = devapis.mallocDevice(1 << 20)
+            assert st == devapis.OpStatus.SUCCESS
+            devapis.memSetAsync(stream, p, 0x40 + num, 1 << 20)
+            devapis.syncStream(stream)
+            back = (ctypes.c_ubyte * 8)()
+            devapis.memCopyD2H(8, ctypes.addressof(back), p)
+            assert bytes(back) == bytes([0x40 + num]) * 8
+            assert devapis.current_device() == index
+            devapis.freeDevice(p)
+        except Exception as exc:  # reported by the main thread
+            errors.append((num, repr(exc)))
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(max(n, 2))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=60)
+    assert not errors, errors
+    assert devapis.current_device() == 0
+
+
+def test_vendor_contract_by_its_mangled_names_on_the_device():
+    """libdipu_vendor_b200_torchabi.so carries the functions DIPU links (namespace dipu::devapis, DIPU's exact C++
+    signatures: runtime/device/deviceapis.h:23-124). They are driven here by their mangled names the way DIPU's proxy layer
+    calls them: stream, device memory, asynchronous copies both ways, events and their status."""
+    import os
+    import torch  # noqa: F401  (libc10 / libtorch_cpu are dependencies of the library)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib = ctypes.CDLL(os.path.join(root, "deeplink.framework_b200", "lib", "libdipu_vendor_b200_torchabi.so"))
+    vp, sz = ctypes.c_void_p, ctypes.c_size_t
+
+    def fn(name, restype, *argtypes):
+        f = getattr(lib, name)
+        f.restype, f.argtypes = restype, list(argtypes)
+        return f
+
+    setDevice = fn("_ZN4dipu7devapis9setDeviceEa", None, ctypes.c_int8)
+    current_device = fn("_ZN4dipu7devapis14current_deviceEv", ctypes.c_int8)
+    createStream = fn("_ZN4dipu7devapis12createStreamEPP11CUstream_stb", None, ctypes.POINTER(vp), ctypes.c_bool)
+    destroyStream = fn("_ZN4dipu7devapis13destroyStreamEP11CUstream_st", None, vp)
+    syncStream = fn("_ZN4dipu7devapis10syncStreamEP11CUstream_st", None, vp)
+    createEvent = fn("_ZN4dipu7devapis11createEventEPP10CUevent_st", None, ctypes.POINTER(vp))
+    destroyEvent = fn("_ZN4dipu7devapis12destroyEventEP10CUevent_st", None, vp)
+    recordEvent = fn("_ZN4dipu7devapis11recordEventEP10CUevent_stP11CUstream_st", None, vp, vp)
+    getEventStatus = fn("_ZN4dipu7devapis14getEventStatusEP10CUevent_st", ctypes.c_int32, vp)
+    mallocDevice = fn("_ZN4dipu7devapis12mallocDeviceEPPvmb", ctypes.c_int32, ctypes.POINTER(vp), sz, ctypes.c_bool)
+    freeDevice = fn("_ZN4dipu7devapis10freeDeviceEPv", None, vp)
+    h2d = fn("_ZN4dipu7devapis15memCopyH2DAsyncEP11CUstream_stmPvPKv", None, vp, sz, vp, vp)
+    d2h = fn("_ZN4dipu7devapis15memCopyD2HAsyncEP11CUstream_stmPvPKv", None, vp, sz, vp, vp)
+
+    setDevice(0)
+    assert current_device() == 0
+    stream, event, dptr = vp(), vp(), vp()
+    createStream(ctypes.byref(stream), False)
+    createEvent(ctypes.byref(event))
+    assert stream.value and event.value
+    n = 1 << 20
+    assert mallocDevice(ctypes.byref(dptr), n, True) == 0 and dptr.value      # OpStatus::SUCCESS
+    src = (ctypes.c_ubyte * n)()
+    ctypes.memset(src, 0xA5, n)
+    dst = (ctypes.c_ubyte * n)()
+    h2d(stream, n, dptr, ctypes.addressof(src))
+    d2h(stream, n, ctypes.addressof(dst), dptr)
+    recordEvent(event, stream)
+    syncStream(stream)
+    assert getEventStatus(event) == 3                                          # EventStatus::READY
+    assert bytes(dst[:64]) == b"\xa5" * 64 and bytes(dst[-64:]) == b"\xa5" * 64
+    # an impossible request reports ERR_NOMEM instead of throwing when asked to
+    huge = vp()
+    assert mallocDevice(ctypes.byref(huge), 1 << 50, False) == 2 and not huge.value
+    freeDevice(dptr)
+    destroyEvent(event)
+    destroyStream(stream)

@@ -156,6 +156,27 @@ def test_multinomial_with_replacement_matches_distribution(pkg, diopi, ctx):
     assert ((picked % 2) == 1).all() and (picked >= 0).all() and (picked < 32000).all()
 
 
+def test_multinomial_never_draws_a_masked_token(diopi, ctx):
+    """Rows as they look after top-k / top-p masking: a few positive weights spread over a vocabulary of zeros, of very
+    different magnitude (so that running sums round), many draws per row: an index of weight zero must never come back."""
+    rows, vocab, n = 32, 32000, 50000
+    rng = np.random.default_rng(21)
+    w = torch.zeros((rows, vocab))
+    for r in range(rows):
+        keep = torch.from_numpy(rng.choice(vocab, size=5 + r, replace=False))
+        w[r, keep] = torch.from_numpy(rng.random(keep.numel()).astype(np.float32) ** 6 + 1e-7)
+    out = torch.empty((rows, n), dtype=torch.int64, device=DEV)
+    diopi.diopiMultinomial(ctx, out, w.to(DEV), n, True, diopi.Generator(seed=99))
+    o = out.cpu()
+    assert (o >= 0).all() and (o < vocab).all()
+    assert (torch.gather(w, 1, o) > 0).all()
+    # and the heaviest token of a row is drawn about as often as its weight says
+    top = w.argmax(1)
+    freq = (o == top.view(-1, 1)).double().mean(1)
+    want = (w.max(1).values / w.sum(1)).double()
+    assert (freq - want).abs().max().item() < 2e-2
+
+
 def test_multinomial_without_replacement(diopi, ctx):
     w = torch.tensor([[1.0, 0.0, 2.0, 3.0, 0.0, 4.0, 5.0, 1.0]])
     gen = diopi.Generator(seed=7)

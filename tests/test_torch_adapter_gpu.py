@@ -187,6 +187,26 @@ def test_scaled_dot_product_attention_reaches_the_fused_kernel(adapter, kv_heads
     assert err <= 2e-2 and rel <= 5e-3, (err, rel)
 
 
+@pytest.mark.parametrize("sq,skv", [(1, 200), (72, 300), (300, 72), (260, 130)])
+def test_scaled_dot_product_attention_causal_with_unequal_lengths(adapter, sq, skv):
+    """is_causal with L != S: torch aligns the mask to the first key (query i sees keys 0..i, the lower triangle of ones(L, S)),
+    the library's operator to the last one. The adapter has to give torch's answer: L = 1 sees key 0 only, and with more
+    queries than keys the late queries see every key."""
+    dev = torch.device("dipu:0")
+    g = torch.Generator().manual_seed(sq * 1000 + skv)
+    b, h, d = 2, 4, 128
+    q = torch.randn(b, sq, h, d, generator=g).to(torch.bfloat16)
+    k = torch.randn(b, skv, h, d, generator=g).to(torch.bfloat16)
+    v = torch.randn(b, skv, h, d, generator=g).to(torch.bfloat16)
+    ref = F.scaled_dot_product_attention(q.float().transpose(1, 2), k.float().transpose(1, 2), v.float().transpose(1, 2), is_causal=True)
+    with torch.no_grad():
+        out = F.scaled_dot_product_attention(q.to(dev).transpose(1, 2), k.to(dev).transpose(1, 2), v.to(dev).transpose(1, 2), is_causal=True)
+        got = out.float().cpu()
+    assert out.shape == (b, h, sq, d)
+    err, rel = (got - ref).abs().max().item(), ((got - ref).norm() / ref.norm()).item()
+    assert err <= 2e-2 and rel <= 5e-3, (err, rel)
+
+
 def test_sampling_ops_through_the_adapter(adapter):
     dev = torch.device("dipu:0")
     g = torch.Generator().manual_seed(5)
@@ -211,3 +231,66 @@ def test_missing_wrapper_raises_instead_of_falling_back(adapter):
     x = torch.ones(8, device="dipu:0")
     with pytest.raises(NotImplementedError):
         torch.flip(x, [0])
+
+
+# ---- copies: the cases of dipu/tests/python/unittests/test_copy.py:88-150 -------------------------------------------------
+def test_h2d_copies_from_freed_pageable_buffers_stay_correct(adapter):
+    """500 non-blocking host-to-device copies whose pageable source tensors are freed right after the call
+    (test_copy.py:126-143): every device tensor must hold its value."""
+    dev = torch.device("dipu:0")
+
+    def copy_tensor(device_tensor, val):
+        cpu_tensor = torch.empty(device_tensor.shape, dtype=torch.float32, pin_memory=False).fill_(val)
+        device_tensor.copy_(cpu_tensor, non_blocking=True)
+        del cpu_tensor
+
+    tensors = []
+    for i in range(500):
+        t = torch.empty(100, 100, dtype=torch.float32, device=dev)
+        copy_tensor(t, float(i))
+        tensors.append(t)
+    for i in range(500):
+        assert torch.equal(tensors[i].cpu(), torch.full((100, 100), float(i)))
+
+
+def test_h2d_copy_blocking_is_really_blocking(adapter):
+    # test_copy.py:145-150: the source may change as soon as copy_ returns
+    a = torch.ones(1000000, pin_memory=True)
+    b = torch.zeros(1000000, device="dipu:0")
+    b.copy_(a, non_blocking=False)
+    a[-1].fill_(-1)
+    assert torch.equal(b.cpu(), torch.ones(1000000))
+
+
+def test_copy_into_a_hollow_strided_destination(adapter):
+    # test_copy.py:78-85
+    g = torch.Generator().manual_seed(3)
+    t1 = torch.rand((6, 4), generator=g)
+    d1 = t1.to("dipu:0")
+    dst = d1.as_strided((2, 2), (4, 1))
+    src = torch.rand((2, 2), generator=g)
+    dst.copy_(src.to("dipu:0"))
+    assert torch.equal(dst.cpu(), src)
+    want = t1.clone()
+    want.as_strided((2, 2), (4, 1)).copy_(src)
+    assert torch.equal(d1.cpu(), want)   # nothing outside the view was touched
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_copies_between_two_devices(adapter):
+    """test_copy.py:88-117: copy_ between tensors of two devices in both directions, and a non-contiguous source (relayed
+    through a dense tensor on its own device)."""
+    g = torch.Generator().manual_seed(4)
+    for a, b in ((0, 1), (1, 0)):
+        src_h, dst_h = torch.rand((640, 400), generator=g), torch.rand((640, 400), generator=g)
+        src, dst = src_h.to("dipu:%d" % a), dst_h.to("dipu:%d" % b)
+        dst.copy_(src)
+        assert torch.equal(dst.cpu(), src_h) and dst.device.index == b and src.device.index == a
+    big = torch.rand((640, 990), generator=g)
+    src = big.to("dipu:1")[::2, ::3]
+    dst = src.to("dipu:0")
+    assert torch.equal(dst.cpu(), big[::2, ::3]) and dst.device.index == 0
+    # other dtype and a strided destination on the receiving side
+    dst2 = torch.zeros((320, 660), dtype=torch.bfloat16, device="dipu:0")[:, ::2]
+    dst2.copy_(src)
+    assert torch.equal(dst2.cpu(), big[::2, ::3].to(torch.bfloat16))
