@@ -251,7 +251,7 @@ def decode_oracle_refs(cfg, w, x4, kc4, vc4, position, world, rank, dist):
     """CPU oracle outputs of the decode step for the first sequences of the batch. kc4 / vc4: this rank's cache shard
     [n, local kv heads, L, D]; every rank fills its shard from the same seed, so the unsharded cache is the shard repeated
     over the ranks along the head dimension."""
-    names = ("fp32", "bf16_stepwise", "bf16_stepwise_fused")
+    names = ("fp32", "bf16_stepwise", "bf16_stepwise_fused", "bf16_stepwise_fused_step")
     out = {}
     if rank == 0:
         from oracle import llama_cpu
@@ -262,6 +262,7 @@ def decode_oracle_refs(cfg, w, x4, kc4, vc4, position, world, rank, dist):
             out["fp32"] = llama_cpu.decoder_layer_decode(cfg, w, xf, kc, vc, position)[0]
             out["bf16_stepwise"] = llama_cpu.decoder_layer_decode(cfg, w, xf, kc, vc, position, step=bf)[0]
             out["bf16_stepwise_fused"] = llama_cpu.decoder_layer_decode(cfg, w, xf, kc, vc, position, step=bf, fused=True)[0]
+            out["bf16_stepwise_fused_step"] = llama_cpu.decoder_layer_decode(cfg, w, xf, kc, vc, position, step=bf, fused=True, fused_gate_up=True)[0]
     if dist is not None:
         for name in names:
             t = out[name].contiguous() if rank == 0 else torch.empty((x4.shape[0], cfg.hidden), dtype=torch.float32)
@@ -818,9 +819,28 @@ def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ra
     ms_fused = max_over_ranks(e0.elapsed_time(e1)) / steps
     outs["fused_attention"] = out_g[:n_check].clone()
     devapis.graphDestroy(replay.graph)
+    # variant: the whole step through the fused entry points (one q/k/v projection, rotary + cache append, add + RMSNorm,
+    # SiLU * up in the epilogue of one gate / up product): ten launches instead of nineteen
+    lay.fused_decode = True
+    for _ in range(3):
+        lay.decode(xd, kc, vc, length - 1, ctx)
+    replay, out_g = lay.capture_decode(xd, kc, vc, length - 1, ctx)
+    for _ in range(5):
+        replay()
+    barrier()
+    e0.record(stream)
+    for _ in range(steps):
+        replay()
+    e1.record(stream)
+    barrier()
+    ms_step = max_over_ranks(e0.elapsed_time(e1)) / steps
+    outs["fused_step"] = out_g[:n_check].clone()
+    devapis.graphDestroy(replay.graph)
+    lay.fused_decode = False
     # tensor parallel: the two 512 KiB partial sums per step reduced by ONE kernel over peer memory on the compute stream
     # (b200_dicl_peer_all_reduce) instead of ncclAllReduce on the communication stream; fused attention stays on
     ms_peer = None
+    ms_step_peer = None
     peer_ok = False
     if world > 1 and lay.tp_group is not None:
         try:
@@ -844,6 +864,22 @@ def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ra
         ms_peer = max_over_ranks(e0.elapsed_time(e1)) / steps
         outs["fused_attention_peer_all_reduce"] = out_g[:n_check].clone()
         devapis.graphDestroy(replay.graph)
+        lay.fused_decode = True
+        for _ in range(3):
+            lay.decode(xd, kc, vc, length - 1, ctx)
+        replay, out_g = lay.capture_decode(xd, kc, vc, length - 1, ctx)
+        for _ in range(5):
+            replay()
+        barrier()
+        e0.record(stream)
+        for _ in range(steps):
+            replay()
+        e1.record(stream)
+        barrier()
+        ms_step_peer = max_over_ranks(e0.elapsed_time(e1)) / steps
+        outs["fused_step_peer_all_reduce"] = out_g[:n_check].clone()
+        devapis.graphDestroy(replay.graph)
+        lay.fused_decode = False
         assert lay.tp_group.peer.status() == 0, "a peer all-reduce wait timed out"
         lay.tp_group.peer.close()
         lay.tp_group.peer = None
@@ -856,7 +892,7 @@ def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ra
         refs = decode_oracle_refs(cfg, host_w, xd[:n_check], kc[:n_check], vc[:n_check], length - 1, world, rank, dist)
         parity = {}
         for name, got in outs.items():
-            form = "bf16_stepwise_fused" if name.startswith("fused") else "bf16_stepwise"
+            form = "bf16_stepwise_fused_step" if name.startswith("fused_step") else ("bf16_stepwise_fused" if name.startswith("fused") else "bf16_stepwise")
             sw = bench_checks.REL_STEPWISE if world == 1 else bench_checks.REL_LOOSE  # TP: partial sums travel rounded to bf16
             entry = bench_checks.parity_entry(got, {form: (refs[form], sw), "fp32": (refs["fp32"], bench_checks.fp32_bound(refs[form], refs["fp32"]))})
             entry["all_ranks_ok"] = all_ranks(entry["ok"], dist)
@@ -876,6 +912,13 @@ def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ra
             "fused_attention": {"tokens_per_s": b / (ms_fused * 1e-3), "ms_per_step": ms_fused,
                                 "hbm_frac": round((weight_bytes + kv_bytes) / (ms_fused * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
                                 "note": "diopiMultiHeadAttention on views of the cache replaces diopiBmm, diopiDivInpScalar, diopiSoftmax, diopiBmm"},
+            "fused_step": {"tokens_per_s": b / (ms_step * 1e-3), "ms_per_step": ms_step,
+                           "hbm_frac": round((weight_bytes + kv_bytes) / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                           "note": "as fused_attention, with one q/k/v projection, diopiB200RopeAppendKV, diopiB200AddRMSNorm and "
+                                   "diopiB200MmSwiGLU (include/diopi/functions_b200.h): ten launches per step"},
+            "fused_step_peer_all_reduce": None if ms_step_peer is None else {
+                "tokens_per_s": b / (ms_step_peer * 1e-3), "ms_per_step": ms_step_peer,
+                "note": "as fused_step, with both all-reduces done by one kernel each over peer memory"},
             "fused_attention_peer_all_reduce": None if ms_peer is None else {
                 "tokens_per_s": b / (ms_peer * 1e-3), "ms_per_step": ms_peer,
                 "note": "as fused_attention, with both all-reduces done by one kernel each over peer memory (NVLink loads, bounded flag waits)"}}

@@ -379,6 +379,33 @@ diopiError_t diopiMm(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiCon
     return mm_like(ctx, "diopiMm", vo, va, vb, nullptr, 1.0, 0.0, false);
 }
 
+// out [M, F] = silu(input x gate columns) * (input x up columns) for mat2 [K, 2F] whose columns 2j / 2j+1 are the gate / up
+// weights of feature j: one product over the interleaved weight with the SiLU and the multiplication in its epilogue.
+diopiError_t diopiB200MmSwiGLU(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input, diopiConstTensorHandle_t mat2) {
+    B200_VIEW(vo, out);
+    B200_VIEW(va, input);
+    B200_VIEW(vb, mat2);
+    B200_CHECK(va.ndim == 2 && vb.ndim == 2 && vo.ndim == 2 && va.shape[1] == vb.shape[0], "diopiB200MmSwiGLU: expected [M, K] x [K, 2F] -> [M, F]");
+    B200_CHECK(vb.shape[1] % 2 == 0 && vo.shape[0] == va.shape[0] && vo.shape[1] * 2 == vb.shape[1], "diopiB200MmSwiGLU: output must be [M, F] for mat2 [K, 2F]");
+    B200_CHECK(va.device == diopi_device && vb.device == diopi_device && vo.device == diopi_device, "diopiB200MmSwiGLU: operands must be device tensors");
+    B200_CHECK(va.dtype == vb.dtype && vo.dtype == va.dtype && (va.dtype == diopi_dtype_bfloat16 || va.dtype == diopi_dtype_float16),
+               "diopiB200MmSwiGLU: bfloat16 or float16 tensors of one dtype");
+    B200_CHECK(va.shape[0] >= 1 && va.shape[0] <= 128, "diopiB200MmSwiGLU: served for 1 to 128 rows (decode batches); got %lld", (long long)va.shape[0]);
+    B200_CHECK(vo.stride[1] == 1 && vo.stride[0] >= vo.shape[1], "diopiB200MmSwiGLU: output rows must be contiguous");
+    GemmProblem g;
+    g.M = va.shape[0]; g.K = va.shape[1]; g.N = vb.shape[1];
+    g.A = va.data; g.a_sm = va.stride[0]; g.a_sk = va.stride[1];
+    g.B = vb.data; g.b_sk = vb.stride[0]; g.b_sn = vb.stride[1];
+    g.C = vo.data; g.c_sm = vo.stride[0]; g.c_sn = 1;
+    g.ab_dtype = va.dtype; g.c_dtype = vo.dtype;
+    g.epilogue = GemmProblem::kSwiGLU;
+    GemmProblem operands = g;   // the layout rules concern the operands; the output is half as wide as the product
+    operands.c_sm = g.c_sm >= g.N ? g.c_sm : g.N;
+    B200_CHECK(gemm_tc_eligible(operands), "diopiB200MmSwiGLU: operands do not meet the tensor-core kernel's layout rules (16-byte aligned pointers, "
+               "pitches that are multiples of 8 elements, K or N contiguous)");
+    return gemm_tc_launch(g, stream_of(ctx));
+}
+
 // mat1 [M, K] x mat2 [K, N]: this rank's partial sum of a row-parallel linear, pushed into the peers' staging slots.
 diopiError_t diopiB200MmPush(diopiContextHandle_t ctx, diopiConstTensorHandle_t input, diopiConstTensorHandle_t mat2, const b200PeerSpace* space,
                              int32_t slot, uint32_t epoch, uint32_t prev_epoch) {

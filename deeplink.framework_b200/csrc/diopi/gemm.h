@@ -25,6 +25,10 @@ struct GemmProblem {
     float alpha = 1.f, beta = 0.f;
     // Status word to report into; nullptr = the per-device word the library allocates on first use.
     uint32_t* status_override = nullptr;
+    // Epilogue of the single-row-block (M <= 128) kernel. kSwiGLU: the N columns of the product are (gate, up) pairs,
+    // columns 2j and 2j+1; C is [M, N / 2] and receives silu(gate_j) * up_j, formed in fp32 and rounded once.
+    enum Epilogue { kPlain = 0, kSwiGLU = 1 };
+    int epilogue = kPlain;
 };
 
 // tcgen05 / TMEM / TMA kernel (bf16 or fp16 operands, fp32 accumulation).

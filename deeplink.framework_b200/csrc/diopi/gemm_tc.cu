@@ -361,8 +361,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // tiles) and shrinking BN makes every CTA re-read all of A. Here a cluster of S CTAs shares one 128 x BN output tile,
 // each CTA contracting its own slice of K (so A is read N/BN times in total, B exactly once, and tiles x S CTAs stream).
 // The fp32 partial tiles are exchanged through distributed shared memory: every CTA parks its accumulator in its own
-// shared memory (the drained pipeline stages), the cluster synchronises, CTA r sums columns [r*BN/S, (r+1)*BN/S) of all
-// S partials in rank order and writes them out. No global workspace, one launch, deterministic.
+// shared memory (the drained pipeline stages), the cluster synchronises, CTA r sums its share of the tile's 16-byte column
+// chunks over all S partials in rank order and writes them out. No global workspace, one launch, deterministic.
+// S is any cluster size from 1 to 8 (the planner picks tiles x S close to the SM count; S = 1 is a wide product whose
+// tiles alone occupy the SMs, each CTA streaming its whole K extent). With swiglu != 0 the tile's columns are (gate, up)
+// pairs and the output is silu(gate) * up, half as wide: the SiLU and the product of the feed-forward block ride in the
+// epilogue of ONE product over the interleaved gate / up weight instead of two products and two element-wise kernels.
 struct SplitKParams {
     int M, N, K, batch;
     int n_blocks, k_blocks, kb_per_cta, splits;
@@ -373,6 +377,7 @@ struct SplitKParams {
     float alpha, beta;
     uint32_t idesc;
     int b_mn_major;
+    int swiglu;
     uint32_t* status;
 };
 
@@ -507,25 +512,43 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     cluster_sync_all();
 
     if (warp >= 2 && *abort_flag == 0) {
-        // epilogue part 2: this CTA owns columns [ks * BN/S, (ks+1) * BN/S) of the tile: sum them over the S partials
-        const int slice_cols = BN / p.splits;           // multiple of 4
-        const int chunks_per_row = slice_cols / 4;
+        // epilogue part 2: this CTA owns the 16-byte column chunks [c0, c1) of the tile: sum them over the S partials
+        constexpr int kChunks = BN / 4;
+        const int c0 = (static_cast<int>(ks) * kChunks) / p.splits, c1 = ((static_cast<int>(ks) + 1) * kChunks) / p.splits;
+        const int chunks_per_row = c1 - c0;
         const int rows = min(p.M, BM);
         const int items = rows * chunks_per_row;
         const uint32_t local_base = smem_u32(partial);
         for (int i = threadIdx.x - 64; i < items; i += 128) {
             const int row = i / chunks_per_row;
-            const int cc = i - row * chunks_per_row;
-            const int chunk = (static_cast<int>(ks) * slice_cols) / 4 + cc;
+            const int chunk = c0 + (i - row * chunks_per_row);
             const uint32_t off = static_cast<uint32_t>(row) * (BN * 4) + ((chunk ^ (row & 7)) * 16);
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int s = 0; s < p.splits; ++s) {
-                const float4 v = ld_cluster_f4(map_to_cta(local_base + off, static_cast<uint32_t>(s)));
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            // all partials of the chunk are requested before the first one is used: a remote shared-memory load takes several
+            // hundred cycles, and a loop that adds them one by one would wait that long per CTA of the cluster
+            float4 v[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                v[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (s < p.splits) v[s] = ld_cluster_f4(map_to_cta(local_base + off, static_cast<uint32_t>(s)));
+            }
+            float4 acc = v[0];
+#pragma unroll
+            for (int s = 1; s < 8; ++s) {
+                if (s < p.splits) {
+                    acc.x += v[s].x; acc.y += v[s].y; acc.z += v[s].z; acc.w += v[s].w;
+                }
             }
             const int col = nb * BN + chunk * 4;
-            float o[4] = {acc.x * p.alpha, acc.y * p.alpha, acc.z * p.alpha, acc.w * p.alpha};
             TOut* crow = static_cast<TOut*>(p.C) + static_cast<int64_t>(b) * p.stride_cb + static_cast<int64_t>(row) * p.ldc;
+            if (p.swiglu) {
+                // columns (col, col + 1) and (col + 2, col + 3) are (gate, up) pairs: two outputs at col / 2
+                const float g0 = acc.x * p.alpha, u0 = acc.y * p.alpha, g1 = acc.z * p.alpha, u1 = acc.w * p.alpha;
+                const int oc = col >> 1;
+                if (col + 1 < p.N) crow[oc] = from_f32<TOut>(g0 / (1.f + __expf(-g0)) * u0);
+                if (col + 3 < p.N) crow[oc + 1] = from_f32<TOut>(g1 / (1.f + __expf(-g1)) * u1);
+                continue;
+            }
+            float o[4] = {acc.x * p.alpha, acc.y * p.alpha, acc.z * p.alpha, acc.w * p.alpha};
             if (p.bias != nullptr) {
                 const TOut* brow = static_cast<const TOut*>(p.bias) + static_cast<int64_t>(b) * p.bias_sb + static_cast<int64_t>(row) * p.bias_sr;
 #pragma unroll
@@ -672,23 +695,36 @@ cudaError_t launch_splitk_bn(int bn, const CUtensorMap& ma, const CUtensorMap& m
     }
 }
 
-// Split-K plan for a single row-block: tile width and cluster size. Returns false when plain tiling is the better choice.
+// Plan of the single-row-block kernel (M <= 128): tile width (256, 128 or 64 columns) and cluster size (1 to 4 CTAs sharing
+// a tile's K extent). The pair that puts the most CTAs on the device without exceeding one CTA per SM wins; among equals the
+// larger cluster (wider tiles re-read A less often). Clusters of 8 measured slower than clusters of 4 on narrower tiles
+// ([64, 4096] x [4096, 4096]: 25.5 against 15.8 us; K = 11008: 38.6 against 25.3 us), so 4 is the limit.
+// Returns false when plain tiling is the better choice: more tiles than SMs even at 256 columns (the persistent kernel walks
+// them), or a single CTA per tile without a fused epilogue (the persistent kernel's TMA-store epilogue serves that).
 bool plan_splitk(const GemmProblem& g, int sms, int* bn_out, int* splits_out) {
     if (g.M > BM) return false;
     const int64_t k_blocks = (g.K + BK - 1) / BK;
-    int bn = 256;
-    for (; bn > 64; bn >>= 1) {
-        const int64_t nb = (g.N + bn - 1) / bn;
-        if (g.N > bn / 2 && nb * g.batch * 8 >= (sms * 3) / 5) break;  // widest tile that can still fill most SMs with 8-way split
+    int best_bn = 0, best_splits = 0;
+    int64_t best_ctas = 0;
+    for (int bn = 256; bn >= 64; bn >>= 1) {
+        if (bn > 64 && g.N <= bn / 2) continue;  // a tile twice as wide as the product
+        const int64_t tiles = ((g.N + bn - 1) / bn) * g.batch;
+        if (tiles > sms) continue;
+        int64_t splits = sms / tiles;
+        if (splits > 4) splits = 4;
+        if (splits > k_blocks) splits = k_blocks;
+        if (splits < 1) splits = 1;
+        const int64_t ctas = tiles * splits;
+        if (ctas > best_ctas || (ctas == best_ctas && splits > best_splits)) {
+            best_ctas = ctas;
+            best_bn = bn;
+            best_splits = static_cast<int>(splits);
+        }
     }
-    const int64_t nb = (g.N + bn - 1) / bn;
-    int splits = 8;
-    while (splits > 1 && (nb * g.batch * splits > (sms * 5) / 4 || splits > k_blocks)) splits >>= 1;
-    // every CTA of the cluster needs a non-empty K slice except possibly the last ones; keep slices balanced
-    if (splits < 2) return false;
-    if (nb * g.batch >= sms / 2) return false;  // enough tiles already
-    *bn_out = bn;
-    *splits_out = splits;
+    if (best_bn == 0) return false;
+    if (best_splits < 2 && g.epilogue == GemmProblem::kPlain) return false;
+    *bn_out = best_bn;
+    *splits_out = best_splits;
     return true;
 }
 
@@ -758,9 +794,13 @@ diopiError_t gemm_tc_launch(const GemmProblem& g, cudaStream_t stream) {
     while (bn > min_bn && (g.N <= bn / 2 || g.batch * m_blocks * ((g.N + bn - 1) / bn) < sms)) bn >>= 1;
     const int64_t n_blocks = (g.N + bn - 1) / bn;
 
-    if (gemm_tc2_applies(g)) return gemm_tc2_launch(g, stream);
+    if (g.epilogue == GemmProblem::kPlain && gemm_tc2_applies(g)) return gemm_tc2_launch(g, stream);
     int sk_bn = 0, sk_splits = 0;
-    if (plan_splitk(g, sms, &sk_bn, &sk_splits)) {
+    const bool planned = plan_splitk(g, sms, &sk_bn, &sk_splits);
+    B200_CHECK(planned || g.epilogue == GemmProblem::kPlain,
+               "gemm: the fused gate / up epilogue is served for up to %d rows and at most %d tiles of 256 columns (got %lld x %lld)", BM, sms,
+               (long long)g.M, (long long)g.N);
+    if (planned) {
         const bool b_mn_sk = b_mn;
         CUtensorMap sa, sb;
         B200_CHECK(encode_map(&sa, g.ab_dtype, g.A, g.K, g.M, g.batch, g.a_sm, g.batch > 1 ? g.a_sb : g.a_sm * g.M, BM),
@@ -783,6 +823,7 @@ diopiError_t gemm_tc_launch(const GemmProblem& g, cudaStream_t stream) {
         q.alpha = g.alpha; q.beta = g.beta;
         q.idesc = make_idesc_f16(is_bf16 ? 1 : 0, b_mn_sk, BM, sk_bn);
         q.b_mn_major = b_mn_sk ? 1 : 0;
+        q.swiglu = g.epilogue == GemmProblem::kSwiGLU ? 1 : 0;
         q.status = g.status_override != nullptr ? g.status_override : status_word();
         B200_CHECK(q.status != nullptr, "gemm: could not allocate the kernel status word");
         const int grid_sk = q.batch * q.n_blocks * sk_splits;

@@ -175,6 +175,8 @@ SIGNATURES = {
     "diopiMultiHeadAttention": "TTTdbbdTttt",
     "diopiArgmax": "TtIb", "diopiSort": "TTtibP", "diopiTopk": "TTtiibb", "diopiCumsum": "Tti", "diopiGather": "Ttit",
     "diopiMultinomial": "TtibG", "diopiIndexPutInp": "TtLb",
+    # additions of this library (include/diopi/functions_b200.h): fused steps of a decode iteration
+    "diopiB200MmSwiGLU": "TTT", "diopiB200AddRMSNorm": "TTTTtd", "diopiB200RopeAppendKV": "TTTTTTi",
 }
 
 _CTYPES = {"T": ctypes.c_void_p, "t": ctypes.c_void_p, "s": ctypes.POINTER(_Scalar), "i": ctypes.c_int64, "d": ctypes.c_double,

@@ -64,6 +64,31 @@ DIOPI_API diopiError_t diopiB200MmPush(diopiContextHandle_t ctx, diopiConstTenso
                                        const b200PeerSpace* space, int32_t slot, uint32_t epoch, uint32_t prev_epoch);
 DIOPI_API void diopiB200SetPushWaitLimitNs(unsigned long long ns);
 
+/* Fused steps of a decode iteration. No counterparts among the reference's call sites, which dispatch the pieces one by one
+ * (dicp/test/model/llama/model.py:34-39 RMSNorm, :58-69 rotary, :134-138 cache append, :174-175 SwiGLU, :193-201 residual
+ * adds); every function rounds where the separate calls round unless stated, so a model can switch call by call.
+ *
+ * diopiB200MmSwiGLU    out [M, F] = silu(input @ gate) * (input @ up) for mat2 [K, 2F] whose columns 2j and 2j+1 are the gate
+ *                      and up weights of feature j (interleave w1 / w3 once at load time; the nn.Linear layout [2F, K] is
+ *                      passed as its transposed view). One product, the SiLU and the multiplication in its epilogue, formed in
+ *                      fp32 and rounded ONCE (the separate calls round the two products, the SiLU and the product again).
+ *                      bfloat16 / float16, 1 to 128 rows.
+ * diopiB200AddRMSNorm  sum_out = input + residual (rounded like diopiAdd), norm_out = RMSNorm(sum_out) * weight (weight may be
+ *                      NULL): the residual add that ends one block and the norm that opens the next, in one pass.
+ *                      [rows, cols] bfloat16 / float16, inputs with contiguous rows, dense outputs.
+ * diopiB200RopeAppendKV  from qkv [B, (Hq + 2 Hkv) * D], the output of ONE projection over the concatenated q / k / v weight:
+ *                      q rotated -> q_out [B, Hq, D]; k rotated -> k_cache[:, :, position, :]; v -> v_cache[:, :, position, :]
+ *                      (caches [B, Hkv, L, D] with any pitches). Half-split rotary layout (pairs i, i + D/2), cos / sin float32
+ *                      [1 or B, D / 2] (row b % rows), products and sums in fp32 rounded once like diopiRotaryEmbedding. */
+DIOPI_API diopiError_t diopiB200MmSwiGLU(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t input,
+                                         diopiConstTensorHandle_t mat2);
+DIOPI_API diopiError_t diopiB200AddRMSNorm(diopiContextHandle_t ctx, diopiTensorHandle_t sum_out, diopiTensorHandle_t norm_out,
+                                           diopiConstTensorHandle_t input, diopiConstTensorHandle_t residual, diopiConstTensorHandle_t weight,
+                                           double eps);
+DIOPI_API diopiError_t diopiB200RopeAppendKV(diopiContextHandle_t ctx, diopiTensorHandle_t q_out, diopiConstTensorHandle_t qkv,
+                                             diopiConstTensorHandle_t cos, diopiConstTensorHandle_t sin, diopiTensorHandle_t k_cache,
+                                             diopiTensorHandle_t v_cache, int64_t position);
+
 #ifdef __cplusplus
 }
 #endif

@@ -197,7 +197,10 @@ def attention_prefill(cfg, w, x, batch, seq, step=_identity, scores_by_baddbmm=F
     return step(out @ w["wo"].t())
 
 
-def feed_forward(w, x, step=_identity):
+def feed_forward(w, x, step=_identity, fused_gate_up=False):
+    if fused_gate_up:
+        # SiLU(gate) * up as ONE materialising op over the two products (the fused gate / up projection): one rounding
+        return step(step(torch.nn.functional.silu(x @ w["w1"].t()) * (x @ w["w3"].t())) @ w["w2"].t())
     gate = step(torch.nn.functional.silu(step(x @ w["w1"].t())))
     return step(step(gate * step(x @ w["w3"].t())) @ w["w2"].t())
 
@@ -213,9 +216,10 @@ def decoder_layer_prefill(cfg, w, embedding, ids, step=_identity, scores_by_badd
     return decoder_layer_prefill_from_hidden(cfg, w, embedding[ids.reshape(-1)], batch, seq, step, scores_by_baddbmm, fused)
 
 
-def decoder_layer_decode(cfg, w, x, k_cache, v_cache, position, step=_identity, fused=False):
+def decoder_layer_decode(cfg, w, x, k_cache, v_cache, position, step=_identity, fused=False, fused_gate_up=False):
     """One new token per sequence. x [B, hidden]; caches [B, kv_heads, L, D] whose slot `position` is overwritten by the
-    new token's key / value; attention covers slots 0..position. Returns (out [B, hidden], k_cache, v_cache)."""
+    new token's key / value; attention covers slots 0..position. Returns (out [B, hidden], k_cache, v_cache).
+    fused: the attention core as one materialising op; fused_gate_up: SiLU(gate) * up as one materialising op."""
     b = x.shape[0]
     d = cfg.head_dim
     hn = step(rms_norm(x, w["attention_norm"], cfg.eps))
@@ -234,7 +238,7 @@ def decoder_layer_decode(cfg, w, x, k_cache, v_cache, position, step=_identity, 
         vb = v_cache[:, :, : position + 1, :].transpose(1, 2)
         ctx = step(fused_attention(q.unsqueeze(1), kb, vb, False)[0]).reshape(b, cfg.heads * d)
         h = step(x + step(ctx @ w["wo"].t()))
-        out = step(h + feed_forward(w, step(rms_norm(h, w["ffn_norm"], cfg.eps)), step))
+        out = step(h + feed_forward(w, step(rms_norm(h, w["ffn_norm"], cfg.eps)), step, fused_gate_up))
         return out, k_cache, v_cache
     keys = _expand_kv(cfg, k_cache[:, :, : position + 1, :])
     vals = _expand_kv(cfg, v_cache[:, :, : position + 1, :])

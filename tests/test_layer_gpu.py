@@ -66,7 +66,7 @@ def test_bf16_prefill_layer(pkg, kv_heads, mode):
     assert max_abs <= 2e-2 and rel <= 1e-2, (max_abs, rel)
 
 
-@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("fused", [False, True, "step"])
 @pytest.mark.parametrize("kv_heads", [8, 4])
 def test_bf16_decode_layer(pkg, kv_heads, fused):
     from dipu_b200 import layer as L
@@ -79,9 +79,10 @@ def test_bf16_decode_layer(pkg, kv_heads, fused):
     bf = torch.bfloat16
     args = (cfg, llama_cpu.round_weights(w, bf), llama_cpu.round_tensor(x, bf), llama_cpu.round_tensor(kc, bf), llama_cpu.round_tensor(vc, bf), pos)
     ref, kref, vref = llama_cpu.decoder_layer_decode(*args)
-    ref16, _, _ = llama_cpu.decoder_layer_decode(*args, step=llama_cpu.stepwise(bf), fused=fused)
+    ref16, _, _ = llama_cpu.decoder_layer_decode(*args, step=llama_cpu.stepwise(bf), fused=bool(fused), fused_gate_up=fused == "step")
     lay = L.DecoderLayer(cfg, w, dtype=bf, device=DEV)
-    lay.fused_attention = fused
+    lay.fused_attention = bool(fused)
+    lay.fused_decode = fused == "step"
     kd, vd = kc.to(bf).to(DEV), vc.to(bf).to(DEV)
     y = lay.decode(x.to(bf).to(DEV), kd, vd, pos)
     torch.cuda.synchronize()
@@ -217,7 +218,7 @@ def test_c3_prefill_layer_at_the_benchmarked_shape(pkg, mode):
         _check_layer(y[rows], ref16, ref32, 1e-2)   # a whole layer at this size: 1e-2 against the op-by-op bf16 CPU path
 
 
-@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("fused", [False, True, "step"])
 def test_c4_decode_layer_at_the_benchmarked_shape(pkg, fused):
     """Llama-2-7B-shaped layer in decode, batch 64, KV length 4096 (the shape bench.py times), against the oracle on four of
     the 64 sequences (first, two inner, last); the cache slots other than the appended one stay untouched."""
@@ -237,12 +238,13 @@ def test_c4_decode_layer_at_the_benchmarked_shape(pkg, fused):
     before = kc[pick, :, : pos].clone()
     lay = L.DecoderLayer(cfg, wd, dtype=bf, device=DEV)
     del wd
-    lay.fused_attention = fused
+    lay.fused_attention = bool(fused)
+    lay.fused_decode = fused == "step"   # merged q/k/v projection, rotary + append, add + RMSNorm, SwiGLU in the GEMM epilogue
     y = lay.decode(x, kc, vc, pos)
     torch.cuda.synchronize()
     assert pkg.diopi.gemm_status() == 0
     ref32, kref, _ = llama_cpu.decoder_layer_decode(cfg, wh, xh, kh, vh, pos)
-    ref16, _, _ = llama_cpu.decoder_layer_decode(cfg, wh, xh, kh, vh, pos, step=llama_cpu.stepwise(bf), fused=fused)
+    ref16, _, _ = llama_cpu.decoder_layer_decode(cfg, wh, xh, kh, vh, pos, step=llama_cpu.stepwise(bf), fused=bool(fused), fused_gate_up=fused == "step")
     _check_layer(y[pick], ref16, ref32, 5e-3)
     ka, _ = _err(kc[pick, :, pos], kref[:, :, pos])
     assert ka <= 2e-2 * max(1.0, kref[:, :, pos].abs().max().item())   # rotated keys reach several units: two bf16 roundings

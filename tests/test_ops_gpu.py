@@ -531,6 +531,90 @@ def test_rope_matches_golden_both_layouts(diopi, ctx):
     np.testing.assert_allclose(o.cpu().numpy(), r["q_out"], rtol=1e-5, atol=1e-6)
 
 
+# ---- fused steps of a decode iteration (include/diopi/functions_b200.h) -----------------------------------------------------
+@pytest.mark.parametrize("rows,cols", [(1, 4096), (64, 4096), (7, 512), (33, 8192)])
+def test_add_rmsnorm_equals_the_two_calls(diopi, ctx, rows, cols):
+    """diopiB200AddRMSNorm against diopiAdd followed by diopiRMSNorm: the same bits (it rounds where they round)."""
+    x, r = rnd((rows, cols), torch.bfloat16, seed=rows), rnd((rows, cols), torch.bfloat16, seed=rows + 1)
+    w = (1.0 + 0.1 * rnd((cols,), seed=2)).to(torch.bfloat16)
+    xd, rd, wd = x.to(DEV), r.to(DEV), w.to(DEV)
+    s1, n1 = torch.empty_like(xd), torch.empty_like(xd)
+    diopi.diopiAdd(ctx, s1, xd, rd, 1)
+    diopi.diopiRMSNorm(ctx, n1, None, s1, [cols], wd, None, 1e-6)
+    s2, n2 = torch.empty_like(xd), torch.empty_like(xd)
+    diopi.diopiB200AddRMSNorm(ctx, s2, n2, xd, rd, wd, 1e-6)
+    assert torch.equal(s2, s1)
+    assert torch.equal(s2.cpu(), (x.float() + r.float()).to(torch.bfloat16))
+    sf = s1.float().cpu()
+    check_bf16(n2, sf * torch.rsqrt(sf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float())
+    assert (n2.float() - n1.float()).abs().max().item() <= 2 ** -6 * n1.float().abs().max().item()   # at most one bf16 step apart
+    # inputs that are row slices of wider tensors, no weight
+    wide = rnd((rows, cols + 64), torch.bfloat16, seed=9).to(DEV)
+    diopi.diopiB200AddRMSNorm(ctx, s2, n2, wide[:, :cols], rd, None, 1e-6)
+    sf = (wide[:, :cols].float() + rd.float()).to(torch.bfloat16).float().cpu()
+    assert torch.equal(s2.float().cpu(), sf)
+    check_bf16(n2, sf * torch.rsqrt(sf.pow(2).mean(-1, keepdim=True) + 1e-6))
+
+
+@pytest.mark.parametrize("b,hq,hk,table_rows", [(4, 8, 8, 1), (64, 32, 32, 1), (6, 8, 2, 6), (3, 4, 1, 1)])
+def test_rope_append_kv_equals_the_separate_calls(diopi, ctx, b, hq, hk, table_rows):
+    """diopiB200RopeAppendKV against diopiRotaryEmbedding on q and k plus the two cache copies: the same bits, and nothing but
+    slot `position` of the caches changes."""
+    d, cap, pos = 128, 40, 17
+    qkv = rnd((b, (hq + 2 * hk) * d), torch.bfloat16, seed=b)
+    cos, sin = _tables(d, 64)
+    cos, sin = cos[5:5 + table_rows].contiguous(), sin[5:5 + table_rows].contiguous()
+    kc, vc = rnd((b, hk, cap, d), torch.bfloat16, seed=3), rnd((b, hk, cap, d), torch.bfloat16, seed=4)
+    qd, kd, vd = qkv.to(DEV), kc.to(DEV), vc.to(DEV)
+    q_out = torch.empty((b, hq, d), dtype=torch.bfloat16, device=DEV)
+    diopi.diopiB200RopeAppendKV(ctx, q_out, qd, cos.to(DEV), sin.to(DEV), kd, vd, pos)
+    q_in = qd[:, : hq * d].reshape(b, hq, d).contiguous()
+    k_in = qd[:, hq * d:(hq + hk) * d].reshape(b, hk, d).contiguous()
+    v_in = qkv[:, (hq + hk) * d:].reshape(b, hk, d)
+    q_ref, k_ref = torch.empty_like(q_in), torch.empty_like(k_in)
+    diopi.diopiRotaryEmbedding(ctx, q_ref, q_in, cos.to(DEV), sin.to(DEV), False, False)
+    diopi.diopiRotaryEmbedding(ctx, k_ref, k_in, cos.to(DEV), sin.to(DEV), False, False)
+    assert torch.equal(q_out, q_ref)
+    assert torch.equal(kd[:, :, pos], k_ref)
+    assert torch.equal(vd[:, :, pos].cpu(), v_in)
+    keep = torch.ones(cap, dtype=torch.bool)
+    keep[pos] = False
+    assert torch.equal(kd.cpu()[:, :, keep], kc[:, :, keep]) and torch.equal(vd.cpu()[:, :, keep], vc[:, :, keep])
+    # against the CPU arithmetic
+    reps = b // table_rows
+    c_, s_ = cos.repeat(reps, 1).view(b, 1, d // 2), sin.repeat(reps, 1).view(b, 1, d // 2)
+    qf = q_in.float().cpu()
+    x0, x1 = qf[..., : d // 2], qf[..., d // 2:]
+    check_bf16(q_out, torch.cat((x0 * c_ - x1 * s_, x0 * s_ + x1 * c_), -1))
+    with pytest.raises(diopi.DiopiError):
+        diopi.diopiB200RopeAppendKV(ctx, q_out, qd, cos.to(DEV), sin.to(DEV), kd, vd, cap)   # no such slot
+
+
+@pytest.mark.parametrize("m,k,f", [(64, 4096, 11008), (1, 512, 1376), (128, 1024, 344), (5, 264, 72)])
+def test_mm_swiglu_against_the_separate_calls(diopi, ctx, m, k, f):
+    """diopiB200MmSwiGLU over the interleaved gate / up weight against fp32 CPU (stated tolerance) and against the op-by-op
+    device sequence mm, mm, silu, mul (which rounds four times where the fused form rounds once)."""
+    x = rnd((m, k), torch.bfloat16, seed=m)
+    w1, w3 = rnd((f, k), torch.bfloat16, seed=1, scale=k ** -0.5), rnd((f, k), torch.bfloat16, seed=2, scale=k ** -0.5)
+    w13 = torch.stack([w1, w3], dim=1).reshape(2 * f, k).contiguous()
+    xd = x.to(DEV)
+    out = torch.empty((m, f), dtype=torch.bfloat16, device=DEV)
+    diopi.diopiB200MmSwiGLU(ctx, out, xd, w13.to(DEV).t())
+    g, u = x.float() @ w1.float().t(), x.float() @ w3.float().t()
+    want = torch.nn.functional.silu(g) * u
+    check_bf16(out, want, max_abs=2e-2 * max(1.0, want.abs().max().item()))   # outputs reach |10|: the bound follows the magnitude
+    gd, ud = torch.empty((m, f), dtype=torch.bfloat16, device=DEV), torch.empty((m, f), dtype=torch.bfloat16, device=DEV)
+    diopi.diopiMm(ctx, gd, xd, w1.to(DEV).t())
+    diopi.diopiMm(ctx, ud, xd, w3.to(DEV).t())
+    diopi.diopiSiluInp(ctx, gd)
+    diopi.diopiMulInp(ctx, gd, ud)
+    step = gd.float().cpu()
+    check_bf16(out, step, max_abs=3 * 2.0 ** -8 * max(1.0, step.abs().max().item()), rel_l2=5e-3)   # a few bf16 steps at the largest magnitude
+    assert diopi.gemm_status() == 0
+    with pytest.raises(diopi.DiopiError):
+        diopi.diopiB200MmSwiGLU(ctx, torch.empty((200, f), dtype=torch.bfloat16, device=DEV), rnd((200, k), torch.bfloat16).to(DEV), w13.to(DEV).t())
+
+
 def test_error_reporting(diopi, ctx):
     a = torch.empty((3, 4), device=DEV)
     b = torch.empty((5, 4), device=DEV)
