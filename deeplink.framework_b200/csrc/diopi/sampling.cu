@@ -562,34 +562,31 @@ __global__ void __launch_bounds__(256) race_keys_kernel(const void* probs, diopi
 }
 
 // ---- tensor indexing -------------------------------------------------------------------------------------------------------------
-// self[i_0, ..., i_{m-1}, ...] with m int64 index tensors broadcast to one shape S: element (s, r) of the result (s in S,
-// r in the remaining dimensions) is self[i_0[s], ..., i_{m-1}[s], r]. Negative indices wrap; out-of-range ones are skipped.
+// self[e_0, ..., e_{k-1}] where every e_d is an int64 index tensor, a boolean mask (which stands for as many index tensors as it
+// has dimensions: the coordinates of its true elements, in row-major order) or "all of this dimension" (NULL; also every
+// dimension after the last entry). The index tensors broadcast to one shape S. As in torch, S takes the place of the indexed
+// dimensions when they are adjacent, and goes first when they are not. Negative indices wrap; out-of-range ones are skipped.
 struct IndexIter {
-    int nidx, ns, nrest;                 // index tensors, dimensions of S, remaining dimensions of self
-    int64_t numel;                       // |S| * |rest|
-    int64_t rest_numel;
+    int nidx, ns, nout;                  // index tensors, dimensions of S, dimensions of the result
+    int64_t numel;                       // elements of the result
     int64_t s_shape[kMaxDims];
     int64_t idx_stride[kMaxDims][kMaxDims];  // [index tensor][dimension of S], 0 where broadcast
     const int64_t* idx_ptr[kMaxDims];
     int64_t self_idx_stride[kMaxDims], self_idx_size[kMaxDims];
-    int64_t rest_shape[kMaxDims], rest_stride[kMaxDims];
+    int64_t out_shape[kMaxDims];
+    int64_t out_self_stride[kMaxDims];   // kept dimensions: the stride in self
+    int out_s_dim[kMaxDims];             // dimensions of S: which one; -1 for a kept dimension
 };
 
 __device__ __forceinline__ bool index_offset(const IndexIter& it, int64_t i, int64_t* self_off) {
-    const int64_t sidx = i / it.rest_numel;
-    int64_t r = i - sidx * it.rest_numel;
-    int64_t off = 0;
-    for (int d = it.nrest - 1; d >= 0; --d) {
-        const int64_t q = r / it.rest_shape[d];
-        off += (r - q * it.rest_shape[d]) * it.rest_stride[d];
-        r = q;
-    }
     int64_t coord[kMaxDims];
-    int64_t rem = sidx;
-    for (int d = it.ns - 1; d >= 0; --d) {
-        const int64_t q = rem / it.s_shape[d];
-        coord[d] = rem - q * it.s_shape[d];
+    int64_t off = 0, rem = i;
+    for (int d = it.nout - 1; d >= 0; --d) {
+        const int64_t q = rem / it.out_shape[d];
+        const int64_t c = rem - q * it.out_shape[d];
         rem = q;
+        if (it.out_s_dim[d] >= 0) coord[it.out_s_dim[d]] = c;
+        else off += c * it.out_self_stride[d];
     }
     for (int t = 0; t < it.nidx; ++t) {
         int64_t io = 0;
@@ -601,6 +598,58 @@ __device__ __forceinline__ bool index_offset(const IndexIter& it, int64_t i, int
     }
     *self_off = off;
     return true;
+}
+
+// Coordinates of the true elements of a mask, in row-major order: coords[d * capacity + n] is coordinate d of the n-th true
+// element; *count receives their number. One CTA walks the mask in chunks of its width with a block-wide scan per chunk
+// (index masks are small; the order of the result is what matters).
+struct MaskDesc {
+    const uint8_t* data;
+    int ndim;
+    int64_t numel;
+    int64_t shape[kMaxDims], stride[kMaxDims];
+};
+__global__ void __launch_bounds__(1024) mask_nonzero_kernel(const MaskDesc m, int64_t* coords, int64_t capacity, int64_t* count) {
+    __shared__ int warp_tot[32];
+    __shared__ int64_t base;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) base = 0;
+    __syncthreads();
+    for (int64_t c0 = 0; c0 < m.numel; c0 += blockDim.x) {
+        const int64_t i = c0 + threadIdx.x;
+        int64_t cd[kMaxDims];
+        int flag = 0;
+        if (i < m.numel) {
+            int64_t off = 0, rem = i;
+            for (int d = m.ndim - 1; d >= 0; --d) {
+                const int64_t q = rem / m.shape[d];
+                cd[d] = rem - q * m.shape[d];
+                off += cd[d] * m.stride[d];
+                rem = q;
+            }
+            flag = m.data[off] != 0 ? 1 : 0;
+        }
+        int incl = flag;
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (lane == 31) warp_tot[warp] = incl;
+        __syncthreads();
+        int before = 0, total = 0;
+        for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) {
+            if (w < warp) before += warp_tot[w];
+            total += warp_tot[w];
+        }
+        if (flag) {
+            const int64_t n = base + before + incl - 1;
+            for (int d = 0; d < m.ndim; ++d) coords[d * capacity + n] = cd[d];
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) base += total;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *count = base;
 }
 
 __global__ void __launch_bounds__(256) index_get_kernel(const void* self, int itemsize, void* out, const IndexIter it) {
@@ -630,33 +679,115 @@ __global__ void __launch_bounds__(256) index_put_kernel(T* self, const T* values
     }
 }
 
-// Fills an IndexIter from the index handles; returns false (with the error string set) when the case is not supported.
-bool build_index_iter(const char* name, const TensorView& self, diopiConstTensorHandle_t* indices, int64_t nums, std::vector<TensorView>* idx_views,
+// Fills an IndexIter from the index handles (NULL = the whole dimension, boolean masks are turned into the coordinates of
+// their true elements first - this reads their count back and therefore synchronises the stream). Returns false with the error
+// string set when the indices do not fit the tensor.
+bool build_index_iter(diopiContextHandle_t ctx, const char* name, const TensorView& self, diopiConstTensorHandle_t* indices, int64_t nums,
                       IndexIter* it) {
-    if (nums < 1 || nums > self.ndim) {
-        set_last_error("%s: %lld index tensors for a %d-dimensional tensor", name, static_cast<long long>(nums), self.ndim);
+    if (nums < 0 || nums > kMaxDims) {
+        set_last_error("%s: %lld index entries", name, static_cast<long long>(nums));
         return false;
     }
-    idx_views->resize(static_cast<size_t>(nums));
-    int ns = 0;
+    // one entry per dimension of self: an int64 index tensor (as a view) or nothing
+    TensorView entry[kMaxDims];
+    bool has[kMaxDims] = {false};
+    int dim = 0;
+    cudaStream_t stream = stream_of(ctx);
     for (int64_t t = 0; t < nums; ++t) {
         if (indices[t] == nullptr) {
-            set_last_error("%s: skipped dimensions (None / ':' before an index tensor) are not supported", name);
+            if (dim >= self.ndim) {
+                set_last_error("%s: too many indices for a %d-dimensional tensor", name, self.ndim);
+                return false;
+            }
+            ++dim;
+            continue;
+        }
+        TensorView v;
+        if (!make_view(indices[t], &v, "index")) return false;
+        if (v.device != diopi_device) {
+            set_last_error("%s: index tensors must be device tensors", name);
             return false;
         }
-        if (!make_view(indices[t], &(*idx_views)[t], "index")) return false;
-        const TensorView& v = (*idx_views)[t];
-        if (v.dtype != diopi_dtype_int64 || v.device != diopi_device) {
-            set_last_error("%s: index tensors must be int64 device tensors (boolean masks are not supported)", name);
+        if (v.dtype == diopi_dtype_int64) {
+            if (dim >= self.ndim) {
+                set_last_error("%s: too many indices for a %d-dimensional tensor", name, self.ndim);
+                return false;
+            }
+            entry[dim] = v;
+            has[dim++] = true;
+            continue;
+        }
+        if (v.dtype != diopi_dtype_bool && v.dtype != diopi_dtype_uint8) {
+            set_last_error("%s: index tensors must be int64 tensors or boolean masks (got %s)", name, dtype_name(v.dtype));
             return false;
         }
-        ns = v.ndim > ns ? v.ndim : ns;
+        // a mask of m dimensions indexes m dimensions of self with the coordinates of its true elements
+        const int m = v.ndim == 0 ? 1 : v.ndim;
+        if (dim + m > self.ndim) {
+            set_last_error("%s: too many indices for a %d-dimensional tensor", name, self.ndim);
+            return false;
+        }
+        for (int d = 0; d < v.ndim; ++d) {
+            if (v.shape[d] != self.shape[dim + d]) {
+                set_last_error("%s: the mask's shape does not match the indexed dimensions", name);
+                return false;
+            }
+        }
+        int64_t count = 0;
+        int64_t* coords = nullptr;
+        const int64_t capacity = v.numel > 0 ? v.numel : 1;
+        if (v.numel > 0) {
+            diopiTensorHandle_t ws = nullptr;
+            void* wsp = nullptr;
+            if (diopiRequireBuffer(ctx, &ws, (static_cast<int64_t>(m) * capacity + 1) * 8, diopi_device) != diopiSuccess || ws == nullptr ||
+                diopiGetTensorData(ws, &wsp) != diopiSuccess || wsp == nullptr) {
+                set_last_error("%s: workspace allocation for a mask failed", name);
+                return false;
+            }
+            coords = static_cast<int64_t*>(wsp);
+            MaskDesc md;
+            md.data = static_cast<const uint8_t*>(v.data);
+            md.ndim = v.ndim;
+            md.numel = v.numel;
+            for (int d = 0; d < v.ndim; ++d) { md.shape[d] = v.shape[d]; md.stride[d] = v.stride[d]; }
+            mask_nonzero_kernel<<<1, 1024, 0, stream>>>(md, coords, capacity, coords + static_cast<int64_t>(m) * capacity);
+            if (cudaMemcpyAsync(&count, coords + static_cast<int64_t>(m) * capacity, 8, cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+                cudaStreamSynchronize(stream) != cudaSuccess) {
+                (void)cudaGetLastError();
+                set_last_error("%s: reading a mask's element count failed", name);
+                return false;
+            }
+        }
+        for (int d = 0; d < m; ++d) {
+            TensorView c;
+            c.data = coords != nullptr ? static_cast<void*>(coords + static_cast<int64_t>(d) * capacity) : nullptr;
+            c.dtype = diopi_dtype_int64;
+            c.device = diopi_device;
+            c.itemsize = 8;
+            c.ndim = 1;
+            c.shape[0] = count;
+            c.stride[0] = 1;
+            c.numel = count;
+            c.defined = true;
+            entry[dim] = c;
+            has[dim++] = true;
+        }
     }
-    it->nidx = static_cast<int>(nums);
+    // broadcast shape S of the index tensors
+    int ns = 0, nidx = 0, first = -1, last = -1;
+    for (int d = 0; d < self.ndim; ++d) {
+        if (!has[d]) continue;
+        ns = entry[d].ndim > ns ? entry[d].ndim : ns;
+        if (first < 0) first = d;
+        last = d;
+        ++nidx;
+    }
+    it->nidx = nidx;
     it->ns = ns;
     for (int d = 0; d < ns; ++d) it->s_shape[d] = 1;
-    for (int64_t t = 0; t < nums; ++t) {
-        const TensorView& v = (*idx_views)[t];
+    for (int d0 = 0; d0 < self.ndim; ++d0) {
+        if (!has[d0]) continue;
+        const TensorView& v = entry[d0];
         for (int d = 0; d < v.ndim; ++d) {
             const int sd = ns - v.ndim + d;
             if (v.shape[d] != 1) {
@@ -668,24 +799,56 @@ bool build_index_iter(const char* name, const TensorView& self, diopiConstTensor
             }
         }
     }
-    int64_t s_numel = 1;
-    for (int d = 0; d < ns; ++d) s_numel *= it->s_shape[d];
-    for (int64_t t = 0; t < nums; ++t) {
-        const TensorView& v = (*idx_views)[t];
-        for (int d = 0; d < ns; ++d) it->idx_stride[t][d] = 0;
-        for (int d = 0; d < v.ndim; ++d) it->idx_stride[t][ns - v.ndim + d] = v.shape[d] == 1 ? 0 : v.stride[d];
+    int t = 0;
+    bool adjacent = true;
+    for (int d = 0; d < self.ndim; ++d) {
+        if (!has[d]) {
+            if (first >= 0 && d > first && d < last) adjacent = false;
+            continue;
+        }
+        const TensorView& v = entry[d];
+        for (int k = 0; k < ns; ++k) it->idx_stride[t][k] = 0;
+        for (int k = 0; k < v.ndim; ++k) it->idx_stride[t][ns - v.ndim + k] = v.shape[k] == 1 ? 0 : v.stride[k];
         it->idx_ptr[t] = static_cast<const int64_t*>(v.data);
-        it->self_idx_stride[t] = self.stride[t];
-        it->self_idx_size[t] = self.shape[t];
+        it->self_idx_stride[t] = self.stride[d];
+        it->self_idx_size[t] = self.shape[d];
+        ++t;
     }
-    it->nrest = self.ndim - static_cast<int>(nums);
-    it->rest_numel = 1;
-    for (int d = 0; d < it->nrest; ++d) {
-        it->rest_shape[d] = self.shape[nums + d];
-        it->rest_stride[d] = self.stride[nums + d];
-        it->rest_numel *= it->rest_shape[d];
+    // result dimensions: kept dimensions before the indexed ones, S, kept dimensions after - or S first when the indexed
+    // dimensions are not adjacent
+    int nout = 0;
+    auto put_kept = [&](int d) {
+        it->out_shape[nout] = self.shape[d];
+        it->out_self_stride[nout] = self.stride[d];
+        it->out_s_dim[nout++] = -1;
+    };
+    auto put_s = [&]() {
+        for (int k = 0; k < ns; ++k) {
+            it->out_shape[nout] = it->s_shape[k];
+            it->out_self_stride[nout] = 0;
+            it->out_s_dim[nout++] = k;
+        }
+    };
+    const int kept = self.ndim - nidx;
+    if (kept + ns > kMaxDims) {
+        set_last_error("%s: the result has too many dimensions", name);
+        return false;
     }
-    it->numel = s_numel * it->rest_numel;
+    if (nidx == 0) {
+        for (int d = 0; d < self.ndim; ++d) put_kept(d);
+    } else if (adjacent) {
+        for (int d = 0; d < first; ++d) put_kept(d);
+        put_s();
+        for (int d = last + 1; d < self.ndim; ++d) put_kept(d);
+    } else {
+        put_s();
+        for (int d = 0; d < self.ndim; ++d) {
+            if (!has[d]) put_kept(d);
+        }
+    }
+    it->nout = nout;
+    it->numel = 1;
+    for (int d = 0; d < nout; ++d) it->numel *= it->out_shape[d];
     return true;
 }
 
@@ -877,14 +1040,11 @@ diopiError_t diopiMultinomial(diopiContextHandle_t ctx, diopiTensorHandle_t out,
 diopiError_t diopiIndex(diopiContextHandle_t ctx, diopiTensorHandle_t* out, diopiConstTensorHandle_t input, diopiConstTensorHandle_t* indices, int64_t nums) {
     B200_CHECK(out != nullptr && indices != nullptr, "diopiIndex: null argument");
     B200_VIEW(vx, input);
-    std::vector<TensorView> idx;
     IndexIter it;
-    if (!build_index_iter("diopiIndex", vx, indices, nums, &idx, &it)) return diopiErrorOccurred;
+    if (!build_index_iter(ctx, "diopiIndex", vx, indices, nums, &it)) return diopiErrorOccurred;
     int64_t shape[kMaxDims];
-    int nd = 0;
-    B200_CHECK(it.ns + it.nrest <= kMaxDims, "diopiIndex: result has too many dimensions");
-    for (int d = 0; d < it.ns; ++d) shape[nd++] = it.s_shape[d];
-    for (int d = 0; d < it.nrest; ++d) shape[nd++] = it.rest_shape[d];
+    const int nd = it.nout;
+    for (int d = 0; d < nd; ++d) shape[d] = it.out_shape[d];
     diopiSize_t size;
     size.data = shape;
     size.len = nd;
@@ -904,20 +1064,16 @@ diopiError_t diopiIndexPutInp(diopiContextHandle_t ctx, diopiTensorHandle_t inpu
     B200_VIEW(vx, input);
     B200_VIEW(vv_raw, values);
     B200_CHECK(vv_raw.dtype == vx.dtype, "diopiIndexPutInp: values must have the tensor's dtype");
-    std::vector<TensorView> idx;
     IndexIter it;
-    if (!build_index_iter("diopiIndexPutInp", vx, indices, nums, &idx, &it)) return diopiErrorOccurred;
+    if (!build_index_iter(ctx, "diopiIndexPutInp", vx, indices, nums, &it)) return diopiErrorOccurred;
     if (it.numel == 0) return diopiSuccess;
     // values broadcast to S + rest, materialised dense (a scalar or a row is the common case and tiny)
     TensorView target;
     target.dtype = vx.dtype;
     target.itemsize = vx.itemsize;
     target.device = diopi_device;
-    target.ndim = it.ns + it.nrest;
-    B200_CHECK(target.ndim <= kMaxDims, "diopiIndexPutInp: too many dimensions");
-    int nd = 0;
-    for (int d = 0; d < it.ns; ++d) target.shape[nd++] = it.s_shape[d];
-    for (int d = 0; d < it.nrest; ++d) target.shape[nd++] = it.rest_shape[d];
+    target.ndim = it.nout;
+    for (int d = 0; d < it.nout; ++d) target.shape[d] = it.out_shape[d];
     int64_t st = 1;
     for (int d = target.ndim - 1; d >= 0; --d) {
         target.stride[d] = st;

@@ -222,9 +222,9 @@ def _bind(name):
                 keep.append(arr)
                 cargs.append(_Size(ctypes.cast(arr, ctypes.POINTER(ctypes.c_int64)), len(vals)))
             elif c == "L":
-                hs = [handle(x) for x in a]
+                hs = [None if x is None else handle(x) for x in a]   # None: an absent optional tensor (NULL handle)
                 keep.append(hs)
-                arr = (ctypes.c_void_p * max(len(hs), 1))(*[h.ptr for h in hs])
+                arr = (ctypes.c_void_p * max(len(hs), 1))(*[None if h is None else h.ptr for h in hs])
                 keep.append(arr)
                 cargs += [arr, len(hs)]
             elif c == "I":
@@ -286,8 +286,8 @@ def diopiIndex(ctx, self_tensor, indices):
     fn = _lib.diopiIndex
     fn.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int64]
     fn.restype = ctypes.c_int
-    hs = [handle(x) for x in indices]
-    arr = (ctypes.c_void_p * max(len(hs), 1))(*[h.ptr for h in hs])
+    hs = [None if x is None else handle(x) for x in indices]   # None: the whole dimension (torch's `:` before an index)
+    arr = (ctypes.c_void_p * max(len(hs), 1))(*[None if h is None else h.ptr for h in hs])
     out = ctypes.c_void_p()
     hself = handle(self_tensor)
     rc = fn(ctx.ptr, ctypes.byref(out), hself.ptr, arr, len(hs))

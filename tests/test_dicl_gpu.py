@@ -27,7 +27,7 @@ def test_collectives_and_tp_layer(world):
         outs = []
         for p in procs:
             try:
-                out, _ = p.communicate(timeout=360)
+                out, _ = p.communicate(timeout=240)
             except subprocess.TimeoutExpired:
                 p.kill()  # the exact child started above
                 out, _ = p.communicate()
@@ -48,7 +48,7 @@ def test_c10d_backend(world):
     outs = []
     for p in procs:
         try:
-            out, _ = p.communicate(timeout=360)
+            out, _ = p.communicate(timeout=240)
         except subprocess.TimeoutExpired:
             p.kill()  # the exact child started above
             out, _ = p.communicate()

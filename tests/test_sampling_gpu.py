@@ -194,6 +194,66 @@ def test_multinomial_without_replacement(diopi, ctx):
     assert (first - w[0] / w.sum()).abs().max().item() < 0.03
 
 
+def test_index_masks_skipped_dimensions_and_empty_cases(diopi, ctx):
+    """The cases of dipu/tests/python/unittests/test_index.py:8-63: index tensors on several leading dimensions, on inner
+    dimensions (`x[..., i, ...]`), boolean masks (alone, mixed with index tensors, of several dimensions), non-adjacent
+    indexed dimensions (S goes first), empty index tensors and an empty input - each against torch's own indexing."""
+    def idx(x, *entries):
+        got = diopi.diopiIndex(ctx, x.to(DEV), [None if e is None else e.to(DEV) for e in entries])
+        torch.cuda.synchronize()
+        ctx.release_workspace()
+        return got.cpu()
+
+    x = _rand((3, 4, 5, 6), seed=21)
+    i = torch.arange(0, 3)
+    assert torch.equal(idx(x, i), x[i])
+    assert torch.equal(idx(x, i, i), x[i, i])
+    assert torch.equal(idx(x, i, i, i), x[i, i, i])
+    assert torch.equal(idx(x, i, i, i, i), x[i, i, i, i])
+    assert torch.equal(idx(x, None, i), x[:, i])                       # an inner dimension
+    assert torch.equal(idx(x, None, None, torch.tensor([4, 0, 0])), x[:, :, torch.tensor([4, 0, 0])])
+    assert torch.equal(idx(x, i, None, i), x[i, :, i])                  # not adjacent: S first
+    assert torch.equal(idx(x, torch.tensor([[0], [2]]), None, None, torch.tensor([1, 5, 5])), x[torch.tensor([[0], [2]]), :, :, torch.tensor([1, 5, 5])])
+    # test_index_bool
+    inp = torch.arange(16).reshape(4, 2, 2)
+    i1, i2, m3 = torch.tensor([2]), torch.tensor([1]), torch.tensor([False, True])
+    assert torch.equal(idx(inp, i1), inp[i1])
+    assert torch.equal(idx(inp, i1, i2), inp[i1, i2])
+    assert torch.equal(idx(inp, None, i2), inp[..., i2, :])
+    assert torch.equal(idx(inp, i1, i2, m3), inp[i1, i2, m3])
+    assert torch.equal(idx(inp, i1, None, m3), inp[i1, ..., m3])
+    m = _rand((4, 2, 2), seed=5) > 0
+    assert torch.equal(idx(inp, m), inp[m])                             # a mask over all dimensions
+    assert torch.equal(idx(inp, m[:, :, 0]), inp[m[:, :, 0]])           # over the two leading ones (a strided mask)
+    assert torch.equal(idx(inp, None, m[0]), inp[:, m[0]])              # over the two trailing ones
+    assert torch.equal(idx(inp, torch.zeros(4, dtype=torch.bool)), inp[torch.zeros(4, dtype=torch.bool)])   # nothing selected
+    big = _rand((3000, 7), seed=6)
+    bm = big[:, 0] > 0.3
+    assert torch.equal(idx(big, bm), big[bm])                           # several chunks of the compaction
+    # test_index_empty_index / test_index_empty_input
+    e3, e1 = torch.empty((0, 3), dtype=torch.long), torch.empty((0, 1), dtype=torch.long)
+    assert idx(inp, e3).shape == inp[e3].shape == (0, 3, 2, 2)
+    assert idx(inp, e3, e1).shape == inp[e3, e1].shape
+    empty = torch.tensor([])
+    assert idx(empty, torch.tensor([], dtype=torch.bool)).shape == (0,)
+    # index_put_ through a mask and through an inner dimension
+    y = _rand((5, 6), seed=8)
+    mk = y > 0
+    yd = y.to(DEV)
+    diopi.diopiIndexPutInp(ctx, yd, torch.tensor(0.0).to(DEV), [mk.to(DEV)], False)
+    torch.cuda.synchronize()
+    want = y.clone()
+    want[mk] = 0.0
+    assert torch.equal(yd.cpu(), want)
+    vals = _rand((5, 2), seed=9)
+    diopi.diopiIndexPutInp(ctx, yd, vals.to(DEV), [None, torch.tensor([5, 1]).to(DEV)], False)
+    torch.cuda.synchronize()
+    want[:, torch.tensor([5, 1])] = vals
+    assert torch.equal(yd.cpu(), want)
+    with pytest.raises(diopi.DiopiError):
+        diopi.diopiIndex(ctx, inp.to(DEV), [torch.ones(3, dtype=torch.bool).to(DEV)])   # mask of the wrong length
+
+
 def test_index_and_index_put(diopi, ctx):
     x = _rand((10, 6, 4), seed=11)
     i0 = torch.tensor([0, 9, -1, 3, 3])
@@ -224,8 +284,10 @@ def test_index_and_index_put(diopi, ctx):
     diopi.diopiIndexPutInp(ctx, ld, torch.tensor(float("-inf"), dtype=torch.bfloat16, device=DEV), [rows.to(DEV), toks.to(DEV)], False)
     logits[rows, toks] = float("-inf")
     assert torch.equal(ld.cpu(), logits)
-    with pytest.raises(diopi.DiopiError, match="boolean masks"):
-        diopi.diopiIndex(ctx, x.to(DEV), [(i0 > 0).to(DEV)])
+    with pytest.raises(diopi.DiopiError, match="mask's shape"):
+        diopi.diopiIndex(ctx, x.to(DEV), [(i0 > 0).to(DEV)])     # a mask of 5 elements over a dimension of 10
+    with pytest.raises(diopi.DiopiError, match="int64 tensors or boolean masks"):
+        diopi.diopiIndex(ctx, x.to(DEV), [i0.to(torch.int32).to(DEV)])
     ctx.release_workspace()
 
 
