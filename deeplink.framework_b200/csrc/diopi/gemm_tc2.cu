@@ -39,7 +39,7 @@ constexpr int BN = 256;      // tile columns (128 of them staged per CTA)
 constexpr int BNH = BN / 2;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int kThreads = 192;
+constexpr int kThreads = 192;      // 4 epilogue warps; the EPI = 8 instantiation runs 320
 constexpr int kGroupM = 8;   // in units of 256-row pair blocks
 constexpr int kABytes = BM * BK * 2;
 constexpr int kBBytes = BNH * BK * 2;
@@ -112,8 +112,12 @@ __device__ __forceinline__ void pair_tile_coords(int tile, const PairParams& p, 
     *nb = r / rows;
 }
 
-template <typename TOut, bool PUSH>
-__global__ void __launch_bounds__(kThreads, 1)
+// EPI = epilogue warps per CTA: 4 (one per 32-lane quarter of tensor memory) or 8 (two per quarter, each draining half of
+// the tile's columns). A 256 x 256 tile takes the tensor cores 0.27 us per 64-deep K block and one warp per quarter about
+// 3 us to drain: with K loops of up to 8 blocks (the row-parallel shards of an 8-way tensor-parallel layer, K = 512) the
+// drain, not the product, paces the kernel unless it is spread over eight warps.
+template <typename TOut, bool PUSH, int EPI>
+__global__ void __launch_bounds__(64 + 32 * EPI, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
                     const PairParams p, const __grid_constant__ PushParams q) {
     extern __shared__ uint8_t smem_raw[];
@@ -143,7 +147,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&acc_full[a], 1);
-            mbar_init(&acc_empty[a], 8);  // 4 epilogue warps in each CTA of the pair
+            mbar_init(&acc_empty[a], 2 * EPI);  // the epilogue warps of both CTAs of the pair
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -246,7 +250,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         bool ok = true;
         constexpr int PIECE_COLS = 128 / static_cast<int>(sizeof(TOut));
         constexpr int LOADS = PIECE_COLS / 32;
-        uint8_t* stage_base = smem_c + (warp - 2) * (2 * 32 * 128);
+        // staging for the TMA store: two 4 KiB buffers per warp with four warps, one with eight (the same 32 KiB)
+        uint8_t* stage_base = smem_c + (warp - 2) * ((EPI == 4 ? 2 : 1) * 32 * 128);
+        constexpr int kPieces = BN / PIECE_COLS;
+        const int c_begin = EPI == 4 ? 0 : ((warp - 2) >> 2) * (kPieces / 2);
+        const int c_end = EPI == 4 ? kPieces : c_begin + kPieces / 2;
         for (int tile = cluster_id; tile < total_tiles && ok; tile += num_clusters, ++local) {
             int b, mp, nb;
             pair_tile_coords(tile, p, &b, &mp, &nb);
@@ -282,12 +290,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             if (row_base < p.M) {
 #pragma unroll 1
-                for (int c = 0; c < BN / PIECE_COLS; ++c) {
+                for (int c = c_begin; c < c_end; ++c) {
                     const int col0 = nb * BN + c * PIECE_COLS;
                     if (col0 >= p.N) break;  // warp-uniform
-                    uint8_t* buf = stage_base + (store_seq & 1) * (32 * 128);
+                    uint8_t* buf = stage_base + (EPI == 4 ? (store_seq & 1) * (32 * 128) : 0);
                     if constexpr (!PUSH) {
-                        if (lane == 0) tma_store_wait_read<1>();
+                        if (lane == 0) {
+                            if constexpr (EPI == 4) tma_store_wait_read<1>();
+                            else tma_store_wait_read<0>();
+                        }
                         __syncwarp();
                     }
                     uint32_t r[LOADS][32];
@@ -384,13 +395,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
-template <typename TOut, bool PUSH>
+template <typename TOut, bool PUSH, int EPI = 4>
 cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const PairParams& p, const PushParams& q, int grid,
                         cudaStream_t stream) {
-    if (cudaError_t e = tc_ensure_smem_attr(reinterpret_cast<const void*>(gemm_tc_pair_kernel<TOut, PUSH>), kSmemBytes); e != cudaSuccess) return e;
+    if (cudaError_t e = tc_ensure_smem_attr(reinterpret_cast<const void*>(gemm_tc_pair_kernel<TOut, PUSH, EPI>), kSmemBytes); e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid));
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(64 + 32 * EPI);
     cfg.dynamicSmemBytes = kSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -400,7 +411,7 @@ cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUte
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<TOut, PUSH>, ma, mb, mc, p, q);
+    return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<TOut, PUSH, EPI>, ma, mb, mc, p, q);
 }
 
 // Tensor maps of A and B and the tile geometry: shared by the storing and the pushing launch.
@@ -474,9 +485,11 @@ diopiError_t gemm_tc2_launch(const GemmProblem& g, cudaStream_t stream) {
     PushParams q = {};
     const int grid = pair_grid(p);
     cudaError_t e;
-    if (g.c_dtype == diopi_dtype_bfloat16) e = launch_pair<bf16, false>(ma, mb, mc, p, q, grid, stream);
-    else if (g.c_dtype == diopi_dtype_float16) e = launch_pair<fp16, false>(ma, mb, mc, p, q, grid, stream);
-    else e = launch_pair<float, false>(ma, mb, mc, p, q, grid, stream);
+    // short K loops: eight epilogue warps, so that draining a tile does not take longer than computing the next one
+    const bool wide_epilogue = p.k_blocks <= 8;
+    if (g.c_dtype == diopi_dtype_bfloat16) e = wide_epilogue ? launch_pair<bf16, false, 8>(ma, mb, mc, p, q, grid, stream) : launch_pair<bf16, false>(ma, mb, mc, p, q, grid, stream);
+    else if (g.c_dtype == diopi_dtype_float16) e = wide_epilogue ? launch_pair<fp16, false, 8>(ma, mb, mc, p, q, grid, stream) : launch_pair<fp16, false>(ma, mb, mc, p, q, grid, stream);
+    else e = wide_epilogue ? launch_pair<float, false, 8>(ma, mb, mc, p, q, grid, stream) : launch_pair<float, false>(ma, mb, mc, p, q, grid, stream);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
         B200_FAIL("gemm: tcgen05 pair kernel launch failed: %s", cudaGetErrorString(e));

@@ -133,10 +133,12 @@ def test_tc_split_k_single_row_block(diopi, ctx, m, n, k, nk):
 
 
 @pytest.mark.parametrize("m,n,k,nk,batch", [(2048, 4096, 512, True, 1), (3000, 2600, 264, True, 1), (2048, 4096, 320, False, 1),
-                                            (1000, 4136, 256, False, 1), (512, 512, 256, True, 40), (512, 640, 256, False, 24)])
+                                            (1000, 4136, 256, False, 1), (512, 512, 256, True, 40), (512, 640, 256, False, 24),
+                                            (2048, 4096, 1024, True, 1), (2304, 2816, 584, False, 1)])
 def test_tc_cta_pair_tiles(diopi, ctx, m, n, k, nk, batch):
     """Products large enough for the CTA-pair kernel (256 x 256 tiles over two SMs): ragged edges, both B layouts, batches,
-    scaled / biased epilogue, fp32 output."""
+    scaled / biased epilogue, fp32 output. K up to 512 takes the instantiation with eight epilogue warps per CTA (short K
+    loops), the longer ones the one with four."""
     shape_a = (batch, m, k) if batch > 1 else (m, k)
     shape_b = ((batch, n, k) if nk else (batch, k, n)) if batch > 1 else ((n, k) if nk else (k, n))
     a = rnd(shape_a, torch.bfloat16, seed=m + k)
