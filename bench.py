@@ -763,7 +763,54 @@ def run_op_sweep(diopi, ctx, device, stream, peaks):
             ctx.release_workspace()
         out["ops"][op] = rec
     torch.cuda.synchronize()
+    out["cpu"] = cpu_op_sweep(16384)
     return out
+
+
+def cpu_op_sweep(t):
+    """The same operators on the host cores at one size (the arithmetic of the reference's CPU fallback: torch CPU aten on
+    bf16-rounded inputs computed in fp32, all threads): a reported baseline beside the device figures, a few seconds of work."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = torch.Generator()
+    g.manual_seed(t)
+    h = 4096
+    x = torch.randn((t, h), generator=g).bfloat16().float()
+    y = torch.randn((t, h), generator=g).bfloat16().float()
+    w = torch.ones(h)
+    ids = torch.randint(0, VOCAB, (t,), generator=g)
+    table = torch.randn((VOCAB, h), generator=g).bfloat16()
+    inv = 1.0 / (10000.0 ** (torch.arange(0, 128, 2).float() / 128))
+    ang = torch.outer(torch.arange(t).float(), inv)
+    cos, sin = torch.cos(ang).view(t, 1, 64), torch.sin(ang).view(t, 1, 64)
+
+    def rope():
+        v = x.view(t, 32, 128)
+        a, b = v[..., :64], v[..., 64:]
+        return torch.cat((a * cos - b * sin, a * sin + b * cos), -1)
+
+    cases = {
+        "rmsnorm": lambda: x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * w,
+        "layernorm": lambda: torch.nn.functional.layer_norm(x, (h,), w, w, 1e-5),
+        "softmax": lambda: torch.softmax(x, -1),
+        "rope": rope,
+        "silu_mul": lambda: torch.nn.functional.silu(x) * y,
+        "cast_up": lambda: table[:t].float(),
+        "cast_down": lambda: x.bfloat16(),
+        "embedding": lambda: table[ids],
+        "add": lambda: x + y,
+    }
+    res = {}
+    with torch.no_grad():
+        for name, fn in cases.items():
+            fn()
+            t0 = time.perf_counter()
+            reps = 0
+            while reps < 3 or (time.perf_counter() - t0 < 0.3 and reps < 20):
+                fn()
+                reps += 1
+            res[name] = {"us": round((time.perf_counter() - t0) / reps * 1e6, 1)}
+    return {"tokens": t, "cores": cores, "kind": "port (torch CPU aten, fp32 compute on bf16-rounded inputs)", "ops": res}
 
 
 def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ranks, peaks, rank=0, dist=None, host_w=None, check=False):

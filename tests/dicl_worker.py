@@ -113,6 +113,9 @@ def main():
     # row-parallel linears with the all-reduce and the residual add fused into the kernels: tiles pushed to the owners of
     # their rows, one reduce-gather kernel per linear; against the op-by-op bf16 CPU oracle and against the NCCL path
     seq = 128 * world
+    # an FFN width whose shard stays a multiple of 8 elements at every world size up to 8 (the tensor-core kernels' pitch rule)
+    cfg = llama_cpu.LayerConfig(hidden=512, heads=8, kv_heads=8, head_dim=64, ffn=1408, eps=1e-6)
+    w = llama_cpu.make_weights(cfg, seed=79)
     idsb = llama_cpu.make_token_ids(2, seq, seed=78)
     refb = llama_cpu.decoder_layer_prefill(cfg, llama_cpu.round_weights(w, torch.bfloat16), llama_cpu.round_tensor(emb, torch.bfloat16), idsb,
                                            step=llama_cpu.stepwise(torch.bfloat16))
