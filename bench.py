@@ -290,6 +290,7 @@ def main():
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the secondary decode measurement")
+    ap.add_argument("--decode-steps", type=int, default=200, help="graph replays timed per decode variant (a quarter of it for the eager one)")
     ap.add_argument("--no-parity", action="store_true", help="skip the (untimed) comparison of every variant's output with the CPU oracle")
     ap.add_argument("--no-checks", action="store_true", help="N > 1: skip the (untimed) closed-form checks of the collectives")
     ap.add_argument("--no-op-sweep", action="store_true", help="N = 1: skip the per-op sweep of the memory-bound operators")
@@ -475,6 +476,30 @@ def main():
         x0 = x[:seq].float().cpu() if rank == 0 else None
         refs = prefill_oracle_refs(cfg, host_weights, x0, seq, rank, dist, forms)
 
+    def layerwise_parity(form, bound):
+        """Every layer of the stack (with the variant flags as they are now) against the op-by-op oracle of THAT layer on the
+        input the device layer had: rows of sequence 0, rank 0 computes, every rank compares its own copy."""
+        kw = dict(PREFILL_FORMS[form])
+        kw.pop("stepwise", None)
+        res = []
+        h = x
+        for i, l_ in enumerate(layers):
+            h_in = h[:seq].float().cpu() if rank == 0 else None
+            h = l_.prefill(h, batch, seq, ctx)
+            torch.cuda.synchronize()
+            want = torch.empty((seq, cfg.hidden), dtype=torch.float32)
+            if rank == 0:
+                from oracle import llama_cpu
+                with torch.no_grad():
+                    want = llama_cpu.decoder_layer_prefill_from_hidden(cfg, host_weights[i], h_in, 1, seq, llama_cpu.stepwise(torch.bfloat16),
+                                                                       **kw).contiguous()
+            if dist is not None:
+                dist.broadcast(want, src=0)
+            e = bench_checks.parity_entry(h[:seq], {form: (want, bound)})
+            res.append({"layer": i, "max_abs": e[form]["max_abs"], "max_abs_bound": e[form]["max_abs_bound"], "rel_l2": e[form]["rel_l2"],
+                        "rel_l2_bound": e[form]["rel_l2_bound"], "ok": e["ok"]})
+        return res
+
     def record_parity(name, y, against):
         """Rows of sequence 0 of a variant's last output against the oracle forms in `against` ({form: relative-L2 bound});
         every rank checks its own (replicated) copy."""
@@ -482,7 +507,19 @@ def main():
             return
         bf16_form = [f for f in against if f != "fp32"][0]
         bounds = {f: (b if f != "fp32" else bench_checks.fp32_bound(refs[bf16_form], refs["fp32"])) for f, b in against.items()}
-        entry = bench_checks.parity_entry(y[:seq], {f: (refs[f], bounds[f]) for f in against})
+        if len(layers) > 1:
+            # A stack: two bf16 evaluations drift apart from layer to layer (at 4 layers of the 70B shape the CPU bf16 path is
+            # itself 5.5e-2 from fp32), so the single-layer bound against the op-by-op path is applied LAYER BY LAYER, every
+            # layer's oracle fed with the input the device layer had; the whole stack is held to the fp32 bound (1.25 x the CPU
+            # bf16 path's own distance) and its distance from the op-by-op path is reported beside it.
+            entry = bench_checks.parity_entry(y[:seq], {"fp32": (refs["fp32"], bounds["fp32"])})
+            mx, rl = bench_checks.errors(y[:seq], refs[bf16_form])
+            entry[bf16_form + "_whole_stack"] = {"max_abs": round(mx, 6), "rel_l2": round(rl, 6)}
+            per_layer = layerwise_parity("bf16_stepwise_baddbmm" if "baddbmm" in name else bf16_form, against[bf16_form])
+            entry["layer_by_layer"] = per_layer
+            entry["ok"] = bool(entry["ok"] and all(e["ok"] for e in per_layer))
+        else:
+            entry = bench_checks.parity_entry(y[:seq], {f: (refs[f], bounds[f]) for f in against})
         entry["cpu_bf16_path_vs_fp32_rel_l2"] = round(bench_checks.errors(refs[bf16_form], refs["fp32"])[1], 6)
         entry["all_ranks_ok"] = all_ranks(entry["ok"], dist)
         entry["rows_checked"] = "sequence 0 (%d tokens)" % seq
@@ -650,7 +687,7 @@ def main():
     decode = None
     if not args.no_decode:
         decode = run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ranks, peaks, rank, dist,
-                            host_weights[0] if host_weights else None, not args.no_parity)
+                            host_weights[0] if host_weights else None, not args.no_parity, max(1, args.decode_steps))
         if decode.get("parity") is not None:
             parity["decode"] = decode.pop("parity")
 
@@ -813,7 +850,7 @@ def cpu_op_sweep(t):
     return {"tokens": t, "cores": cores, "kind": "port (torch CPU aten, fp32 compute on bf16-rounded inputs)", "ops": res}
 
 
-def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ranks, peaks, rank=0, dist=None, host_w=None, check=False):
+def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ranks, peaks, rank=0, dist=None, host_w=None, check=False, graph_steps=200):
     """7B-shaped layer in decode: batch 64, one new token per sequence, bf16 KV cache of length 4096 per sequence."""
     b, length = 64, 4096
     n_check = 4  # sequences whose output is compared with the CPU oracle
@@ -826,7 +863,7 @@ def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ra
     for _ in range(5):
         lay.decode(xd, kc, vc, length - 1, ctx)
     barrier()
-    steps = 50
+    steps = max(1, graph_steps // 4)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(steps):
@@ -841,7 +878,7 @@ def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ra
     for _ in range(5):
         replay()
     barrier()
-    steps = 200
+    steps = graph_steps
     e0.record(stream)
     for _ in range(steps):
         replay()
@@ -867,7 +904,7 @@ def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ra
     outs["fused_attention"] = out_g[:n_check].clone()
     devapis.graphDestroy(replay.graph)
     # variant: the whole step through the fused entry points (one q/k/v projection, rotary + cache append, add + RMSNorm,
-    # SiLU * up in the epilogue of one gate / up product): ten launches instead of nineteen
+    # SiLU * up in the epilogue of one gate / up product, the last residual add in the down projection): nine launches instead of nineteen
     lay.fused_decode = True
     for _ in range(3):
         lay.decode(xd, kc, vc, length - 1, ctx)
@@ -962,7 +999,7 @@ def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ra
             "fused_step": {"tokens_per_s": b / (ms_step * 1e-3), "ms_per_step": ms_step,
                            "hbm_frac": round((weight_bytes + kv_bytes) / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
                            "note": "as fused_attention, with one q/k/v projection, diopiB200RopeAppendKV, diopiB200AddRMSNorm and "
-                                   "diopiB200MmSwiGLU (include/diopi/functions_b200.h): ten launches per step"},
+                                   "diopiB200MmSwiGLU (include/diopi/functions_b200.h), diopiAddmm for down projection + residual: nine launches per step"},
             "fused_step_peer_all_reduce": None if ms_step_peer is None else {
                 "tokens_per_s": b / (ms_step_peer * 1e-3), "ms_per_step": ms_step_peer,
                 "note": "as fused_step, with both all-reduces done by one kernel each over peer memory"},

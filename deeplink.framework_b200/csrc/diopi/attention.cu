@@ -701,6 +701,7 @@ __device__ __forceinline__ void merge_partial(float& m_a, float& l_a, float (&ac
 
 template <typename T, int GT, int U>
 __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const DecodeParams p) {
+    grid_launch_dependents();   // the product that follows may set itself up meanwhile (gemm_tc.cu, launch_splitk)
     __shared__ float red[8][GT][130];
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -880,6 +881,7 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const DecodePa
 // Merges the key slices of one (batch, head): 128 threads, one per output column.
 template <typename T>
 __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const DecodeParams p) {
+    grid_launch_dependents();   // the product that follows may set itself up meanwhile (gemm_tc.cu, launch_splitk)
     const int bh = blockIdx.x;
     const int b = bh / p.Hq;
     const int h = bh - b * p.Hq;

@@ -7,6 +7,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "diopi/diopirt.h"
@@ -65,6 +66,13 @@ int64_t dtype_size(diopiDtype_t t);
 const char* dtype_name(diopiDtype_t t);
 
 cudaStream_t stream_of(diopiContextHandle_t ctx);
+
+// Programmatic dependent launch (the single-row-block product in gemm_tc.cu is launched that way); B200_NO_PDL in the
+// environment turns the launch attribute off.
+inline bool pdl_enabled() {
+    static const bool on = std::getenv("B200_NO_PDL") == nullptr;
+    return on;
+}
 
 // Number of SMs of the current device (cached per device).
 int sm_count();

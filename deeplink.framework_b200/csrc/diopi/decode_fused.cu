@@ -19,6 +19,9 @@ template <typename T, int VPT>
 __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ weight,
                                                            T* __restrict__ sum_out, T* __restrict__ norm_out, int cols, int64_t x_pitch,
                                                            int64_t res_pitch, float eps) {
+    // A product that follows in the stream may set itself up while this grid runs (it touches global memory only after its own
+    // griddepcontrol.wait); without such a dependent this does nothing.
+    grid_launch_dependents();
     __shared__ float red[32];
     const int nvec = cols / 8;
     const int64_t r = blockIdx.x;

@@ -173,4 +173,11 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return r;
 }
 
+// Programmatic dependent launch. A kernel launched with cudaLaunchAttributeProgrammaticStreamSerialization may start while
+// the kernel before it in the stream is still running; grid_dependency_wait() returns once that kernel has completed and its
+// writes are visible (at once when the launch carried no such attribute). grid_launch_dependents() lets a dependent kernel
+// of THIS grid be scheduled as soon as every CTA has executed it or exited (no effect without such a dependent).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 }  // namespace b200

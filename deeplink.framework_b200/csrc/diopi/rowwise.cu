@@ -24,10 +24,12 @@ struct RowCfg {
     int vpt;
 };
 
-// Picks the CTA width so that each thread owns about four vectors (enough bytes in flight per SM with many
-// resident CTAs) and never more than kMaxVpt.
-bool pick_row_cfg(int64_t nvec, RowCfg* cfg) {
-    int64_t threads = (nvec + 3) / 4;
+// Picks the CTA width so that each thread owns about `target` vectors (four: enough bytes in flight per SM with many
+// resident CTAs) and never more than kMaxVpt. The softmax keeps its share of the row as fp32 exponentials between its passes;
+// with two vectors per thread it stays within 32 registers and the SM holds its full 64 warps (rows of 4096 bf16: 0.83 -> 0.88
+// of the copy bandwidth at 16 k rows), while the norms, which re-widen the packed row instead, measured best with four.
+bool pick_row_cfg(int64_t nvec, RowCfg* cfg, int target = 4) {
+    int64_t threads = (nvec + target - 1) / target;
     threads = ((threads + 31) / 32) * 32;
     if (threads < 32) threads = 32;
     if (threads > 1024) threads = 1024;
@@ -78,6 +80,7 @@ __device__ __forceinline__ Vec16<T> vec_from_pairs(const float2 (&p)[Vec16<T>::N
 template <typename T, int VPT>
 __global__ void __launch_bounds__(1024) rmsnorm_kernel(const T* __restrict__ in, T* __restrict__ out, const T* __restrict__ weight,
                                                        const T* __restrict__ bias, void* inv_rms, diopiDtype_t inv_dt, int64_t cols, float eps) {
+    grid_launch_dependents();   // the product that follows may set itself up meanwhile (gemm_tc.cu, launch_splitk)
     constexpr int V = Vec16<T>::N;
     __shared__ float red[32];
     const int64_t nvec = cols / V;
@@ -442,11 +445,11 @@ __global__ void reduce_sum_strided_kernel(const void* in, diopiDtype_t in_dt, vo
     }
 
 // Can `v` use the register-resident row kernels for rows of `cols` elements?
-bool row_fast_ok(const TensorView& v, int64_t cols, RowCfg* cfg) {
+bool row_fast_ok(const TensorView& v, int64_t cols, RowCfg* cfg, int target = 4) {
     if (!(v.dtype == diopi_dtype_bfloat16 || v.dtype == diopi_dtype_float16 || v.dtype == diopi_dtype_float32)) return false;
     const int V = 16 / static_cast<int>(v.itemsize);
     if (cols % V != 0 || !v.aligned(16)) return false;
-    return pick_row_cfg(cols / V, cfg);
+    return pick_row_cfg(cols / V, cfg, target);
 }
 
 int64_t shape_product(diopiSize_t s) {
@@ -573,7 +576,7 @@ diopiError_t diopiSoftmax(diopiContextHandle_t ctx, diopiTensorHandle_t out, dio
     for (int d = static_cast<int>(dim) + 1; d < vx.ndim; ++d) inner *= vx.shape[d];
     cudaStream_t stream = stream_of(ctx);
     RowCfg cfg;
-    if (inner == 1 && vo.dtype == vx.dtype && row_fast_ok(vx, n, &cfg) && vo.aligned(16) && outer <= 0x7fffffffLL) {
+    if (inner == 1 && vo.dtype == vx.dtype && row_fast_ok(vx, n, &cfg, 2) && vo.aligned(16) && outer <= 0x7fffffffLL) {
         const unsigned grid = static_cast<unsigned>(outer);
         const int64_t nvec = n * vx.itemsize / 16;
         if (nvec <= 256 && outer >= 1024) {

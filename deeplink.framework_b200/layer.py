@@ -406,7 +406,7 @@ class DecoderLayer:
         return self._wqkv, self._w13
 
     def _decode_fused(self, x, k_cache, v_cache, position, ctx):
-        """The decode step with the library's fused entry points (include/diopi/functions_b200.h): ten launches instead of
+        """The decode step with the library's fused entry points (include/diopi/functions_b200.h): nine launches instead of
         nineteen. Same arithmetic as the op-by-op step except that SiLU * up is formed in fp32 from the unrounded products."""
         b, d, hq, hk = x.shape[0], self.head_dim, self.heads, self.kv_heads
         length = position + 1
@@ -427,10 +427,14 @@ class DecoderLayer:
         self._call(diopi.diopiB200AddRMSNorm, ctx, h, hn2, x, attn, self.ffn_norm, self.eps)
         g = self._empty(b, self.ffn)
         self._call(diopi.diopiB200MmSwiGLU, ctx, g, hn2, w13.t())
-        dn = self._linear(ctx, g, self.w2)
-        self._all_reduce(ctx, dn)
+        # the block's residual rides in the down projection (diopiAddmm: the sum is formed in fp32 and rounded once); under tensor
+        # parallelism rank 0 alone adds it, so that the all-reduce of the partial sums delivers the block's output
         out = self._like(x)
-        self._call(diopi.diopiAdd, ctx, out, h, dn, 1)
+        if self.tp_rank == 0:
+            self._call(diopi.diopiAddmm, ctx, out, h, g, self.w2.t(), 1.0, 1.0)
+        else:
+            self._call(diopi.diopiMm, ctx, out, g, self.w2.t())
+        self._all_reduce(ctx, out)
         ctx.release_workspace()
         return out
 

@@ -197,10 +197,15 @@ def attention_prefill(cfg, w, x, batch, seq, step=_identity, scores_by_baddbmm=F
     return step(out @ w["wo"].t())
 
 
-def feed_forward(w, x, step=_identity, fused_gate_up=False):
+def feed_forward(w, x, step=_identity, fused_gate_up=False, residual=None):
+    """residual (with fused_gate_up only): the block's residual is added to the unrounded down projection, one materialising op
+    (an addmm) instead of a product and an add. Returns the block's output then, else the feed-forward result."""
     if fused_gate_up:
         # SiLU(gate) * up as ONE materialising op over the two products (the fused gate / up projection): one rounding
-        return step(step(torch.nn.functional.silu(x @ w["w1"].t()) * (x @ w["w3"].t())) @ w["w2"].t())
+        inner = step(torch.nn.functional.silu(x @ w["w1"].t()) * (x @ w["w3"].t()))
+        if residual is not None:
+            return step(residual + inner @ w["w2"].t())
+        return step(inner @ w["w2"].t())
     gate = step(torch.nn.functional.silu(step(x @ w["w1"].t())))
     return step(step(gate * step(x @ w["w3"].t())) @ w["w2"].t())
 
@@ -238,7 +243,10 @@ def decoder_layer_decode(cfg, w, x, k_cache, v_cache, position, step=_identity, 
         vb = v_cache[:, :, : position + 1, :].transpose(1, 2)
         ctx = step(fused_attention(q.unsqueeze(1), kb, vb, False)[0]).reshape(b, cfg.heads * d)
         h = step(x + step(ctx @ w["wo"].t()))
-        out = step(h + feed_forward(w, step(rms_norm(h, w["ffn_norm"], cfg.eps)), step, fused_gate_up))
+        if fused_gate_up:
+            out = feed_forward(w, step(rms_norm(h, w["ffn_norm"], cfg.eps)), step, True, residual=h)
+        else:
+            out = step(h + feed_forward(w, step(rms_norm(h, w["ffn_norm"], cfg.eps)), step))
         return out, k_cache, v_cache
     keys = _expand_kv(cfg, k_cache[:, :, : position + 1, :])
     vals = _expand_kv(cfg, v_cache[:, :, : position + 1, :])
