@@ -904,7 +904,7 @@ def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ra
     outs["fused_attention"] = out_g[:n_check].clone()
     devapis.graphDestroy(replay.graph)
     # variant: the whole step through the fused entry points (one q/k/v projection, rotary + cache append, add + RMSNorm,
-    # SiLU * up in the epilogue of one gate / up product, the last residual add in the down projection): nine launches instead of nineteen
+    # SiLU * up in the epilogue of one gate / up product, the last residual add in the down projection): eight launches instead of nineteen
     lay.fused_decode = True
     for _ in range(3):
         lay.decode(xd, kc, vc, length - 1, ctx)
@@ -999,7 +999,7 @@ def run_decode(lay, cfg, ctx, stream, device, dtype, world, barrier, max_over_ra
             "fused_step": {"tokens_per_s": b / (ms_step * 1e-3), "ms_per_step": ms_step,
                            "hbm_frac": round((weight_bytes + kv_bytes) / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
                            "note": "as fused_attention, with one q/k/v projection, diopiB200RopeAppendKV, diopiB200AddRMSNorm and "
-                                   "diopiB200MmSwiGLU (include/diopi/functions_b200.h), diopiAddmm for down projection + residual: nine launches per step"},
+                                   "diopiB200MmSwiGLU (include/diopi/functions_b200.h), diopiAddmm for down projection + residual: eight launches per step"},
             "fused_step_peer_all_reduce": None if ms_step_peer is None else {
                 "tokens_per_s": b / (ms_step_peer * 1e-3), "ms_per_step": ms_step_peer,
                 "note": "as fused_step, with both all-reduces done by one kernel each over peer memory"},

@@ -277,6 +277,40 @@ __global__ void __launch_bounds__(256, 4) ew_repeat_kernel(T* out, const T* dens
     }
 }
 
+// The same operation with one CTA per (tile of the block, repetition) and the block's vectors read through L2 (an 8 MB mask
+// stays there): no loop, so every CTA has all its loads in flight at once like the plain vector kernel, and the grid's second
+// dimension is the repetition, so no index needs a remainder. Preferred; the looping form above serves more than 65535
+// repetitions.
+template <typename T, int REP, typename Op>
+__global__ void __launch_bounds__(256, 4) ew_repeat_tile_kernel(T* out, const T* dense, const T* block, int64_t period, const Op op) {
+    constexpr int V = Vec16<T>::N;
+    constexpr int UNROLL = 4;
+    const int64_t tile0 = static_cast<int64_t>(blockIdx.x) * (256 * UNROLL) + threadIdx.x;
+    const int64_t base = static_cast<int64_t>(blockIdx.y) * period;
+    Vec16<T> x[UNROLL], blk[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        const int64_t iv = tile0 + u * 256;
+        if (iv < period) {
+            x[u] = ld16_stream(dense + (base + iv) * V);
+            blk[u] = ld16(block + iv * V);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        const int64_t iv = tile0 + u * 256;
+        if (iv < period) {
+            Vec16<T> y;
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                const float a = to_f32(x[u].v[e]), b = to_f32(blk[u].v[e]);
+                y.v[e] = from_f32<T>(REP == 1 ? op(a, b) : op(b, a));
+            }
+            st16_stream(out + (base + iv) * V, y);
+        }
+    }
+}
+
 // ---- row kernel --------------------------------------------------------------------------------------------------------
 // Operands of one 2- or 4-byte float dtype whose innermost run is dense (or, for an input, broadcast) while the outer
 // dimensions have arbitrary pitches: transposed views ([B, S, h, D] read as [B, h, S, D]), slices, tables broadcast over
@@ -381,6 +415,15 @@ void launch_vec(const TensorView& out, const void* const* p, const VecPeriods& p
             if (ysplit > reps) ysplit = reps;
             if (ysplit > 65535) ysplit = 65535;
             if (ysplit < 1) ysplit = 1;
+            // one CTA per (tile, repetition) wherever the repetitions fit the grid's second dimension: mask add on the 2 GiB score
+            // tensor 0.75 -> 0.62 ms (1.07 of the copy bandwidth) against the looping form below
+            if (tiles <= 0x7fffffffLL && reps <= 65535) {
+                dim3 grid(static_cast<unsigned>(tiles), static_cast<unsigned>(reps));
+                T* o = static_cast<T*>(out.data);
+                if (rep == 1) ew_repeat_tile_kernel<T, 1, Op><<<grid, 256, 0, stream>>>(o, static_cast<const T*>(p[0]), static_cast<const T*>(p[1]), period, op);
+                else ew_repeat_tile_kernel<T, 0, Op><<<grid, 256, 0, stream>>>(o, static_cast<const T*>(p[1]), static_cast<const T*>(p[0]), period, op);
+                return;
+            }
             if (tiles <= 0x7fffffffLL) {
                 dim3 grid(static_cast<unsigned>(tiles), static_cast<unsigned>(ysplit));
                 T* o = static_cast<T*>(out.data);

@@ -406,8 +406,8 @@ class DecoderLayer:
         return self._wqkv, self._w13
 
     def _decode_fused(self, x, k_cache, v_cache, position, ctx):
-        """The decode step with the library's fused entry points (include/diopi/functions_b200.h): nine launches instead of
-        nineteen. Same arithmetic as the op-by-op step except that SiLU * up is formed in fp32 from the unrounded products."""
+        """The decode step with the library's fused entry points (include/diopi/functions_b200.h): eight launches (nine when the
+        attention splits the keys over CTAs) instead of nineteen. Same arithmetic as the op-by-op step except that SiLU * up is formed in fp32 from the unrounded products."""
         b, d, hq, hk = x.shape[0], self.head_dim, self.heads, self.kv_heads
         length = position + 1
         wqkv, w13 = self._merged_weights()
