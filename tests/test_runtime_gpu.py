@@ -65,6 +65,29 @@ def test_streams_events_copies(devapis):
     devapis.destroyStream(s)
 
 
+def test_large_async_copies_of_ragged_size_arrive_bit_exact(devapis):
+    """memCopyH2DAsync / memCopyD2HAsync issue a transfer above 1 MiB as a train of 256 KiB pieces: a size that is no multiple
+    of the piece (and an odd one) must arrive whole, from pinned and from pageable host memory, at an offset into both buffers."""
+    devapis.setDevice(0)
+    s = devapis.createStream()
+    n = (3 << 20) + 12345
+    src = torch.randint(0, 256, (n + 64,), dtype=torch.uint8)
+    for pinned in (True, False):
+        h_in = src.pin_memory() if pinned else src.clone()
+        h_out = torch.zeros(n + 64, dtype=torch.uint8)
+        h_out = h_out.pin_memory() if pinned else h_out
+        st, d = devapis.mallocDevice(n + 64)
+        assert st == devapis.OpStatus.SUCCESS
+        devapis.memSetAsync(s, d, 0, n + 64)
+        devapis.memCopyH2DAsync(s, n, d + 16, h_in.data_ptr() + 3)
+        devapis.memCopyD2HAsync(s, n, h_out.data_ptr() + 5, d + 16)
+        devapis.syncStream(s)
+        assert torch.equal(h_out[5:5 + n], h_in[3:3 + n])
+        assert int(h_out[:5].sum()) == 0 and int(h_out[5 + n:].sum()) == 0  # nothing written beyond the requested bytes
+        devapis.freeDevice(d)
+    devapis.destroyStream(s)
+
+
 def test_malloc_device_reports_nomem_without_raising(devapis):
     devapis.setDevice(0)
     _, total = devapis.getDeviceStatus(0)
