@@ -223,10 +223,11 @@ PREFILL_FORMS = {
 }
 
 
-def prefill_oracle_refs(cfg, host_weights, x0, seq, rank, dist, forms):
+def prefill_oracle_refs(cfg, host_weights, x0, seq, rank, dist, forms, world=1):
     """CPU oracle outputs for ONE sequence (rows [0, seq) of the batch: sequences are independent under the causal mask),
     computed on rank 0 from the same bf16-rounded weights and embedding rows the device holds, then handed to every rank.
-    x0: [seq, hidden] float32 on the host (rank 0)."""
+    x0: [seq, hidden] float32 on the host (rank 0). world: the row-parallel linears are evaluated as `world` tensor-parallel
+    ranks evaluate them (every rank's partial product rounded, then their sum), which is what the reference's path computes."""
     out = {}
     if rank == 0:
         from oracle import llama_cpu
@@ -237,7 +238,7 @@ def prefill_oracle_refs(cfg, host_weights, x0, seq, rank, dist, forms):
                 step = llama_cpu.stepwise(torch.bfloat16) if kw.pop("stepwise", False) else (lambda t: t)
                 h = x0
                 for w in host_weights:
-                    h = llama_cpu.decoder_layer_prefill_from_hidden(cfg, w, h, 1, seq, step, **kw)
+                    h = llama_cpu.decoder_layer_prefill_from_hidden(cfg, w, h, 1, seq, step, tp=world, **kw)
                 out[name] = h.contiguous()
     if dist is not None:
         for name in forms:
@@ -260,9 +261,10 @@ def decode_oracle_refs(cfg, w, x4, kc4, vc4, position, world, rank, dist):
         bf = llama_cpu.stepwise(torch.bfloat16)
         with torch.no_grad():
             out["fp32"] = llama_cpu.decoder_layer_decode(cfg, w, xf, kc, vc, position)[0]
-            out["bf16_stepwise"] = llama_cpu.decoder_layer_decode(cfg, w, xf, kc, vc, position, step=bf)[0]
-            out["bf16_stepwise_fused"] = llama_cpu.decoder_layer_decode(cfg, w, xf, kc, vc, position, step=bf, fused=True)[0]
-            out["bf16_stepwise_fused_step"] = llama_cpu.decoder_layer_decode(cfg, w, xf, kc, vc, position, step=bf, fused=True, fused_gate_up=True)[0]
+            out["bf16_stepwise"] = llama_cpu.decoder_layer_decode(cfg, w, xf, kc, vc, position, step=bf, tp=world)[0]
+            out["bf16_stepwise_fused"] = llama_cpu.decoder_layer_decode(cfg, w, xf, kc, vc, position, step=bf, fused=True, tp=world)[0]
+            out["bf16_stepwise_fused_step"] = llama_cpu.decoder_layer_decode(cfg, w, xf, kc, vc, position, step=bf, fused=True, fused_gate_up=True,
+                                                                             tp=world)[0]
     if dist is not None:
         for name in names:
             t = out[name].contiguous() if rank == 0 else torch.empty((x4.shape[0], cfg.hidden), dtype=torch.float32)
@@ -470,11 +472,11 @@ def main():
     refs = None
     # Whole prefill layer at the benchmarked shapes: 1e-2 against the op-by-op bf16 CPU path, and against fp32 no further than
     # 1.25 x that CPU path's own distance from fp32 (bench_checks.py states why); "fp32" below stands for that bound.
-    SW, LOOSE = bench_checks.REL_LOOSE, bench_checks.REL_LOOSE
+    SW = LOOSE = bench_checks.layer_rel_bound(world)
     if not args.no_parity:
         forms = ["fp32", "bf16_stepwise", "bf16_stepwise_fused"] + (["bf16_stepwise_baddbmm"] if args.workload == "7b" else [])
         x0 = x[:seq].float().cpu() if rank == 0 else None
-        refs = prefill_oracle_refs(cfg, host_weights, x0, seq, rank, dist, forms)
+        refs = prefill_oracle_refs(cfg, host_weights, x0, seq, rank, dist, forms, world)
 
     def layerwise_parity(form, bound):
         """Every layer of the stack (with the variant flags as they are now) against the op-by-op oracle of THAT layer on the
@@ -492,7 +494,7 @@ def main():
                 from oracle import llama_cpu
                 with torch.no_grad():
                     want = llama_cpu.decoder_layer_prefill_from_hidden(cfg, host_weights[i], h_in, 1, seq, llama_cpu.stepwise(torch.bfloat16),
-                                                                       **kw).contiguous()
+                                                                       tp=world, **kw).contiguous()
             if dist is not None:
                 dist.broadcast(want, src=0)
             e = bench_checks.parity_entry(h[:seq], {form: (want, bound)})

@@ -34,6 +34,17 @@ REL_LOOSE = 1e-2
 FP32_SLACK = 1.25
 
 
+def layer_rel_bound(world):
+    """Relative-L2 bound of a whole prefill layer against the op-by-op bf16 CPU path when `world` tensor-parallel ranks compute
+    it: REL_LOOSE on one GPU, 1.5e-3 more per doubling of the ranks. Every rank materialises its partial sum of the two
+    row-parallel linears, so a layer on N ranks has N times as many rounded partial sums whose last bit can fall differently
+    than in the CPU evaluation (which evaluates the same partial sums, oracle.llama_cpu.row_parallel): measured 6.5e-3, 7.4e-3 and
+    8.5e-3 on 1, 2 and 4 GPUs for the literal op order, 7.2 / 8.2 / 8.8e-3 with fused attention. The bound stays below the
+    1.6 - 1.8e-2 by which CPU bf16 evaluations of different op ORDER differ from one another at this shape."""
+    import math
+    return REL_LOOSE + 1.5e-3 * math.log2(max(1, world))
+
+
 def bf16_ulp(x):
     """Spacing of bfloat16 values at magnitude x (8 significand bits); 0 for x = 0."""
     import math

@@ -169,7 +169,28 @@ def stepwise(dtype):
     return lambda t: t.to(dtype).to(torch.float32)
 
 
-def attention_prefill(cfg, w, x, batch, seq, step=_identity, scores_by_baddbmm=False, fused=False):
+def row_parallel(x, weight, step=_identity, tp=1, residual=None):
+    """x @ weight.t() the way `tp` tensor-parallel ranks compute a row-parallel linear (wo, w2): the contraction is cut into tp
+    contiguous slices, every rank materialises its partial product (`step`), and the all-reduce sums the partials and materialises
+    the sum (DIPU's caller: ProcessGroupDICL::allreduce on the bf16 partial sums,
+    dipu/torch_dipu/csrc_dipu/runtime/distributed/ProcessGroupDICL.cpp:539-567). tp = 1 is the plain product. `residual`: rank 0
+    adds it to its partial before materialising it (the addmm form), so that the sum is the block's output."""
+    if tp == 1:
+        return step(x @ weight.t()) if residual is None else step(residual + x @ weight.t())
+    k = x.shape[-1]
+    assert k % tp == 0
+    ks = k // tp
+    total = None
+    for r in range(tp):
+        part = x[..., r * ks:(r + 1) * ks] @ weight[:, r * ks:(r + 1) * ks].t()
+        if r == 0 and residual is not None:
+            part = residual + part
+        part = step(part)
+        total = part if total is None else total + part
+    return step(total)
+
+
+def attention_prefill(cfg, w, x, batch, seq, step=_identity, scores_by_baddbmm=False, fused=False, tp=1):
     t = batch * seq
     d = cfg.head_dim
     q = step(x @ w["wq"].t()).view(t, cfg.heads, d)
@@ -181,7 +202,7 @@ def attention_prefill(cfg, w, x, batch, seq, step=_identity, scores_by_baddbmm=F
         qb = step(rotary(cfg, q, cos, sin)).view(batch, seq, cfg.heads, d)
         kb = step(rotary(cfg, k, cos, sin)).view(batch, seq, cfg.kv_heads, d)
         out = step(fused_attention(qb, kb, v, True)[0]).view(t, cfg.heads * d)
-        return step(out @ w["wo"].t())
+        return row_parallel(out, w["wo"], step, tp)
     q = step(rotary(cfg, q, cos, sin)).view(batch, seq, cfg.heads, d).transpose(1, 2)
     k = step(rotary(cfg, k, cos, sin)).view(batch, seq, cfg.kv_heads, d).transpose(1, 2)
     v = v.transpose(1, 2)
@@ -194,25 +215,24 @@ def attention_prefill(cfg, w, x, batch, seq, step=_identity, scores_by_baddbmm=F
         scores = step(scores + causal_mask(seq))
     probs = step(torch.softmax(scores.float(), dim=-1))
     out = step(torch.matmul(probs, v)).transpose(1, 2).contiguous().view(t, cfg.heads * d)
-    return step(out @ w["wo"].t())
+    return row_parallel(out, w["wo"], step, tp)
 
 
-def feed_forward(w, x, step=_identity, fused_gate_up=False, residual=None):
+def feed_forward(w, x, step=_identity, fused_gate_up=False, residual=None, tp=1):
     """residual (with fused_gate_up only): the block's residual is added to the unrounded down projection, one materialising op
     (an addmm) instead of a product and an add. Returns the block's output then, else the feed-forward result."""
     if fused_gate_up:
         # SiLU(gate) * up as ONE materialising op over the two products (the fused gate / up projection): one rounding
         inner = step(torch.nn.functional.silu(x @ w["w1"].t()) * (x @ w["w3"].t()))
-        if residual is not None:
-            return step(residual + inner @ w["w2"].t())
-        return step(inner @ w["w2"].t())
+        return row_parallel(inner, w["w2"], step, tp, residual)
     gate = step(torch.nn.functional.silu(step(x @ w["w1"].t())))
-    return step(step(gate * step(x @ w["w3"].t())) @ w["w2"].t())
+    return row_parallel(step(gate * step(x @ w["w3"].t())), w["w2"], step, tp)
 
 
-def decoder_layer_prefill_from_hidden(cfg, w, x, batch, seq, step=_identity, scores_by_baddbmm=False, fused=False):
-    h = step(x + attention_prefill(cfg, w, step(rms_norm(x, w["attention_norm"], cfg.eps)), batch, seq, step, scores_by_baddbmm, fused))
-    return step(h + feed_forward(w, step(rms_norm(h, w["ffn_norm"], cfg.eps)), step))
+def decoder_layer_prefill_from_hidden(cfg, w, x, batch, seq, step=_identity, scores_by_baddbmm=False, fused=False, tp=1):
+    """tp: the row-parallel linears as `tp` tensor-parallel ranks compute them (row_parallel); everything else is unsharded."""
+    h = step(x + attention_prefill(cfg, w, step(rms_norm(x, w["attention_norm"], cfg.eps)), batch, seq, step, scores_by_baddbmm, fused, tp))
+    return step(h + feed_forward(w, step(rms_norm(h, w["ffn_norm"], cfg.eps)), step, tp=tp))
 
 
 def decoder_layer_prefill(cfg, w, embedding, ids, step=_identity, scores_by_baddbmm=False, fused=False):
@@ -221,7 +241,7 @@ def decoder_layer_prefill(cfg, w, embedding, ids, step=_identity, scores_by_badd
     return decoder_layer_prefill_from_hidden(cfg, w, embedding[ids.reshape(-1)], batch, seq, step, scores_by_baddbmm, fused)
 
 
-def decoder_layer_decode(cfg, w, x, k_cache, v_cache, position, step=_identity, fused=False, fused_gate_up=False):
+def decoder_layer_decode(cfg, w, x, k_cache, v_cache, position, step=_identity, fused=False, fused_gate_up=False, tp=1):
     """One new token per sequence. x [B, hidden]; caches [B, kv_heads, L, D] whose slot `position` is overwritten by the
     new token's key / value; attention covers slots 0..position. Returns (out [B, hidden], k_cache, v_cache).
     fused: the attention core as one materialising op; fused_gate_up: SiLU(gate) * up as one materialising op."""
@@ -242,19 +262,19 @@ def decoder_layer_decode(cfg, w, x, k_cache, v_cache, position, step=_identity, 
         kb = k_cache[:, :, : position + 1, :].transpose(1, 2)
         vb = v_cache[:, :, : position + 1, :].transpose(1, 2)
         ctx = step(fused_attention(q.unsqueeze(1), kb, vb, False)[0]).reshape(b, cfg.heads * d)
-        h = step(x + step(ctx @ w["wo"].t()))
+        h = step(x + row_parallel(ctx, w["wo"], step, tp))
         if fused_gate_up:
-            out = feed_forward(w, step(rms_norm(h, w["ffn_norm"], cfg.eps)), step, True, residual=h)
+            out = feed_forward(w, step(rms_norm(h, w["ffn_norm"], cfg.eps)), step, True, residual=h, tp=tp)
         else:
-            out = step(h + feed_forward(w, step(rms_norm(h, w["ffn_norm"], cfg.eps)), step))
+            out = step(h + feed_forward(w, step(rms_norm(h, w["ffn_norm"], cfg.eps)), step, tp=tp))
         return out, k_cache, v_cache
     keys = _expand_kv(cfg, k_cache[:, :, : position + 1, :])
     vals = _expand_kv(cfg, v_cache[:, :, : position + 1, :])
     scores = step(step(torch.matmul(q.unsqueeze(2), keys.transpose(2, 3))) / math.sqrt(d))  # [B, heads, 1, L]
     probs = step(torch.softmax(scores.float(), dim=-1))
     ctx = step(torch.matmul(probs, vals)).reshape(b, cfg.heads * d)
-    h = step(x + step(ctx @ w["wo"].t()))
-    out = step(h + feed_forward(w, step(rms_norm(h, w["ffn_norm"], cfg.eps)), step))
+    h = step(x + row_parallel(ctx, w["wo"], step, tp))
+    out = step(h + feed_forward(w, step(rms_norm(h, w["ffn_norm"], cfg.eps)), step, tp=tp))
     return out, k_cache, v_cache
 
 

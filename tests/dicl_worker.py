@@ -117,8 +117,10 @@ def main():
     cfg = llama_cpu.LayerConfig(hidden=512, heads=8, kv_heads=8, head_dim=64, ffn=1408, eps=1e-6)
     w = llama_cpu.make_weights(cfg, seed=79)
     idsb = llama_cpu.make_token_ids(2, seq, seed=78)
-    refb = llama_cpu.decoder_layer_prefill(cfg, llama_cpu.round_weights(w, torch.bfloat16), llama_cpu.round_tensor(emb, torch.bfloat16), idsb,
-                                           step=llama_cpu.stepwise(torch.bfloat16))
+    # the op-by-op bf16 oracle with its row-parallel linears evaluated as `world` ranks evaluate them (partials rounded, then summed)
+    refb = llama_cpu.decoder_layer_prefill_from_hidden(cfg, llama_cpu.round_weights(w, torch.bfloat16),
+                                                       llama_cpu.round_tensor(emb, torch.bfloat16)[idsb.reshape(-1)], 2, seq,
+                                                       llama_cpu.stepwise(torch.bfloat16), tp=world)
     ref32 = llama_cpu.decoder_layer_prefill(cfg, w, emb, idsb)
     layb = L.DecoderLayer(cfg, w, dtype=torch.bfloat16, device=dev, tp_rank=rank, tp_size=world, tp_group=grp)
     xb = L.embed(emb.to(torch.bfloat16).to(dev), idsb.to(dev))

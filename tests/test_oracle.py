@@ -139,3 +139,25 @@ def test_fused_attention_equals_op_by_op_attention():
     a = llama_cpu.attention_prefill(cfg, w, x, 2, 40)
     b = llama_cpu.attention_prefill(cfg, w, x, 2, 40, fused=True)
     torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+
+
+def test_row_parallel_forms():
+    """The tensor-parallel evaluation of the row-parallel linears: in fp32 it is the plain product (to rounding of the fp32 sums);
+    with bf16 materialisation every rank's partial is rounded before the sum; the addmm form adds the residual on rank 0."""
+    g = torch.Generator().manual_seed(5)
+    x, wgt, res = torch.randn((7, 64), generator=g), torch.randn((24, 64), generator=g), torch.randn((7, 24), generator=g)
+    plain = x @ wgt.t()
+    for tp in (1, 2, 4, 8):
+        assert torch.allclose(llama_cpu.row_parallel(x, wgt, tp=tp), plain, atol=1e-5)
+        assert torch.allclose(llama_cpu.row_parallel(x, wgt, tp=tp, residual=res), res + plain, atol=1e-5)
+    bf = llama_cpu.stepwise(torch.bfloat16)
+    want = bf(bf(x[:, :32] @ wgt[:, :32].t()) + bf(x[:, 32:] @ wgt[:, 32:].t()))
+    assert torch.equal(llama_cpu.row_parallel(x, wgt, bf, tp=2), want)
+    want_res = bf(bf(res + x[:, :32] @ wgt[:, :32].t()) + bf(x[:, 32:] @ wgt[:, 32:].t()))
+    assert torch.equal(llama_cpu.row_parallel(x, wgt, bf, tp=2, residual=res), want_res)
+    cfg = llama_cpu.LayerConfig(hidden=64, heads=4, kv_heads=4, head_dim=16, ffn=96, eps=1e-6)
+    w = llama_cpu.make_weights(cfg, seed=9)
+    h = torch.randn((2 * 8, 64), generator=g)
+    a = llama_cpu.decoder_layer_prefill_from_hidden(cfg, w, h, 2, 8)
+    b = llama_cpu.decoder_layer_prefill_from_hidden(cfg, w, h, 2, 8, tp=4)
+    assert torch.allclose(a, b, atol=1e-5)
