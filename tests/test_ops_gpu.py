@@ -445,9 +445,11 @@ def test_sweep_softmax_bf16(diopi, ctx, t):
 
 
 @pytest.mark.parametrize("rows,cols,dtype", [(4096, 2048, torch.bfloat16), (2000, 264, torch.bfloat16), (1500, 1000, torch.float32),
-                                            (1025, 8, torch.float16), (3000, 1024, torch.float32)])
+                                            (1025, 8, torch.float16), (3000, 1024, torch.float32), (1027, 1544, torch.float16)])
 def test_softmax_many_short_rows(diopi, ctx, rows, cols, dtype):
-    """Score-tensor-like inputs (many rows of at most 256 vectors) take the warp-per-row kernel; causal -inf entries, in place."""
+    """Score-tensor-like inputs (many rows of at most 256 vectors) take the warp-per-row kernel, 2-byte rows of more than 128 vectors
+    the two-warps-per-row one (also with a row count that does not fill the last CTA and a ragged vector count); causal -inf entries,
+    in place."""
     x = rnd((rows, cols), dtype, seed=rows, scale=3.0)
     k = min(rows, cols)
     x[:k, :k] = (x[:k, :k].float() + torch.triu(torch.full((k, k), float("-inf")), diagonal=1)).to(dtype)
