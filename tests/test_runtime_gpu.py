@@ -70,9 +70,9 @@ def test_large_async_copies_of_ragged_size_arrive_bit_exact(devapis):
     of the piece (and an odd one) must arrive whole, from pinned and from pageable host memory, at an offset into both buffers."""
     devapis.setDevice(0)
     s = devapis.createStream()
-    n = (3 << 20) + 12345
-    src = torch.randint(0, 256, (n + 64,), dtype=torch.uint8)
-    for pinned in (True, False):
+    # 3 MiB + 12345: pieces of 256 KiB; 17 MiB + 7: more than 64 such pieces, so the pieces grow to a sixty-fourth of the transfer
+    for n, pinned in (((3 << 20) + 12345, True), ((3 << 20) + 12345, False), ((17 << 20) + 7, True)):
+        src = torch.randint(0, 256, (n + 64,), dtype=torch.uint8)
         h_in = src.pin_memory() if pinned else src.clone()
         h_out = torch.zeros(n + 64, dtype=torch.uint8)
         h_out = h_out.pin_memory() if pinned else h_out
